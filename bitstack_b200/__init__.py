@@ -1,0 +1,11 @@
+"""bitstack_b200: the BitStack residual-block linear layer on B200 (sm_100a).
+
+Public surface (mirrors the reference's operator API):
+    BitStackLinear            module with the reference's constructor / buffers / methods
+    pack_sign, unpack_sign    sign bit packing on the device
+    forward_grouped           several projections of one input in one launch sequence
+"""
+from .linear import BitStackLinear, forward_grouped, get_workspace
+from .pack import pack_sign, unpack_sign
+
+__all__ = ["BitStackLinear", "forward_grouped", "get_workspace", "pack_sign", "unpack_sign"]

@@ -1,0 +1,246 @@
+// extern "C" entry points declared in include/bitstack_b200.h: argument checks,
+// kernel choice, workspace carving.  No device allocation, no host sync (except the
+// *_host variant, whose contract is to return finished host data).
+#include <stdarg.h>
+#include <string.h>
+
+#include "common.cuh"
+
+namespace bsb {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+
+int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+static int check_weight(const bsb_weight* w) {
+  BSB_CHECK_ARG(w != nullptr, "weight is NULL");
+  BSB_CHECK_ARG(w->out_features >= 0 && w->in_features >= 0 && w->k >= 1 && w->blocks >= 0,
+                "bad weight dims out=%d in=%d k=%d blocks=%d", w->out_features, w->in_features, w->k, w->blocks);
+  if (w->blocks > 0 && (int64_t)w->out_features * w->in_features > 0) {
+    BSB_CHECK_ARG(w->qweight && w->u && w->vt, "weight has NULL qweight/u/vt");
+    const int64_t e = (int64_t)w->out_features * w->in_features;
+    BSB_CHECK_ARG(w->blocks == 1 || w->q_block_stride >= (e + 7) / 8, "q_block_stride %lld too small", (long long)w->q_block_stride);
+    BSB_CHECK_ARG(w->blocks == 1 || w->u_block_stride >= (int64_t)w->out_features * w->k, "u_block_stride too small");
+    BSB_CHECK_ARG(w->blocks == 1 || w->vt_block_stride >= (int64_t)w->in_features * w->k, "vt_block_stride too small");
+  }
+  return BSB_OK;
+}
+
+static int pick_algo(const bsb_weight& w, int64_t rows, int algo) {
+  if (algo != BSB_ALGO_AUTO) return algo;
+  if (rows <= 4 && gemv_mma_supported(w)) return BSB_ALGO_GEMV_MMA;
+  if (rebuild_supported(w) && gemm_supported(rows, w.out_features, w.in_features)) return BSB_ALGO_REBUILD_GEMM;
+  return BSB_ALGO_GENERAL;
+}
+
+static int64_t workspace_for(const bsb_weight& w, int64_t rows, int algo) {
+  switch (pick_algo(w, rows, algo)) {
+    case BSB_ALGO_GEMV_MMA:
+      return gemv_mma_workspace_bytes(&w, 1);
+    case BSB_ALGO_REBUILD_GEMM:
+      return align_up64((int64_t)w.out_features * w.in_features * 2, 256);
+    default:
+      return 0;
+  }
+}
+
+// fp16 zero / bias fill for weights with no active block
+__global__ void fill_bias_kernel(__half* y, int64_t rows, int64_t y_stride, int M, const __half* bias) {
+  const int64_t total = rows * M;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / M;
+    const int m = (int)(i % M);
+    y[r * y_stride + m] = bias ? bias[m] : __float2half(0.f);
+  }
+}
+
+static int forward_one(const bsb_weight& w, const __half* x, int64_t rows, int64_t x_stride, __half* y,
+                       int64_t y_stride, void* workspace, int64_t workspace_bytes, int algo, cudaStream_t s) {
+  if (rows == 0 || w.out_features == 0) return BSB_OK;
+  BSB_CHECK_ARG(x != nullptr && y != nullptr, "x or y is NULL");
+  BSB_CHECK_ARG(x_stride >= w.in_features && y_stride >= w.out_features, "row stride smaller than the row");
+  if (w.blocks == 0 || w.in_features == 0) {
+    const int64_t total = rows * w.out_features;
+    fill_bias_kernel<<<(unsigned)min((int64_t)1024, ceil_div64(total, 256)), 256, 0, s>>>(
+        y, rows, y_stride, w.out_features, reinterpret_cast<const __half*>(w.bias));
+    return check_launch("fill_bias_kernel");
+  }
+  const int a = pick_algo(w, rows, algo);
+  const int64_t need = workspace_for(w, rows, a);
+  if (need > 0 && (workspace == nullptr || workspace_bytes < need)) {
+    set_error("workspace of %lld bytes needed, %lld given", (long long)need, (long long)workspace_bytes);
+    return BSB_EWORKSPACE;
+  }
+  switch (a) {
+    case BSB_ALGO_GENERAL:
+      return launch_general_forward(w, x, rows, x_stride, y, y_stride, s);
+    case BSB_ALGO_GEMV_MMA: {
+      BSB_CHECK_ARG(gemv_mma_supported(w), "GEMV_MMA: unsupported shape/alignment (out=%d in=%d k=%d)",
+                    w.out_features, w.in_features, w.k);
+      for (int64_t r = 0; r < rows; ++r) {
+        __half* yr = y + r * y_stride;
+        if (int rc = launch_gemv_mma(&w, 1, x + r * x_stride, &yr, workspace, workspace_bytes, s)) return rc;
+      }
+      return BSB_OK;
+    }
+    case BSB_ALGO_REBUILD_GEMM: {
+      BSB_CHECK_ARG(rebuild_supported(w) && gemm_supported(rows, w.out_features, w.in_features),
+                    "REBUILD_GEMM: unsupported shape/alignment (out=%d in=%d k=%d)", w.out_features,
+                    w.in_features, w.k);
+      BSB_CHECK_ARG((uintptr_t)workspace % 16 == 0, "workspace must be 16-byte aligned");
+      __half* wbuf = (__half*)workspace;
+      if (int rc = launch_rebuild_weight(w, wbuf, s)) return rc;
+      return launch_gemm_xwt(x, rows, x_stride, wbuf, w.out_features, w.in_features,
+                             reinterpret_cast<const __half*>(w.bias), y, y_stride, s);
+    }
+    default:
+      set_error("unknown or unavailable algo %d", a);
+      return BSB_EINVAL;
+  }
+}
+
+}  // namespace bsb
+
+using namespace bsb;
+
+extern "C" {
+
+int bsb_version(void) { return 100; }
+
+const char* bsb_last_error(void) { return g_err; }
+
+int bsb_device_info(int* sm, int* major, int* minor) {
+  int dev = 0;
+  BSB_CUDA(cudaGetDevice(&dev));
+  cudaDeviceProp p;
+  BSB_CUDA(cudaGetDeviceProperties(&p, dev));
+  if (sm) *sm = p.multiProcessorCount;
+  if (major) *major = p.major;
+  if (minor) *minor = p.minor;
+  return BSB_OK;
+}
+
+int bsb_pack_sign(const int8_t* sign, int64_t n, uint8_t* packed, int32_t* bad_count, void* stream) {
+  BSB_CHECK_ARG(n >= 0, "negative element count");
+  BSB_CHECK_ARG(n == 0 || (sign && packed), "NULL buffer");
+  return launch_pack_sign(sign, n, packed, bad_count, (cudaStream_t)stream);
+}
+
+int bsb_unpack_sign(const uint8_t* packed, int64_t n, int8_t* out, void* stream) {
+  BSB_CHECK_ARG(n >= 0, "negative element count");
+  BSB_CHECK_ARG(n == 0 || (packed && out), "NULL buffer");
+  return launch_unpack_sign(packed, n, out, (cudaStream_t)stream);
+}
+
+int bsb_reconstruct_weight(const bsb_weight* w, uint16_t* w_out, void* stream) {
+  if (int rc = check_weight(w)) return rc;
+  if ((int64_t)w->out_features * w->in_features == 0) return BSB_OK;
+  BSB_CHECK_ARG(w_out != nullptr, "output is NULL");
+  if (w->blocks > 0 && rebuild_supported(*w)) return launch_rebuild_weight(*w, (__half*)w_out, (cudaStream_t)stream);
+  return launch_general_reconstruct(*w, (__half*)w_out, (cudaStream_t)stream);
+}
+
+int bsb_vt_absmax(const bsb_weight* w, float* out, void* stream) {
+  if (int rc = check_weight(w)) return rc;
+  BSB_CHECK_ARG(out != nullptr, "output is NULL");
+  return launch_vt_absmax(*w, out, (cudaStream_t)stream);
+}
+
+int64_t bsb_linear_workspace_bytes(const bsb_weight* w, int64_t rows, int algo) {
+  if (check_weight(w) != BSB_OK || rows < 0) return -1;
+  if (w->blocks == 0 || rows == 0) return 0;
+  return workspace_for(*w, rows, algo);
+}
+
+int bsb_linear_forward(const bsb_weight* w, const uint16_t* x, int64_t rows, int64_t x_stride, uint16_t* y,
+                       int64_t y_stride, void* workspace, int64_t workspace_bytes, int algo, void* stream) {
+  if (int rc = check_weight(w)) return rc;
+  BSB_CHECK_ARG(rows >= 0, "negative row count");
+  return forward_one(*w, (const __half*)x, rows, x_stride, (__half*)y, y_stride, workspace, workspace_bytes,
+                     algo, (cudaStream_t)stream);
+}
+
+int bsb_linear_forward_grouped(const bsb_weight* ws, int32_t n_weights, const uint16_t* x, int64_t rows,
+                               int64_t x_stride, uint16_t* const* ys, const int64_t* y_strides, void* workspace,
+                               int64_t workspace_bytes, int algo, void* stream) {
+  BSB_CHECK_ARG(n_weights >= 1 && ws && ys && y_strides, "bad group arguments");
+  BSB_CHECK_ARG(rows >= 0, "negative row count");
+  for (int i = 0; i < n_weights; ++i) {
+    if (int rc = check_weight(&ws[i])) return rc;
+    BSB_CHECK_ARG(ws[i].in_features == ws[0].in_features, "grouped weights must share in_features");
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  // one fused launch sequence when every member qualifies for the decode kernel
+  bool fused = (algo == BSB_ALGO_AUTO || algo == BSB_ALGO_GEMV_MMA) && rows >= 1 && rows <= 4 && n_weights <= 4;
+  for (int i = 0; i < n_weights && fused; ++i)
+    fused = ws[i].blocks > 0 && ws[i].out_features > 0 && gemv_mma_supported(ws[i]);
+  if (fused) {
+    const int64_t need = gemv_mma_workspace_bytes(ws, n_weights);
+    if (workspace == nullptr || workspace_bytes < need) {
+      set_error("workspace of %lld bytes needed, %lld given", (long long)need, (long long)workspace_bytes);
+      return BSB_EWORKSPACE;
+    }
+    for (int64_t r = 0; r < rows; ++r) {
+      __half* yr[4];
+      for (int i = 0; i < n_weights; ++i) yr[i] = (__half*)ys[i] + r * y_strides[i];
+      if (int rc = launch_gemv_mma(ws, n_weights, (const __half*)x + r * x_stride, yr, workspace, workspace_bytes, s))
+        return rc;
+    }
+    return BSB_OK;
+  }
+  for (int i = 0; i < n_weights; ++i) {
+    if (int rc = forward_one(ws[i], (const __half*)x, rows, x_stride, (__half*)ys[i], y_strides[i], workspace,
+                             workspace_bytes, algo, s))
+      return rc;
+  }
+  return BSB_OK;
+}
+
+int64_t bsb_linear_grouped_workspace_bytes(const bsb_weight* ws, int32_t n_weights, int64_t rows, int algo) {
+  if (!ws || n_weights < 1 || rows < 0) return -1;
+  int64_t need = 0;
+  bool fused = (algo == BSB_ALGO_AUTO || algo == BSB_ALGO_GEMV_MMA) && rows >= 1 && rows <= 4 && n_weights <= 4;
+  for (int i = 0; i < n_weights; ++i) {
+    if (check_weight(&ws[i]) != BSB_OK) return -1;
+    fused = fused && ws[i].blocks > 0 && ws[i].out_features > 0 && gemv_mma_supported(ws[i]);
+    if (ws[i].blocks > 0 && rows > 0) need = max(need, workspace_for(ws[i], rows, algo));
+  }
+  if (fused) need = max(need, gemv_mma_workspace_bytes(ws, n_weights));
+  return need;
+}
+
+int bsb_linear_forward_host(const bsb_weight* w, const uint16_t* host_x, int64_t rows, uint16_t* host_y,
+                            uint16_t* dev_x, uint16_t* dev_y, void* workspace, int64_t workspace_bytes, int algo,
+                            void* stream) {
+  if (int rc = check_weight(w)) return rc;
+  BSB_CHECK_ARG(rows >= 0, "negative row count");
+  if (rows == 0) return BSB_OK;
+  BSB_CHECK_ARG(host_x && host_y && dev_x && dev_y, "NULL buffer");
+  cudaStream_t s = (cudaStream_t)stream;
+  BSB_CUDA(cudaMemcpyAsync(dev_x, host_x, (size_t)rows * w->in_features * 2, cudaMemcpyHostToDevice, s));
+  if (int rc = forward_one(*w, (const __half*)dev_x, rows, w->in_features, (__half*)dev_y, w->out_features,
+                           workspace, workspace_bytes, algo, s))
+    return rc;
+  BSB_CUDA(cudaMemcpyAsync(host_y, dev_y, (size_t)rows * w->out_features * 2, cudaMemcpyDeviceToHost, s));
+  BSB_CUDA(cudaStreamSynchronize(s));
+  return BSB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,73 @@
+// Shared helpers for the bitstack_b200 kernels (sm_100a only).
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/bitstack_b200.h"
+
+namespace bsb {
+
+// thread-local error text returned by bsb_last_error()
+void set_error(const char* fmt, ...);
+
+#define BSB_CHECK_ARG(cond, ...)      \
+  do {                                \
+    if (!(cond)) {                    \
+      ::bsb::set_error(__VA_ARGS__);  \
+      return BSB_EINVAL;              \
+    }                                 \
+  } while (0)
+
+#define BSB_CUDA(call)                                                        \
+  do {                                                                        \
+    cudaError_t e__ = (call);                                                 \
+    if (e__ != cudaSuccess) {                                                 \
+      ::bsb::set_error("%s failed: %s (%s:%d)", #call, cudaGetErrorString(e__), \
+                       __FILE__, __LINE__);                                   \
+      return BSB_ECUDA;                                                       \
+    }                                                                         \
+  } while (0)
+
+inline int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error("launch of %s failed: %s", what, cudaGetErrorString(e));
+    return BSB_ECUDA;
+  }
+  return BSB_OK;
+}
+
+static inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
+static inline int64_t align_up64(int64_t a, int64_t b) { return ceil_div64(a, b) * b; }
+
+// number of multiprocessors of the current device (cached per device)
+int sm_count();
+
+// ---- launchers implemented in the kernel translation units -------------------
+int launch_pack_sign(const int8_t* sign, int64_t n, uint8_t* packed, int32_t* bad, cudaStream_t s);
+int launch_unpack_sign(const uint8_t* packed, int64_t n, int8_t* out, cudaStream_t s);
+
+int launch_general_forward(const bsb_weight& w, const __half* x, int64_t rows, int64_t x_stride,
+                           __half* y, int64_t y_stride, cudaStream_t s);
+int launch_general_reconstruct(const bsb_weight& w, __half* w_out, cudaStream_t s);
+
+// fast reconstruction (k == 16, in % 32 == 0, out % 16 == 0)
+bool rebuild_supported(const bsb_weight& w);
+int launch_rebuild_weight(const bsb_weight& w, __half* w_out, cudaStream_t s);
+
+// y[rows][out] = x[rows][in] . W[out][in]^T (+bias), fp16 in, fp32 accumulate
+bool gemm_supported(int64_t rows, int out_features, int in_features);
+int launch_gemm_xwt(const __half* x, int64_t rows, int64_t x_stride, const __half* w,
+                    int out_features, int in_features, const __half* bias, __half* y,
+                    int64_t y_stride, cudaStream_t s);
+
+// decode path: packed signs streamed into fp8 tensor-core MMAs
+int launch_vt_absmax(const bsb_weight& w, float* out, cudaStream_t s);
+bool gemv_mma_supported(const bsb_weight& w);
+int64_t gemv_mma_workspace_bytes(const bsb_weight* ws, int n_weights);
+int launch_gemv_mma(const bsb_weight* ws, int n_weights, const __half* x, __half* const* ys,
+                    void* workspace, int64_t workspace_bytes, cudaStream_t s);
+
+}  // namespace bsb

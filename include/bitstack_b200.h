@@ -1,0 +1,134 @@
+/*
+ * bitstack_b200 -- C ABI of the B200 (sm_100a) BitStack linear hot path.
+ *
+ * Every entry point takes plain device pointers and sizes, enqueues its work on
+ * the CUDA stream it is given (a cudaStream_t passed as void*, NULL = the legacy
+ * default stream), never synchronises the host and never allocates device
+ * memory: scratch space is passed in by the caller.  Return value: 0 on
+ * success, a negative BSB_E* code otherwise; bsb_last_error() then returns a
+ * text describing the failure for the calling thread.
+ *
+ * Storage layout (identical to what the reference module keeps after
+ * stack_blocks(), bitstack/modules/BitStackLinear.py:183-195):
+ *   qweight  uint8  [blocks][out*in/8]   sign bits, 8 per byte, first sign in the
+ *                                         most significant bit, row-major over
+ *                                         (out, in), +1 -> 1, -1 -> 0
+ *   u        fp16   [blocks][out][k]
+ *   vt       fp16   [blocks][k][in]
+ *   bias     fp16   [out] or NULL
+ * Only k == 16 is accelerated (the reference's operating point); other k values
+ * run on the general kernel.
+ */
+#ifndef BITSTACK_B200_H
+#define BITSTACK_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BSB_OK 0
+#define BSB_EINVAL (-1)    /* bad argument (shape, alignment, null pointer) */
+#define BSB_ECUDA (-2)     /* a CUDA runtime call or launch failed */
+#define BSB_EWORKSPACE (-3)/* scratch buffer missing or too small */
+#define BSB_ELIMIT (-4)    /* size beyond a documented maximum */
+
+/* One stacked BitStack weight.  Strides are between consecutive blocks:
+ * q_block_stride in bytes, u/vt_block_stride in fp16 elements.  `blocks` is the
+ * number of ACTIVE blocks (the reference's w_bit); changing it needs no repack
+ * (bitstack/modules/BitStackLinear.py:173-181). */
+typedef struct bsb_weight {
+  const uint8_t* qweight;
+  const uint16_t* u;
+  const uint16_t* vt;
+  const uint16_t* bias; /* may be NULL */
+  const float* vt_absmax; /* optional fp32 [blocks][k]: max |vt| per (block, rank), as
+                             bsb_vt_absmax() writes it; NULL = recomputed on every call */
+  int64_t q_block_stride;
+  int64_t u_block_stride;
+  int64_t vt_block_stride;
+  int32_t out_features;
+  int32_t in_features;
+  int32_t k;
+  int32_t blocks;
+} bsb_weight;
+
+/* Kernel choice for bsb_linear_forward.  AUTO picks by shape and row count. */
+enum {
+  BSB_ALGO_AUTO = 0,
+  BSB_ALGO_GENERAL = 1,   /* any shape, CUDA cores, fp32 */
+  BSB_ALGO_GEMV_MMA = 2,  /* decode: packed signs streamed into fp8 tensor-core MMAs */
+  BSB_ALGO_REBUILD_GEMM = 3, /* batch/prefill: rebuild fp16 W tiles, dense MMA */
+  BSB_ALGO_GEMV_TC5 = 4   /* decode: tcgen05 / tensor-memory variant */
+};
+
+int bsb_version(void);
+const char* bsb_last_error(void);
+
+/* Multiprocessor count etc. of the current device; fills nothing and returns
+ * BSB_ECUDA when there is no usable device. */
+int bsb_device_info(int* sm_count, int* cc_major, int* cc_minor);
+
+/* Replaces pack_sign (bitstack/utils/pack_utils.py:5-18).  sign: n int8 values,
+ * each +1 or -1.  packed: (n+7)/8 bytes; padding bits are written as 0.
+ * If bad_count is not NULL the number of values that are neither +1 nor -1 is
+ * ADDED to *bad_count (device int32; the caller zeroes it) -- the reference
+ * asserts on such input. */
+int bsb_pack_sign(const int8_t* sign, int64_t n, uint8_t* packed, int32_t* bad_count, void* stream);
+
+/* Replaces unpack_sign / unpack_sign_v2 / unpack_sign_triton
+ * (bitstack/utils/pack_utils.py:20-26, 50-82, 84-138, 177-204).
+ * out: n int8 values +1/-1; padding bits are never written. */
+int bsb_unpack_sign(const uint8_t* packed, int64_t n, int8_t* out, void* stream);
+
+/* Replaces the weight reconstruction of the fused levels:
+ * reconstruct_w_triton, unpack_and_reconstruct_w_triton{,_v2,_v3}
+ * (bitstack/utils/inference_utils.py:135-156, 371-387, 465-488, 571-595) and the
+ * per-block loop of forward_l0 (bitstack/modules/BitStackLinear.py:107-113).
+ * w: fp16 [out][in] = sum over active blocks of sign * (u @ vt), accumulated in
+ * fp32 and rounded once. */
+int bsb_reconstruct_weight(const bsb_weight* w, uint16_t* w_out, void* stream);
+
+/* One-time helper for the decode kernels: out[j*k + r] = max_n |vt[j][r][n]| over
+ * the first w->blocks blocks.  No reference counterpart (the reference has no
+ * quantised intermediate); the result only sets the scale of an internal fp8
+ * operand and is a pure function of the stored factors. */
+int bsb_vt_absmax(const bsb_weight* w, float* out, void* stream);
+
+/* Scratch bytes bsb_linear_forward needs for this weight / row count / algo. */
+int64_t bsb_linear_workspace_bytes(const bsb_weight* w, int64_t rows, int algo);
+
+/* Replaces BitStackLinear.forward for every fused level
+ * (bitstack/modules/BitStackLinear.py:88-157): y = x @ W^T (+ bias), fp32
+ * accumulation, fp16 output.  x: [rows][in] fp16 with row stride x_stride
+ * (elements); y: [rows][out] fp16 with row stride y_stride. */
+int bsb_linear_forward(const bsb_weight* w, const uint16_t* x, int64_t rows, int64_t x_stride,
+                       uint16_t* y, int64_t y_stride, void* workspace, int64_t workspace_bytes,
+                       int algo, void* stream);
+
+/* Several weights applied to the SAME x in one launch sequence (q/k/v, gate/up
+ * of a decoder layer; the reference calls the module once per projection,
+ * bitstack/modules/BitStackLinear.py:88-103).  All weights share in_features.
+ * ys[i]: [rows][w[i].out_features], row stride y_strides[i]. */
+int bsb_linear_forward_grouped(const bsb_weight* ws, int32_t n_weights, const uint16_t* x,
+                               int64_t rows, int64_t x_stride, uint16_t* const* ys,
+                               const int64_t* y_strides, void* workspace, int64_t workspace_bytes,
+                               int algo, void* stream);
+
+/* Scratch bytes bsb_linear_forward_grouped needs. */
+int64_t bsb_linear_grouped_workspace_bytes(const bsb_weight* ws, int32_t n_weights, int64_t rows, int algo);
+
+/* Same forward with HOST x and y buffers: copies x to the device, runs the
+ * forward, copies y back and waits for it -- the call a host-only user makes.
+ * dev_x / dev_y are caller-provided device staging buffers of rows*in and
+ * rows*out fp16 elements. */
+int bsb_linear_forward_host(const bsb_weight* w, const uint16_t* host_x, int64_t rows,
+                            uint16_t* host_y, uint16_t* dev_x, uint16_t* dev_y, void* workspace,
+                            int64_t workspace_bytes, int algo, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BITSTACK_B200_H */

@@ -97,6 +97,26 @@ def forward_f64(x, qweight, u, vt, blocks, bias=None) -> np.ndarray:
     return y
 
 
+def forward_f64_rows(x, qweight, u, vt, blocks, row_idx, bias=None) -> np.ndarray:
+    """forward_f64 restricted to the output features in `row_idx` (cheap check at
+    full benchmark sizes)."""
+    row_idx = np.asarray(row_idx)
+    m, n = u.shape[1], vt.shape[2]
+    w = np.zeros((row_idx.size, n), dtype=np.float64)
+    row_bytes_ok = (n % 8 == 0)
+    for j in range(blocks):
+        if row_bytes_ok:
+            bits = np.unpackbits(np.asarray(qweight[j]).reshape(m, n // 8)[row_idx], axis=1)
+            s = bits.astype(np.float64) * 2 - 1
+        else:
+            s = unpack_sign(qweight[j], (m, n))[row_idx].astype(np.float64)
+        w += s * (np.asarray(u[j], dtype=np.float64)[row_idx] @ np.asarray(vt[j], dtype=np.float64))
+    y = np.asarray(x, dtype=np.float64) @ w.T
+    if bias is not None:
+        y = y + np.asarray(bias, dtype=np.float64)[row_idx]
+    return y
+
+
 # ----------------------------------------------------------------------------
 # fp16-semantics restatement of the reference's unfused forward (torch CPU)
 # ----------------------------------------------------------------------------

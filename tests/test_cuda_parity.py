@@ -1,0 +1,367 @@
+"""GPU parity tests: the CUDA path, called through the C ABI, against the CPU oracle
+and against fixtures produced by the reference itself.
+
+Tolerances.  Integer work (pack / unpack) is bit exact.  Outputs are fp16 with fp32
+accumulation; the bar is max|dy| / max|y_ref| <= 1e-2 and rel-L2 <= 1e-2 against the
+reference's unfused forward (whose own fp16 noise is ~5e-4), and the tighter
+`EXACT_TOL` against the float64 meaning of the stored data.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import bitstack_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-2          # vs the reference's fp16 level-0 forward
+EXACT_TOL = 4e-3    # vs float64 evaluation of the same stored tensors
+
+
+@pytest.fixture(scope="module")
+def dev():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    return torch.device("cuda:0")
+
+
+def make_module(q, u, vt, bias, dev, level=6, stacked=True):
+    from bitstack_b200 import BitStackLinear
+    nb, m, k = u.shape
+    n = vt.shape[2]
+    mod = BitStackLinear(w_bit=nb, in_features=n, out_features=m, k=k, bias=bias is not None,
+                         no_avd=False, dev=dev, fused_level=level)
+    for j in range(nb):
+        getattr(mod, f"qweight_{j}").copy_(torch.from_numpy(np.ascontiguousarray(q[j])))
+        getattr(mod, f"u_{j}").copy_(torch.from_numpy(np.ascontiguousarray(u[j])))
+        getattr(mod, f"vt_{j}").copy_(torch.from_numpy(np.ascontiguousarray(vt[j])))
+    if bias is not None:
+        mod.bias.copy_(torch.from_numpy(bias))
+    if stacked:
+        mod.stack_blocks()
+    return mod
+
+
+def errs(y, ref):
+    return orc.max_normalised_error(y, ref), orc.rel_l2_error(y, ref)
+
+
+# --------------------------------------------------------------------------- pack / unpack
+def test_pack_unpack_golden_bit_exact(dev, golden_dir):
+    from bitstack_b200 import pack_sign, unpack_sign
+    z = np.load(os.path.join(golden_dir, "pack_kat.npz"))
+    assert pack_sign(torch.from_numpy(z["kat_sign"]).to(dev)).cpu().tolist() == [128, 1]
+    for i in range(int(z["n_cases"])):
+        s, p = z[f"sign_{i}"], z[f"packed_{i}"]
+        got_p = pack_sign(torch.from_numpy(s).to(dev)).cpu().numpy()
+        assert np.array_equal(got_p, p), f"pack case {i}"
+        got_s = unpack_sign(torch.from_numpy(p).to(dev), s.shape).cpu().numpy()
+        assert np.array_equal(got_s, s), f"unpack case {i}"
+
+
+@pytest.mark.parametrize("n", [0, 1, 7, 8, 9, 31, 32, 33, 255, 4096, 100003, 1 << 22])
+def test_unpack_pack_random_sizes(dev, n):
+    from bitstack_b200 import pack_sign, unpack_sign
+    rng = np.random.default_rng(n)
+    s = (rng.integers(0, 2, size=n) * 2 - 1).astype(np.int8)
+    p_ref = orc.pack_sign(s) if n else np.zeros(0, np.uint8)
+    p = pack_sign(torch.from_numpy(s).to(dev))
+    assert np.array_equal(p.cpu().numpy(), p_ref)
+    back = unpack_sign(p, (n,))
+    assert np.array_equal(back.cpu().numpy(), s)
+
+
+def test_unpack_unaligned_view_and_padding_untouched(dev):
+    from bitstack_b200 import unpack_sign
+    rng = np.random.default_rng(3)
+    raw = torch.from_numpy(rng.integers(0, 256, size=1001, dtype=np.uint8)).to(dev)
+    view = raw[1:]  # 1-byte offset: forces the element-wise path
+    n = 1000 * 8 - 3
+    got = unpack_sign(view, (n,)).cpu().numpy()
+    assert np.array_equal(got, orc.unpack_sign(raw.cpu().numpy()[1:], (n,)))
+
+
+def test_pack_rejects_non_sign(dev):
+    from bitstack_b200 import pack_sign
+    with pytest.raises(AssertionError):
+        pack_sign(torch.tensor([1, 0, -1, 1, 1, 1, 1, 1], dtype=torch.int8, device=dev))
+
+
+def test_unpack_full_layer_is_bit_exact(dev):
+    from bitstack_b200 import unpack_sign
+    rng = np.random.default_rng(9)
+    p = rng.integers(0, 256, size=4096 * 4096 // 8, dtype=np.uint8)
+    got = unpack_sign(torch.from_numpy(p).to(dev), (4096, 4096)).cpu().numpy()
+    ref = np.unpackbits(p).astype(np.int8).reshape(4096, 4096) * 2 - 1
+    assert np.array_equal(got, ref)
+
+
+# --------------------------------------------------------------------------- reconstruction
+@pytest.mark.parametrize("fname", ["decomp_small.npz", "decomp_1024.npz"])
+def test_reconstruct_weight_matches_oracle(dev, golden_dir, fname):
+    z = np.load(os.path.join(golden_dir, fname))
+    q, u, vt = z["qweight"], z["u"], z["vt"]
+    nb, m, _ = u.shape
+    n = vt.shape[2]
+    mod = make_module(q, u, vt, None, dev)
+    for b in z["bits"]:
+        mod.set_bit(int(b))
+        w = mod.reconstruct_weight().cpu().numpy()
+        w64 = orc.reconstruct_f64(q, u, vt, int(b), m, n)
+        assert np.max(np.abs(w - w64)) <= 1e-3 * np.max(np.abs(w64)) + 1e-6
+        w_l0 = orc.reconstruct_l0(q, u, vt, int(b)).numpy()
+        assert orc.max_normalised_error(w, w_l0) <= 5e-3
+
+
+# --------------------------------------------------------------------------- forward vs golden
+@pytest.mark.parametrize("level", [6, 7, 8, 9])
+@pytest.mark.parametrize("fname", ["decomp_small.npz", "decomp_1024.npz"])
+def test_forward_matches_reference_fixtures(dev, golden_dir, fname, level):
+    z = np.load(os.path.join(golden_dir, fname))
+    q, u, vt = z["qweight"], z["u"], z["vt"]
+    bias = z["bias"] if "bias" in z.files else None
+    n = vt.shape[2]
+    if level in (8, 9) and n % 128 != 0:
+        pytest.skip("tensor-core kernels need in_features % 128 == 0; ragged shapes use the general kernel")
+    mod = make_module(q, u, vt, bias, dev, level=level)
+    for rows in z["rows"]:
+        x = torch.from_numpy(z[f"x_{rows}"]).to(dev)
+        for b in z["bits"]:
+            mod.set_bit(int(b))
+            y = mod(x).float().cpu().numpy()
+            y_ref = z[f"y_{rows}_{b}"].astype(np.float64)
+            e_max, e_l2 = errs(y, y_ref)
+            assert e_max <= TOL and e_l2 <= TOL, (fname, level, rows, b, e_max, e_l2)
+            y64 = orc.forward_f64(z[f"x_{rows}"], q, u, vt, int(b), bias)
+            e_max, e_l2 = errs(y, y64)
+            assert e_max <= EXACT_TOL and e_l2 <= EXACT_TOL, ("f64", fname, level, rows, b, e_max, e_l2)
+
+
+@pytest.mark.parametrize("level", [6, 7, 8, 9])
+def test_forward_matches_reference_synthetic(dev, golden_dir, level):
+    z = np.load(os.path.join(golden_dir, "synth_l0.npz"))
+    cache = {}
+    for (m, n, nb, seed, rows, a) in z["cases"]:
+        key = (int(m), int(n), int(nb), int(seed))
+        if key not in cache:
+            q, u, vt = orc.synthetic_layer(*key)
+            cache[key] = (q, u, vt, make_module(q, u, vt, None, dev, level=level))
+        q, u, vt, mod = cache[key]
+        if level == 7 and m * n * a * rows > 1024 * 4096 * 16:
+            continue
+        x_np = orc.synthetic_input(int(rows), int(n), int(seed) + 1000)
+        mod.set_bit(int(a))
+        y = mod(torch.from_numpy(x_np).to(dev)).float().cpu().numpy()
+        y_ref = z[f"y_{m}_{n}_{seed}_{rows}_{a}"].astype(np.float64)
+        e_max, e_l2 = errs(y, y_ref)
+        assert e_max <= TOL and e_l2 <= TOL, (level, key, rows, a, e_max, e_l2)
+        y64 = orc.forward_f64(x_np, q, u, vt, int(a))
+        e_max, e_l2 = errs(y, y64)
+        assert e_max <= EXACT_TOL and e_l2 <= EXACT_TOL, ("f64", level, key, rows, a, e_max, e_l2)
+
+
+# --------------------------------------------------------------------------- benchmark shapes
+LLAMA8B = {"q": (4096, 4096), "k": (1024, 4096), "gate": (14336, 4096), "down": (4096, 14336)}
+
+
+@pytest.mark.parametrize("name", list(LLAMA8B))
+@pytest.mark.parametrize("rows", [1, 4, 16, 64])
+def test_llama8b_shapes_against_oracle_rows(dev, name, rows):
+    m, n = LLAMA8B[name]
+    nb = 16
+    q, u, vt = orc.synthetic_layer(m, n, nb, seed=200 + m % 97 + n % 89)
+    x_np = orc.synthetic_input(rows, n, seed=17 + rows)
+    mod = make_module(q, u, vt, None, dev, level=6)
+    rng = np.random.default_rng(5)
+    idx = np.sort(rng.choice(m, size=96, replace=False))
+    active = {"q": 16, "k": 2, "gate": 7, "down": 11}[name]
+    mod.set_bit(active)
+    y = mod(torch.from_numpy(x_np).to(dev)).float().cpu().numpy()
+    assert y.shape == (rows, m)
+    y64 = orc.forward_f64_rows(x_np, q, u, vt, active, idx)
+    e_max, e_l2 = errs(y[:, idx], y64)
+    assert e_max <= EXACT_TOL and e_l2 <= EXACT_TOL, (name, rows, e_max, e_l2)
+    # the general CUDA-core kernel (fp32, no quantised operand) must agree on every output
+    if rows == 1:
+        mod.fused_level = 7
+        y_gen = mod(torch.from_numpy(x_np).to(dev)).float().cpu().numpy()
+        e_max, e_l2 = errs(y, y_gen)
+        assert e_max <= EXACT_TOL and e_l2 <= EXACT_TOL, ("vs general", name, rows, e_max, e_l2)
+
+
+def test_prefill_2048_tokens(dev):
+    m, n, nb = 4096, 4096, 8
+    q, u, vt = orc.synthetic_layer(m, n, nb, seed=77)
+    x_np = orc.synthetic_input(2048, n, seed=78)
+    mod = make_module(q, u, vt, None, dev, level=6)
+    y = mod(torch.from_numpy(x_np).to(dev).view(2, 1024, n))
+    assert y.shape == (2, 1024, m)
+    y = y.float().cpu().numpy().reshape(2048, m)
+    idx = np.arange(0, m, 61)
+    y64 = orc.forward_f64_rows(x_np, q, u, vt, nb, idx)
+    e_max, e_l2 = errs(y[:, idx], y64)
+    assert e_max <= EXACT_TOL and e_l2 <= EXACT_TOL, (e_max, e_l2)
+
+
+def test_real_decomposition_4096(dev):
+    """The 'real weights' configuration at full size: W ~ N(0, 0.02) 4096x4096,
+    8 residual blocks, k 16, decomposed with the reference's recipe (on the GPU
+    here), y at 2 / 4 / 8 active blocks against the CPU oracle on the same tensors."""
+    from bitstack_b200 import BitStackLinear
+    torch.manual_seed(0)
+    lin = torch.nn.Linear(4096, 4096, bias=False)
+    with torch.no_grad():
+        lin.weight.copy_(torch.randn(4096, 4096) * 0.02)
+    lin = lin.to(dev)
+    mod = BitStackLinear.from_linear(lin, w_bit=8, k=16, bias=False, fused_level=6)
+    q = np.stack([getattr(mod, f"qweight_{i}").cpu().numpy() for i in range(8)])
+    u = np.stack([getattr(mod, f"u_{i}").cpu().numpy() for i in range(8)])
+    vt = np.stack([getattr(mod, f"vt_{i}").cpu().numpy() for i in range(8)])
+    # the decomposition must approximate W better with every block
+    w = lin.weight.detach().float().cpu().numpy()
+    x_np = orc.synthetic_input(1, 4096, seed=5)
+    x = torch.from_numpy(x_np).to(dev)
+    idx = np.arange(0, 4096, 37)
+    prev = None
+    for b in (2, 4, 8):
+        mod.set_bit(b)
+        y = mod(x).float().cpu().numpy()
+        y_l0 = orc.forward_l0(x_np, q, u, vt, b).float().numpy()
+        e_max, e_l2 = errs(y, y_l0)
+        assert e_max <= TOL and e_l2 <= TOL, (b, e_max, e_l2)
+        y64 = orc.forward_f64_rows(x_np, q, u, vt, b, idx)
+        e_max, e_l2 = errs(y[:, idx], y64)
+        assert e_max <= EXACT_TOL and e_l2 <= EXACT_TOL, ("f64", b, e_max, e_l2)
+        approx = orc.rel_l2_error(y, x_np.astype(np.float64) @ w.T.astype(np.float64))
+        assert prev is None or approx < prev
+        prev = approx
+
+
+# --------------------------------------------------------------------------- API behaviour
+def test_set_bit_needs_no_repack_and_is_deterministic(dev):
+    q, u, vt = orc.synthetic_layer(512, 1024, 6, seed=31)
+    x_np = orc.synthetic_input(1, 1024, seed=32)
+    x = torch.from_numpy(x_np).to(dev)
+    mod = make_module(q, u, vt, None, dev, level=8)
+    outs = {}
+    for b in (6, 1, 3, 6):
+        mod.set_bit(b)
+        y = mod(x)
+        if b in outs:
+            assert torch.equal(outs[b], y), "same block count must give bit-identical output"
+        outs[b] = y
+        e_max, _ = errs(y.float().cpu().numpy(), orc.forward_f64(x_np, q, u, vt, b))
+        assert e_max <= EXACT_TOL
+    mod.set_bit(7)
+    with pytest.raises(ValueError):
+        mod(x)
+
+
+def test_level0_keeps_checkpoint_buffers(dev):
+    q, u, vt = orc.synthetic_layer(256, 512, 3, seed=41)
+    x_np = orc.synthetic_input(2, 512, seed=42)
+    mod = make_module(q, u, vt, None, dev, level=0, stacked=False)
+    y = mod(torch.from_numpy(x_np).to(dev)).float().cpu().numpy()
+    assert "qweight_2" in mod.state_dict()
+    e_max, _ = errs(y, orc.forward_f64(x_np, q, u, vt, 3))
+    assert e_max <= EXACT_TOL
+    # loading new values into the buffers must be seen by the next forward
+    q2, u2, vt2 = orc.synthetic_layer(256, 512, 3, seed=43)
+    sd = {f"qweight_{j}": torch.from_numpy(q2[j]) for j in range(3)}
+    sd.update({f"u_{j}": torch.from_numpy(u2[j]) for j in range(3)})
+    sd.update({f"vt_{j}": torch.from_numpy(vt2[j]) for j in range(3)})
+    mod.load_state_dict(sd)
+    y2 = mod(torch.from_numpy(x_np).to(dev)).float().cpu().numpy()
+    e_max, _ = errs(y2, orc.forward_f64(x_np, q2, u2, vt2, 3))
+    assert e_max <= EXACT_TOL
+
+
+def test_bias_3d_input_and_empty_batch(dev):
+    q, u, vt = orc.synthetic_layer(128, 256, 2, seed=51)
+    bias = (np.random.default_rng(1).standard_normal(128) * 0.1).astype(np.float16)
+    mod = make_module(q, u, vt, bias, dev, level=6)
+    x_np = orc.synthetic_input(6, 256, seed=52)
+    y = mod(torch.from_numpy(x_np).to(dev).view(2, 3, 256))
+    assert y.shape == (2, 3, 128) and y.dtype == torch.float16
+    e_max, _ = errs(y.float().cpu().numpy().reshape(6, 128), orc.forward_f64(x_np, q, u, vt, 2, bias))
+    assert e_max <= EXACT_TOL
+    y1 = mod(torch.from_numpy(x_np[:1]).to(dev))
+    e_max, _ = errs(y1.float().cpu().numpy(), orc.forward_f64(x_np[:1], q, u, vt, 2, bias))
+    assert e_max <= EXACT_TOL
+    empty = mod(torch.zeros(0, 256, dtype=torch.float16, device=dev))
+    assert empty.shape == (0, 128)
+    mod.set_bit(0)  # no active block: bias only
+    y0 = mod(torch.from_numpy(x_np).to(dev)).float().cpu().numpy()
+    assert np.allclose(y0, np.broadcast_to(bias.astype(np.float32), (6, 128)))
+
+
+def test_linearity_and_block_additivity(dev):
+    """Size-independent properties: y(a x1 + x2) = a y(x1) + y(x2); the output with b
+    blocks equals the sum of single-block outputs."""
+    from bitstack_b200 import BitStackLinear
+    m, n, nb = 1024, 2048, 4
+    q, u, vt = orc.synthetic_layer(m, n, nb, seed=61)
+    mod = make_module(q, u, vt, None, dev, level=8)
+    x1 = torch.from_numpy(orc.synthetic_input(1, n, 62)).to(dev)
+    x2 = torch.from_numpy(orc.synthetic_input(1, n, 63)).to(dev)
+    y12 = mod((x1.float() * 0.5 + x2.float()).half()).float()
+    ysum = mod(x1).float() * 0.5 + mod(x2).float()
+    assert (y12 - ysum).abs().max() <= 6e-3 * ysum.abs().max()
+    total = torch.zeros(1, m, device=dev)
+    for j in range(nb):
+        single = make_module(q[j:j + 1], u[j:j + 1], vt[j:j + 1], None, dev, level=8)
+        total += single(x1).float()
+    assert (total - mod(x1).float()).abs().max() <= 4e-3 * total.abs().max()
+
+
+def test_grouped_projections_match_individual(dev):
+    from bitstack_b200 import forward_grouped
+    n = 4096
+    shapes = [(4096, 5), (1024, 2), (1024, 9)]
+    mods = []
+    for i, (m, act) in enumerate(shapes):
+        q, u, vt = orc.synthetic_layer(m, n, 10, seed=300 + i)
+        mod = make_module(q, u, vt, None, dev, level=6)
+        mod.set_bit(act)
+        mods.append(mod)
+    x = torch.from_numpy(orc.synthetic_input(1, n, 99)).to(dev)
+    ys = forward_grouped(mods, x)
+    for mod, y in zip(mods, ys):
+        assert torch.equal(y, mod(x))
+
+
+def test_host_buffer_entry_point(dev):
+    import ctypes as C
+    from bitstack_b200 import _lib, get_workspace
+    q, u, vt = orc.synthetic_layer(512, 1024, 3, seed=71)
+    mod = make_module(q, u, vt, None, dev, level=6)
+    x_np = orc.synthetic_input(1, 1024, seed=72)
+    hx = torch.from_numpy(x_np).pin_memory()
+    hy = torch.empty(1, 512, dtype=torch.float16).pin_memory()
+    dx = torch.empty(1, 1024, dtype=torch.float16, device=dev)
+    dy = torch.empty(1, 512, dtype=torch.float16, device=dev)
+    d = mod.weight_desc(dev)
+    lib = _lib.load()
+    need = lib.bsb_linear_workspace_bytes(C.byref(d), 1, 0)
+    ws = get_workspace(dev, need)
+    torch.cuda.synchronize()
+    rc = lib.bsb_linear_forward_host(C.byref(d), hx.data_ptr(), 1, hy.data_ptr(), dx.data_ptr(), dy.data_ptr(),
+                                     ws.data_ptr(), ws.numel(), 0, torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, lib.bsb_last_error()
+    e_max, _ = errs(hy.float().numpy(), orc.forward_f64(x_np, q, u, vt, 3))
+    assert e_max <= EXACT_TOL
+
+
+def test_workspace_too_small_is_an_error_not_a_fault(dev):
+    import ctypes as C
+    from bitstack_b200 import _lib
+    q, u, vt = orc.synthetic_layer(256, 512, 2, seed=81)
+    mod = make_module(q, u, vt, None, dev, level=6)
+    d = mod.weight_desc(dev)
+    x = torch.zeros(1, 512, dtype=torch.float16, device=dev)
+    y = torch.zeros(1, 256, dtype=torch.float16, device=dev)
+    lib = _lib.load()
+    rc = lib.bsb_linear_forward(C.byref(d), x.data_ptr(), 1, 512, y.data_ptr(), 256, None, 0, 0, None)
+    assert rc == -3 and b"workspace" in lib.bsb_last_error()
