@@ -45,6 +45,7 @@ static int check_weight(const bsb_weight* w) {
 
 static int pick_algo(const bsb_weight& w, int64_t rows, int algo) {
   if (algo != BSB_ALGO_AUTO) return algo;
+  if (rows <= 4 && gemv_tc5_supported(w)) return BSB_ALGO_GEMV_TC5;
   if (rows <= 4 && gemv_mma_supported(w)) return BSB_ALGO_GEMV_MMA;
   if (rebuild_supported(w) && gemm_supported(rows, w.out_features, w.in_features)) return BSB_ALGO_REBUILD_GEMM;
   return BSB_ALGO_GENERAL;
@@ -54,6 +55,8 @@ static int64_t workspace_for(const bsb_weight& w, int64_t rows, int algo) {
   switch (pick_algo(w, rows, algo)) {
     case BSB_ALGO_GEMV_MMA:
       return gemv_mma_workspace_bytes(&w, 1);
+    case BSB_ALGO_GEMV_TC5:
+      return gemv_tc5_workspace_bytes(&w, 1);
     case BSB_ALGO_REBUILD_GEMM:
       return align_up64((int64_t)w.out_features * w.in_features * 2, 256);
     default:
@@ -97,6 +100,15 @@ static int forward_one(const bsb_weight& w, const __half* x, int64_t rows, int64
       for (int64_t r = 0; r < rows; ++r) {
         __half* yr = y + r * y_stride;
         if (int rc = launch_gemv_mma(&w, 1, x + r * x_stride, &yr, workspace, workspace_bytes, s)) return rc;
+      }
+      return BSB_OK;
+    }
+    case BSB_ALGO_GEMV_TC5: {
+      BSB_CHECK_ARG(gemv_tc5_supported(w), "GEMV_TC5: unsupported shape/alignment (out=%d in=%d k=%d)",
+                    w.out_features, w.in_features, w.k);
+      for (int64_t r = 0; r < rows; ++r) {
+        __half* yr = y + r * y_stride;
+        if (int rc = launch_gemv_tc5(&w, 1, x + r * x_stride, &yr, workspace, workspace_bytes, s)) return rc;
       }
       return BSB_OK;
     }
@@ -188,11 +200,13 @@ int bsb_linear_forward_grouped(const bsb_weight* ws, int32_t n_weights, const ui
   }
   cudaStream_t s = (cudaStream_t)stream;
   // one fused launch sequence when every member qualifies for the decode kernel
-  bool fused = (algo == BSB_ALGO_AUTO || algo == BSB_ALGO_GEMV_MMA) && rows >= 1 && rows <= 4 && n_weights <= 4;
+  const bool use_tc5 = (algo == BSB_ALGO_AUTO || algo == BSB_ALGO_GEMV_TC5);
+  bool fused = (use_tc5 || algo == BSB_ALGO_GEMV_MMA) && rows >= 1 && rows <= 4 && n_weights <= 4;
   for (int i = 0; i < n_weights && fused; ++i)
-    fused = ws[i].blocks > 0 && ws[i].out_features > 0 && gemv_mma_supported(ws[i]);
+    fused = ws[i].blocks > 0 && ws[i].out_features > 0 &&
+            (use_tc5 ? gemv_tc5_supported(ws[i]) : gemv_mma_supported(ws[i]));
   if (fused) {
-    const int64_t need = gemv_mma_workspace_bytes(ws, n_weights);
+    const int64_t need = use_tc5 ? gemv_tc5_workspace_bytes(ws, n_weights) : gemv_mma_workspace_bytes(ws, n_weights);
     if (workspace == nullptr || workspace_bytes < need) {
       set_error("workspace of %lld bytes needed, %lld given", (long long)need, (long long)workspace_bytes);
       return BSB_EWORKSPACE;
@@ -200,8 +214,10 @@ int bsb_linear_forward_grouped(const bsb_weight* ws, int32_t n_weights, const ui
     for (int64_t r = 0; r < rows; ++r) {
       __half* yr[4];
       for (int i = 0; i < n_weights; ++i) yr[i] = (__half*)ys[i] + r * y_strides[i];
-      if (int rc = launch_gemv_mma(ws, n_weights, (const __half*)x + r * x_stride, yr, workspace, workspace_bytes, s))
-        return rc;
+      const int rc = use_tc5
+          ? launch_gemv_tc5(ws, n_weights, (const __half*)x + r * x_stride, yr, workspace, workspace_bytes, s)
+          : launch_gemv_mma(ws, n_weights, (const __half*)x + r * x_stride, yr, workspace, workspace_bytes, s);
+      if (rc) return rc;
     }
     return BSB_OK;
   }
@@ -216,14 +232,24 @@ int bsb_linear_forward_grouped(const bsb_weight* ws, int32_t n_weights, const ui
 int64_t bsb_linear_grouped_workspace_bytes(const bsb_weight* ws, int32_t n_weights, int64_t rows, int algo) {
   if (!ws || n_weights < 1 || rows < 0) return -1;
   int64_t need = 0;
-  bool fused = (algo == BSB_ALGO_AUTO || algo == BSB_ALGO_GEMV_MMA) && rows >= 1 && rows <= 4 && n_weights <= 4;
+  const bool use_tc5 = (algo == BSB_ALGO_AUTO || algo == BSB_ALGO_GEMV_TC5);
+  bool fused = (use_tc5 || algo == BSB_ALGO_GEMV_MMA) && rows >= 1 && rows <= 4 && n_weights <= 4;
   for (int i = 0; i < n_weights; ++i) {
     if (check_weight(&ws[i]) != BSB_OK) return -1;
-    fused = fused && ws[i].blocks > 0 && ws[i].out_features > 0 && gemv_mma_supported(ws[i]);
+    fused = fused && ws[i].blocks > 0 && ws[i].out_features > 0 &&
+            (use_tc5 ? gemv_tc5_supported(ws[i]) : gemv_mma_supported(ws[i]));
     if (ws[i].blocks > 0 && rows > 0) need = max(need, workspace_for(ws[i], rows, algo));
   }
-  if (fused) need = max(need, gemv_mma_workspace_bytes(ws, n_weights));
+  if (fused) need = max(need, use_tc5 ? gemv_tc5_workspace_bytes(ws, n_weights) : gemv_mma_workspace_bytes(ws, n_weights));
   return need;
+}
+
+int bsb_debug_gemv_status(const bsb_weight* ws, int32_t n_weights, const void* workspace, int32_t* status_out) {
+  BSB_CHECK_ARG(ws && workspace && status_out, "NULL argument");
+  const int64_t off = gemv_tc5_status_offset(ws, n_weights);
+  BSB_CHECK_ARG(off >= 0, "bad group size");
+  BSB_CUDA(cudaMemcpy(status_out, (const uint8_t*)workspace + off, 4, cudaMemcpyDeviceToHost));
+  return BSB_OK;
 }
 
 int bsb_linear_forward_host(const bsb_weight* w, const uint16_t* host_x, int64_t rows, uint16_t* host_y,

@@ -1,0 +1,614 @@
+// Decode path, tcgen05 generation: packed sign bits -> e4m3 operand in TENSOR MEMORY
+// -> tcgen05.mma (kind::f8f6f4, M=128, N=32, K=32) with the x-scaled factors Z' as the
+// shared-memory operand, staged by bulk TMA copies.
+//
+// Replaces, for single-row inputs, every fused level of the reference forward
+// (bitstack/modules/BitStackLinear.py:116-157).
+//
+// Math (see also gemv_mma.cu).  For block j, Z_j[n,r] = Vt_j[r,n] x[n] and
+//     y[m] = sum_j sum_r U_j[m,r] D_j[m,r],   D_j[m,r] = sum_n S_j[m,n] Z_j[n,r].
+// A 32-bit word of packed signs (32 columns of one row) is expanded by eight logic
+// instructions into eight registers of four e4m3 numbers: register i holds, in byte
+// c, the number v0_i + b d_i where b is the sign bit of column 8c+7-i (class table
+// below).  The eight registers are one row of a 128 x 32 A operand and go to tensor
+// memory with tcgen05.st.  The B operand (32 x 32) holds Z'[n,r] = 2 s_r Z / d_class(n)
+// as two e4m3 pieces (rows 0-15 "hi", 16-31 "lo") in the same K order, so
+//     T[m,r] = D_hi + D_lo = C_r + 2 s_r sum_n b Z,    D_j[m,r] = (T - C_r)/s_r - sum_n Z.
+//
+// CTA = 192 threads: warps 0-3 stream sign bytes (cp.async FIFO in shared memory, one
+// row per thread), expand, feed tensor memory, and run the epilogue; warp 4 issues the
+// MMAs; warp 5 owns tensor-memory allocation and the Z' bulk copies.  All hand-offs
+// are mbarriers with time-bounded waits: on a timeout the kernel raises a status word
+// and leaves, it never spins forever.
+#include <cuda_fp8.h>
+
+#include "common.cuh"
+
+namespace bsb {
+
+namespace {
+
+constexpr int kChunkCols = 512;                 // columns per Z' slab / per 64 B of a sign row
+constexpr int kChunkBytes = kChunkCols * 32;    // 16 words x 1 KB operand tile
+constexpr int kTileRows = 128;
+constexpr int kThreads = 192;
+constexpr int kNA = 6;                          // A-operand ring stages (32 tensor-memory columns each)
+constexpr int kNZ = 3;                          // Z' slabs resident in shared memory
+constexpr int kNP = 4;                          // sign chunks in the per-thread FIFO
+constexpr int kTmemCols = 256;                  // 32 (D) + kNA*32 (A ring) rounded up to a power of two
+constexpr int kMaxGroup = 4;
+constexpr float kTargetMax = 320.f;
+constexpr float kMinD = 0.75f;
+constexpr uint64_t kWaitLimitNs = 200ull * 1000 * 1000;
+
+__constant__ float kV0[8] = {8.f, 4.f, 2.f, 0.75f, 0.375f, 0.09375f, 0.f, 1.f};
+__constant__ float kD[8] = {1.f, 1.f, 1.f, 0.75f, 1.125f, 1.40625f, 2.f, -2.f};
+__host__ __device__ constexpr uint32_t class_byte(int i) {
+  return i == 0 ? 0x50u : i == 1 ? 0x48u : i == 2 ? 0x40u : i == 3 ? 0x34u
+       : i == 4 ? 0x2Cu : i == 5 ? 0x1Cu : i == 6 ? 0x00u : 0x38u;
+}
+
+struct TcParams {
+  bsb_weight w[kMaxGroup];
+  const float* vt_absmax[kMaxGroup];
+  __half* y[kMaxGroup];
+  int n_weights;
+  int n_chunks;                    // ceil(in / 512)
+  int item_base[kMaxGroup + 1];
+  int tile_base[kMaxGroup + 1];    // first 128-row tile of each weight
+  int blk_base[kMaxGroup + 1];
+  int splits[kMaxGroup];
+  int chunks_per_item[kMaxGroup];
+  uint8_t* zops;     // [(weight,block)][chunk][16 KB]
+  float* kconst;     // [(weight,block)][chunk][16]
+  float* inv_scale;  // [(weight,block)][16]
+  int* counters;     // [row tile]
+  int* status;       // 0 = fine, else the code of the wait that gave up
+  float* partials;
+  int64_t part_base[kMaxGroup];
+};
+
+// ------------------------------------------------------------------ PTX helpers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+               : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// time-bounded wait; false = gave up
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+#pragma unroll 1
+  for (int i = 0; i < 256; ++i)
+    if (mbar_test(bar, parity)) return true;
+  const uint64_t t0 = global_ns();
+#pragma unroll 1
+  while (true) {
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i) {
+      if (mbar_test(bar, parity)) return true;
+      __nanosleep(40);
+    }
+    if (global_ns() - t0 > kWaitLimitNs) return false;
+  }
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst, int cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst)), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, int cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+}
+// D[tmem] (+)= A[tmem] . B[smem]^T, e4m3 x e4m3 -> f32
+__device__ __forceinline__ void mma_ts_f8(uint32_t d, uint32_t a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n}"
+      ::"r"(d), "r"(a), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// K-major operand without swizzle: 8-row x 16-byte core matrices; the two 16-byte K
+// halves of a core-matrix row group are `lbo` bytes apart, row groups `sbo` bytes apart
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+  d |= (uint64_t)((lbo >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;
+  return d;
+}
+__host__ __device__ constexpr uint32_t make_idesc_f8(int M, int N) {
+  return (1u << 4) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_u32(smem)), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void bulk_g2s(void* smem, const void* gmem, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(smem)), "l"(gmem), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ float e4m3_to_float(uint8_t v) {
+  const __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)v, __NV_E4M3);
+  return __half2float(__half(h));
+}
+template <int I>
+__device__ __forceinline__ uint32_t expand(uint32_t word) {
+  return (word & (0x01010101u << I)) | (class_byte(I) * 0x01010101u);
+}
+__device__ __forceinline__ void expand_word(uint32_t word, uint32_t* r) {
+  r[0] = expand<0>(word); r[1] = expand<1>(word); r[2] = expand<2>(word); r[3] = expand<3>(word);
+  r[4] = expand<4>(word); r[5] = expand<5>(word); r[6] = expand<6>(word); r[7] = expand<7>(word);
+}
+
+// ------------------------------------------------------------------ Z' preparation
+// grid = (n_chunks, total blocks), 256 threads.  Operand tile of word w (32 columns):
+// byte offset (n%8)*16 + (n/8)*256 + (k%16) + (k/16)*128 with n = 16*piece + rank and
+// k = 4*i + c for the column 8c+7-i of the word.
+__global__ void __launch_bounds__(256) zprep_tc5_kernel(TcParams P, const __half* __restrict__ x) {
+  __shared__ __align__(16) __half vt_s[16][kChunkCols + 8];
+  __shared__ float x_s[kChunkCols];
+  __shared__ float red[8];
+  __shared__ float kred[16][16];
+
+  const int chunk = blockIdx.x;
+  int wi = 0;
+  while (wi + 1 < P.n_weights && (int)blockIdx.y >= P.blk_base[wi + 1]) ++wi;
+  const bsb_weight& w = P.w[wi];
+  const int j = blockIdx.y - P.blk_base[wi];
+  const int N = w.in_features;
+  const int col0 = chunk * kChunkCols;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+  if (blockIdx.x == 0 && blockIdx.y == 0) {
+    for (int i = tid; i < P.tile_base[P.n_weights]; i += blockDim.x) P.counters[i] = 0;
+    if (tid == 0) *P.status = 0;
+  }
+  float xm = 0.f;
+  for (int n = tid; n < N; n += blockDim.x) xm = fmaxf(xm, fabsf(__half2float(x[n])));
+  for (int o = 16; o > 0; o >>= 1) xm = fmaxf(xm, __shfl_xor_sync(0xFFFFFFFFu, xm, o));
+  if (lane == 0) red[warp] = xm;
+
+  const __half* vt = reinterpret_cast<const __half*>(w.vt) + (int64_t)j * w.vt_block_stride;
+  for (int i = tid; i < 16 * (kChunkCols / 8); i += blockDim.x) {
+    const int r = i / (kChunkCols / 8), c8 = (i % (kChunkCols / 8)) * 8;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (col0 + c8 < N) v = __ldg(reinterpret_cast<const uint4*>(vt + (int64_t)r * N + col0 + c8));
+    *reinterpret_cast<uint4*>(&vt_s[r][c8]) = v;
+  }
+  for (int i = tid; i < kChunkCols; i += blockDim.x) x_s[i] = (col0 + i < N) ? __half2float(x[col0 + i]) : 0.f;
+  __syncthreads();
+  xm = red[0];
+#pragma unroll
+  for (int i = 1; i < 8; ++i) xm = fmaxf(xm, red[i]);
+
+  const int r = tid & 15;         // rank
+  const int kh = (tid >> 4) & 1;  // which 16-byte K half: classes 4kh .. 4kh+3
+  const float vmax = P.vt_absmax[wi][j * 16 + r];
+  const float bound = vmax * xm;
+  const float scale = (bound > 0.f) ? (kTargetMax * kMinD) / (2.f * bound) : 1.f;
+  const float inv_scale = 1.f / scale;
+  if (chunk == 0 && tid < 16) P.inv_scale[(int64_t)blockIdx.y * 16 + r] = inv_scale;
+
+  uint8_t* zout = P.zops + ((int64_t)blockIdx.y * P.n_chunks + chunk) * kChunkBytes;
+  float c_sum = 0.f, z_sum = 0.f;
+#pragma unroll
+  for (int it = 0; it < 2; ++it) {
+    const int word = (tid >> 5) + 8 * it;
+    uint32_t hi[4], lo[4];
+#pragma unroll
+    for (int il = 0; il < 4; ++il) {
+      const int cls = 4 * kh + il;
+      const float mul = 2.f * scale / kD[cls];
+      const float v0 = kV0[cls];
+      hi[il] = 0;
+      lo[il] = 0;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int col = 32 * word + 8 * c + 7 - cls;
+        const float z = __half2float(vt_s[r][col]) * x_s[col];
+        const float zp = z * mul;
+        const uint8_t qh = (uint8_t)__nv_cvt_float_to_fp8(zp, __NV_SATFINITE, __NV_E4M3);
+        const float fh = e4m3_to_float(qh);
+        const uint8_t ql = (uint8_t)__nv_cvt_float_to_fp8(zp - fh, __NV_SATFINITE, __NV_E4M3);
+        const float fl = e4m3_to_float(ql);
+        c_sum = fmaf(v0, fh + fl, c_sum);
+        z_sum += z;
+        hi[il] |= (uint32_t)qh << (8 * c);
+        lo[il] |= (uint32_t)ql << (8 * c);
+      }
+    }
+    uint8_t* tile = zout + word * 1024;
+    // n = r (hi) and n = 16 + r (lo); 16 consecutive k bytes starting at 16*kh
+    const int off_hi = (r % 8) * 16 + (r / 8) * 256 + kh * 128;
+    const int off_lo = (r % 8) * 16 + ((16 + r) / 8) * 256 + kh * 128;
+    *reinterpret_cast<uint4*>(tile + off_hi) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+    *reinterpret_cast<uint4*>(tile + off_lo) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+  }
+  // constant of this (block, chunk, rank): C_r / s_r + sum Z over the chunk's columns
+  kred[tid >> 4][r] = c_sum * inv_scale + z_sum;
+  __syncthreads();
+  if (tid < 16) {
+    float v = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v += kred[i][tid];
+    P.kconst[((int64_t)blockIdx.y * P.n_chunks + chunk) * 16 + tid] = v;
+  }
+}
+
+// ------------------------------------------------------------------ main kernel
+struct __align__(16) SmemLayout {
+  uint8_t zs[kNZ][kChunkBytes];         // Z' operand slabs (bulk-copied)
+  uint4 fifo[kNP][4][kTileRows];        // per-thread sign FIFO: [slot][16-byte piece][thread]
+  uint64_t afull[kNA], aempty[kNA], zfull[kNZ], zempty[kNZ], dfull;
+  float ksum[16], inv[16];
+  uint32_t tmem_base;
+  int last, abort_flag;
+};
+
+__global__ void __launch_bounds__(kThreads) gemv_tc5_kernel(TcParams P) {
+  extern __shared__ uint8_t smem_raw[];
+  SmemLayout& S = *reinterpret_cast<SmemLayout*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~(uintptr_t)127);
+
+  int wi = 0;
+  while (wi + 1 < P.n_weights && (int)blockIdx.x >= P.item_base[wi + 1]) ++wi;
+  const bsb_weight& w = P.w[wi];
+  const int nsplit = P.splits[wi];
+  int item = blockIdx.x - P.item_base[wi];
+  const int split = item % nsplit;
+  item /= nsplit;
+  const int j = item % w.blocks;
+  const int rt = item / w.blocks;
+  const int N = w.in_features, M = w.out_features;
+  const int c_lo = split * P.chunks_per_item[wi];
+  const int c_hi = min(P.n_chunks, c_lo + P.chunks_per_item[wi]);
+  const int nch = c_hi - c_lo;
+  const int jb = P.blk_base[wi] + j;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  // ---- set-up ---------------------------------------------------------------------
+  if (warp == 5) {
+    tmem_alloc(&S.tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  if (tid == 0) {
+    for (int i = 0; i < kNA; ++i) { mbar_init(&S.afull[i], kTileRows); mbar_init(&S.aempty[i], 1); }
+    for (int i = 0; i < kNZ; ++i) { mbar_init(&S.zfull[i], 1); mbar_init(&S.zempty[i], 1); }
+    mbar_init(&S.dfull, 1);
+    S.abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (tid < 16) {
+    float kk = 0.f;
+    for (int c = c_lo; c < c_hi; ++c) kk += P.kconst[((int64_t)jb * P.n_chunks + c) * 16 + tid];
+    S.ksum[tid] = kk;
+    S.inv[tid] = P.inv_scale[(int64_t)jb * 16 + tid];
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tbase = S.tmem_base;
+  const uint32_t colD = 0, colA = 32;
+
+  if (warp == 5) {
+    // ---- Z' loader -------------------------------------------------------------------
+    if (lane == 0) {
+      const uint8_t* zsrc = P.zops + ((int64_t)jb * P.n_chunks + c_lo) * kChunkBytes;
+      for (int ci = 0; ci < nch; ++ci) {
+        const int slot = ci % kNZ, n = ci / kNZ;
+        if (n >= 1 && !mbar_wait(&S.zempty[slot], (n - 1) & 1)) { atomicExch(P.status, 1); S.abort_flag = 1; break; }
+        mbar_expect_tx(&S.zfull[slot], kChunkBytes);
+        bulk_g2s(S.zs[slot], zsrc + (int64_t)ci * kChunkBytes, kChunkBytes, &S.zfull[slot]);
+      }
+    }
+  } else if (warp == 4) {
+    // ---- MMA issuer ------------------------------------------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_f8(128, 32);
+      int it = 0;
+      bool ok = true;
+      for (int ci = 0; ci < nch && ok; ++ci) {
+        const int slot = ci % kNZ, n = ci / kNZ;
+        if (!mbar_wait(&S.zfull[slot], n & 1)) { atomicExch(P.status, 2); S.abort_flag = 1; ok = false; break; }
+        const uint32_t zaddr = smem_u32(S.zs[slot]);
+#pragma unroll 1
+        for (int q = 0; q < 4; ++q, ++it) {
+          const int a = it % kNA, na = it / kNA;
+          if (!mbar_wait(&S.afull[a], na & 1)) { atomicExch(P.status, 3); S.abort_flag = 1; ok = false; break; }
+          tc_fence_after();
+#pragma unroll
+          for (int ww = 0; ww < 4; ++ww) {
+            const uint64_t bdesc = make_smem_desc(zaddr + (uint32_t)(q * 4 + ww) * 1024u, 128, 256);
+            mma_ts_f8(tbase + colD, tbase + colA + a * 32 + ww * 8, bdesc, idesc, (it > 0 || ww > 0) ? 1u : 0u);
+          }
+          mma_commit(&S.aempty[a]);
+        }
+        if (ok) mma_commit(&S.zempty[slot]);
+      }
+      if (ok) mma_commit(&S.dfull);
+    }
+  } else {
+    // ---- producers: one sign row per thread ---------------------------------------------
+    const int row = min(rt * kTileRows + tid, M - 1);
+    const uint8_t* rowp = w.qweight + (int64_t)j * w.q_block_stride + (int64_t)row * (N / 8);
+    const uint32_t lane_base = tbase + ((uint32_t)(warp * 32) << 16);
+    auto issue = [&](int ci) {
+      const int slot = ci % kNP;
+#pragma unroll
+      for (int p = 0; p < 4; ++p) {
+        const int byte = (c_lo + ci) * (kChunkCols / 8) + p * 16;
+        if (byte * 8 < N) cp_async16(&S.fifo[slot][p][tid], rowp + byte);
+        else S.fifo[slot][p][tid] = make_uint4(0, 0, 0, 0);
+      }
+    };
+#pragma unroll
+    for (int ci = 0; ci < kNP - 1; ++ci) {
+      if (ci < nch) issue(ci);
+      asm volatile("cp.async.commit_group;\n" ::: "memory");
+    }
+    int it = 0;
+    bool ok = true;
+#pragma unroll 1
+    for (int ci = 0; ci < nch && ok; ++ci) {
+      if (ci + kNP - 1 < nch) issue(ci + kNP - 1);
+      asm volatile("cp.async.commit_group;\n" ::: "memory");
+      asm volatile("cp.async.wait_group %0;\n" ::"n"(kNP - 1) : "memory");
+      const int slot = ci % kNP;
+#pragma unroll 1
+      for (int p = 0; p < 4; ++p, ++it) {
+        const uint4 v = S.fifo[slot][p][tid];
+        const int a = it % kNA, na = it / kNA;
+        if (na >= 1) {
+          // warp-uniform decision: the tensor-memory store below is a warp-wide instruction
+          const bool got = __all_sync(0xFFFFFFFFu, mbar_wait(&S.aempty[a], (na - 1) & 1) ? 1 : 0);
+          if (!got) { atomicExch(P.status, 4); S.abort_flag = 1; ok = false; break; }
+          tc_fence_after();
+        }
+        uint32_t r[32];
+        expand_word(v.x, r);
+        expand_word(v.y, r + 8);
+        expand_word(v.z, r + 16);
+        expand_word(v.w, r + 24);
+        tmem_st32(lane_base + colA + a * 32, r);
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(&S.afull[a]);
+      }
+    }
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+
+    // ---- epilogue: y_part[m] = sum_r U[m,r] ((D_hi + D_lo)[m,r] / s_r - K_r) -------------
+    // every lane of the warp takes the same branch: the tensor-memory load is warp-wide
+    const int mine = ok ? (mbar_wait(&S.dfull, 0) ? 1 : 0) : 0;
+    const bool done = __all_sync(0xFFFFFFFFu, mine);
+    if (!done && lane == 0) atomicExch(P.status, 5);
+    float ypart = 0.f;
+    if (done) {
+      tc_fence_after();
+      uint32_t d[32];
+      tmem_ld32(lane_base + colD, d);
+      tmem_wait_ld();
+      const __half* u = reinterpret_cast<const __half*>(w.u) + (int64_t)j * w.u_block_stride + (int64_t)row * 16;
+      const uint4 u0 = __ldg(reinterpret_cast<const uint4*>(u));
+      const uint4 u1 = __ldg(reinterpret_cast<const uint4*>(u) + 1);
+      const uint32_t uw[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+#pragma unroll
+      for (int rr = 0; rr < 8; ++rr) {
+        const __half2 h2 = *reinterpret_cast<const __half2*>(&uw[rr]);
+        const float t0 = __uint_as_float(d[2 * rr]) + __uint_as_float(d[16 + 2 * rr]);
+        const float t1 = __uint_as_float(d[2 * rr + 1]) + __uint_as_float(d[16 + 2 * rr + 1]);
+        ypart = fmaf(__low2float(h2), t0 * S.inv[2 * rr] - S.ksum[2 * rr], ypart);
+        ypart = fmaf(__high2float(h2), t1 * S.inv[2 * rr + 1] - S.ksum[2 * rr + 1], ypart);
+      }
+    }
+    float* part = P.partials + P.part_base[wi] + ((int64_t)rt * (w.blocks * nsplit) + (j * nsplit + split)) * kTileRows;
+    part[tid] = done ? ypart : __int_as_float(0x7FC00000);  // NaN marks a tile that was given up
+    __threadfence();
+  }
+
+  // ---- tear-down: tensor memory is released only after every role is done ---------------
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0) {
+    const int expected = w.blocks * nsplit;
+    const int old = atomicAdd(&P.counters[P.tile_base[wi] + rt], 1);
+    S.last = (old == expected - 1);
+  }
+  if (warp == 5) {
+    __syncwarp();
+    tmem_dealloc(tbase, kTmemCols);
+  }
+  __syncthreads();
+  if (!S.last || tid >= kTileRows) return;
+  // the last CTA of this row tile adds all partial sums in a fixed order
+  __threadfence();
+  const int m = rt * kTileRows + tid;
+  if (m >= M) return;
+  const int n_part = w.blocks * nsplit;
+  const float* all = P.partials + P.part_base[wi] + (int64_t)rt * n_part * kTileRows;
+  float sum = 0.f;
+  for (int i = 0; i < n_part; ++i) sum += __ldcg(all + (int64_t)i * kTileRows + tid);
+  if (w.bias) sum += __half2float(reinterpret_cast<const __half*>(w.bias)[m]);
+  P.y[wi][m] = __float2half_rn(sum);
+}
+
+struct TcPlan {
+  TcParams P;
+  int64_t bytes;
+  int total_blocks, total_items;
+  int64_t absmax_off[kMaxGroup];
+  int64_t status_off;
+};
+
+void make_tc_plan(const bsb_weight* ws, int n, TcPlan& pl) {
+  TcParams& P = pl.P;
+  memset(&P, 0, sizeof(P));
+  P.n_weights = n;
+  const int N = ws[0].in_features;
+  P.n_chunks = (int)ceil_div64(N, kChunkCols);
+  const int target = sm_count() * 6;   // items wanted: a few per resident CTA slot
+  int total_tile_blocks = 0;
+  for (int i = 0; i < n; ++i) total_tile_blocks += (int)ceil_div64(ws[i].out_features, kTileRows) * ws[i].blocks;
+  int items = 0, tiles = 0, blks = 0;
+  int64_t part_floats = 0;
+  for (int i = 0; i < n; ++i) {
+    P.w[i] = ws[i];
+    const int n_rt = (int)ceil_div64(ws[i].out_features, kTileRows);
+    int S = (int)ceil_div64(target, total_tile_blocks > 0 ? total_tile_blocks : 1);
+    const int max_split = (P.n_chunks + 1) / 2;   // at least two chunks per item when possible
+    if (S > max_split) S = max_split;
+    if (S < 1) S = 1;
+    const int cpi = (int)ceil_div64(P.n_chunks, S);
+    S = (int)ceil_div64(P.n_chunks, cpi);
+    P.splits[i] = S;
+    P.chunks_per_item[i] = cpi;
+    P.item_base[i] = items;
+    P.tile_base[i] = tiles;
+    P.blk_base[i] = blks;
+    P.part_base[i] = part_floats;
+    items += n_rt * ws[i].blocks * S;
+    tiles += n_rt;
+    blks += ws[i].blocks;
+    part_floats += (int64_t)n_rt * ws[i].blocks * S * kTileRows;
+  }
+  P.item_base[n] = items;
+  P.tile_base[n] = tiles;
+  P.blk_base[n] = blks;
+  pl.total_blocks = blks;
+  pl.total_items = items;
+  int64_t off = 0;
+  const int64_t z_off = off;
+  off = align_up64(off + (int64_t)blks * P.n_chunks * kChunkBytes, 256);
+  const int64_t k_off = off;
+  off = align_up64(off + (int64_t)blks * P.n_chunks * 16 * 4, 256);
+  const int64_t s_off = off;
+  off = align_up64(off + (int64_t)blks * 16 * 4, 256);
+  const int64_t c_off = off;
+  off = align_up64(off + (int64_t)tiles * 4, 256);
+  pl.status_off = off;
+  off += 256;
+  const int64_t p_off = off;
+  off = align_up64(off + part_floats * 4, 256);
+  for (int i = 0; i < n; ++i) {
+    pl.absmax_off[i] = off;
+    off = align_up64(off + (int64_t)ws[i].blocks * 16 * 4, 256);
+  }
+  pl.bytes = off;
+  P.zops = (uint8_t*)z_off;
+  P.kconst = (float*)k_off;
+  P.inv_scale = (float*)s_off;
+  P.counters = (int*)c_off;
+  P.partials = (float*)p_off;
+}
+
+}  // namespace
+
+bool gemv_tc5_supported(const bsb_weight& w) {
+  return w.k == 16 && w.blocks >= 1 && w.in_features % 128 == 0 && w.out_features >= 1 &&
+         ((uintptr_t)w.qweight % 16 == 0) && (w.q_block_stride % 16 == 0) &&
+         ((uintptr_t)w.vt % 16 == 0) && (w.vt_block_stride % 8 == 0) &&
+         ((uintptr_t)w.u % 16 == 0) && (w.u_block_stride % 8 == 0);
+}
+
+int64_t gemv_tc5_workspace_bytes(const bsb_weight* ws, int n_weights) {
+  if (n_weights < 1 || n_weights > kMaxGroup) return -1;
+  TcPlan pl;
+  make_tc_plan(ws, n_weights, pl);
+  return pl.bytes;
+}
+
+int64_t gemv_tc5_status_offset(const bsb_weight* ws, int n_weights) {
+  if (n_weights < 1 || n_weights > kMaxGroup) return -1;
+  TcPlan pl;
+  make_tc_plan(ws, n_weights, pl);
+  return pl.status_off;
+}
+
+int launch_gemv_tc5(const bsb_weight* ws, int n_weights, const __half* x, __half* const* ys, void* workspace,
+                    int64_t workspace_bytes, cudaStream_t s) {
+  BSB_CHECK_ARG(n_weights >= 1 && n_weights <= kMaxGroup, "gemv: 1..%d weights per group", kMaxGroup);
+  for (int i = 0; i < n_weights; ++i) {
+    BSB_CHECK_ARG(gemv_tc5_supported(ws[i]), "gemv: weight %d has an unsupported shape/alignment", i);
+    BSB_CHECK_ARG(ws[i].in_features == ws[0].in_features, "gemv: grouped weights must share in_features");
+  }
+  TcPlan pl;
+  make_tc_plan(ws, n_weights, pl);
+  if (workspace == nullptr || workspace_bytes < pl.bytes) {
+    set_error("gemv: workspace of %lld bytes needed, %lld given", (long long)pl.bytes, (long long)workspace_bytes);
+    return BSB_EWORKSPACE;
+  }
+  BSB_CHECK_ARG((uintptr_t)workspace % 256 == 0, "gemv: workspace must be 256-byte aligned");
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  BSB_CUDA(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    BSB_CUDA(cudaFuncSetAttribute(gemv_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SmemLayout) + 128));
+    attr_set[dev] = true;
+  }
+  TcParams& P = pl.P;
+  uint8_t* base = (uint8_t*)workspace;
+  P.zops = base + (int64_t)(uintptr_t)P.zops;
+  P.kconst = (float*)(base + (int64_t)(uintptr_t)P.kconst);
+  P.inv_scale = (float*)(base + (int64_t)(uintptr_t)P.inv_scale);
+  P.counters = (int*)(base + (int64_t)(uintptr_t)P.counters);
+  P.partials = (float*)(base + (int64_t)(uintptr_t)P.partials);
+  P.status = (int*)(base + pl.status_off);
+  for (int i = 0; i < n_weights; ++i) {
+    P.y[i] = ys[i];
+    if (ws[i].vt_absmax) {
+      P.vt_absmax[i] = ws[i].vt_absmax;
+    } else {
+      float* am = (float*)(base + pl.absmax_off[i]);
+      if (int rc = launch_vt_absmax(ws[i], am, s)) return rc;
+      P.vt_absmax[i] = am;
+    }
+  }
+  zprep_tc5_kernel<<<dim3(P.n_chunks, pl.total_blocks), 256, 0, s>>>(P, x);
+  if (int rc = check_launch("zprep_tc5_kernel")) return rc;
+  gemv_tc5_kernel<<<pl.total_items, kThreads, sizeof(SmemLayout) + 128, s>>>(P);
+  return check_launch("gemv_tc5_kernel");
+}
+
+}  // namespace bsb

@@ -9,8 +9,9 @@ reference staged its Triton kernels -- and extra levels pin one kernel:
 
     0-5, 6  automatic choice (decode kernel for <= 4 rows, rebuild+GEMM above)
     7       shape-agnostic CUDA-core kernel
-    8       decode kernel (packed signs -> fp8 tensor-core MMAs), any row count
+    8       decode kernel, warp-level MMA generation, any row count
     9       rebuild fp16 weight + dense MMA
+    10      decode kernel, tcgen05 generation (sign operand in tensor memory)
 
 There is no CPU path: inputs must be CUDA fp16 tensors.  `no_avd=True` (the
 reference's ablation without sign matrices) is not supported.
@@ -27,7 +28,8 @@ from .pack import pack_sign, unpack_sign
 
 _LEVEL_TO_ALGO = {0: _lib.ALGO_AUTO, 1: _lib.ALGO_AUTO, 2: _lib.ALGO_AUTO, 3: _lib.ALGO_AUTO,
                   4: _lib.ALGO_AUTO, 5: _lib.ALGO_AUTO, 6: _lib.ALGO_AUTO,
-                  7: _lib.ALGO_GENERAL, 8: _lib.ALGO_GEMV_MMA, 9: _lib.ALGO_REBUILD_GEMM}
+                  7: _lib.ALGO_GENERAL, 8: _lib.ALGO_GEMV_MMA, 9: _lib.ALGO_REBUILD_GEMM,
+                  10: _lib.ALGO_GEMV_TC5}
 
 # scratch memory per (device index, stream handle); grown on demand, never shrunk
 _workspaces: dict = {}

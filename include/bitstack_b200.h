@@ -120,6 +120,12 @@ int bsb_linear_forward_grouped(const bsb_weight* ws, int32_t n_weights, const ui
 /* Scratch bytes bsb_linear_forward_grouped needs. */
 int64_t bsb_linear_grouped_workspace_bytes(const bsb_weight* ws, int32_t n_weights, int64_t rows, int algo);
 
+/* Debug aid (no reference counterpart): after the work queued by a tcgen05 decode
+ * call on `workspace` has finished, copies that call's device status word to
+ * *status_out (host): 0 = every hand-off completed, otherwise the code of the
+ * time-bounded wait that gave up.  Synchronises the device. */
+int bsb_debug_gemv_status(const bsb_weight* ws, int32_t n_weights, const void* workspace, int32_t* status_out);
+
 /* Same forward with HOST x and y buffers: copies x to the device, runs the
  * forward, copies y back and waits for it -- the call a host-only user makes.
  * dev_x / dev_y are caller-provided device staging buffers of rows*in and

@@ -116,14 +116,14 @@ def test_reconstruct_weight_matches_oracle(dev, golden_dir, fname):
 
 
 # --------------------------------------------------------------------------- forward vs golden
-@pytest.mark.parametrize("level", [6, 7, 8, 9])
+@pytest.mark.parametrize("level", [6, 7, 8, 9, 10])
 @pytest.mark.parametrize("fname", ["decomp_small.npz", "decomp_1024.npz"])
 def test_forward_matches_reference_fixtures(dev, golden_dir, fname, level):
     z = np.load(os.path.join(golden_dir, fname))
     q, u, vt = z["qweight"], z["u"], z["vt"]
     bias = z["bias"] if "bias" in z.files else None
     n = vt.shape[2]
-    if level in (8, 9) and n % 128 != 0:
+    if level in (8, 9, 10) and n % 128 != 0:
         pytest.skip("tensor-core kernels need in_features % 128 == 0; ragged shapes use the general kernel")
     mod = make_module(q, u, vt, bias, dev, level=level)
     for rows in z["rows"]:
@@ -139,7 +139,7 @@ def test_forward_matches_reference_fixtures(dev, golden_dir, fname, level):
             assert e_max <= EXACT_TOL and e_l2 <= EXACT_TOL, ("f64", fname, level, rows, b, e_max, e_l2)
 
 
-@pytest.mark.parametrize("level", [6, 7, 8, 9])
+@pytest.mark.parametrize("level", [6, 7, 8, 9, 10])
 def test_forward_matches_reference_synthetic(dev, golden_dir, level):
     z = np.load(os.path.join(golden_dir, "synth_l0.npz"))
     cache = {}
@@ -244,7 +244,7 @@ def test_set_bit_needs_no_repack_and_is_deterministic(dev):
     q, u, vt = orc.synthetic_layer(512, 1024, 6, seed=31)
     x_np = orc.synthetic_input(1, 1024, seed=32)
     x = torch.from_numpy(x_np).to(dev)
-    mod = make_module(q, u, vt, None, dev, level=8)
+    mod = make_module(q, u, vt, None, dev, level=10)
     outs = {}
     for b in (6, 1, 3, 6):
         mod.set_bit(b)
@@ -329,7 +329,13 @@ def test_grouped_projections_match_individual(dev):
     x = torch.from_numpy(orc.synthetic_input(1, n, 99)).to(dev)
     ys = forward_grouped(mods, x)
     for mod, y in zip(mods, ys):
-        assert torch.equal(y, mod(x))
+        # grouped and single launches may split the columns differently, so the fp32
+        # partial sums are added in a different order: equal up to fp16 rounding
+        ref = mod(x).float()
+        assert (y.float() - ref).abs().max() <= 2e-3 * ref.abs().max()
+    again = forward_grouped(mods, x)
+    for a, b in zip(ys, again):
+        assert torch.equal(a, b), "the same grouped call must be bit-identical"
 
 
 def test_host_buffer_entry_point(dev):
