@@ -1,0 +1,347 @@
+"""Benchmark: greedy decode tokens/s of a Llama-architecture BitStack model.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload llama3-8b|llama3-70b] [--layers L]
+
+One "step" is one decode token: every BitStack projection of every layer is applied
+once to a single-row input (batch 1 for the 8B shape), plus the attention / norm /
+head glue.  Default workload (N=1): random-init Llama-3.1-8B architecture, seeded
+per-weight block counts in [2, 16] trimmed to 5.5 GB of packed blocks, 512-token
+prompt, then K greedy steps.
+
+The printed JSON line carries: `value` (device-timed, CUDA-graph replay, inputs
+resident), `e2e` (host-driven `generate()` with a host<->device token round trip per
+step), `roofline` (the tcgen05 decode kernel: algorithmic bytes / event-timed launch
+duration vs the measured HBM copy bandwidth), `cpu_baseline` (the CPU oracle's
+restatement of the reference's unfused forward on a bounded sample of the same
+layers), `clocks`, `gpu_launches`.
+
+`--impl reference` times only the CPU restatement of the reference path (the
+reference itself is Python that cannot travel to the GPU box) on bounded samples.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+TARGET_PACKED_BYTES = int(5.5e9)
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="llama3-8b", choices=["llama3-8b", "llama3-70b"])
+    ap.add_argument("--layers", type=int, default=0, help="debug: override the layer count (invalidates the number)")
+    ap.add_argument("--prompt-len", type=int, default=0)
+    ap.add_argument("--cpu-seconds", type=float, default=15.0, help="CPU time budget of the cpu_baseline leg")
+    ap.add_argument("--no-graph", action="store_true")
+    return ap.parse_args()
+
+
+def workload_spec(args):
+    from bitstack_b200 import decode
+    if args.workload == "llama3-8b":
+        shape = decode.LLAMA3_8B
+        counts_args = dict(seed=1234, lo=2, hi=16, target_bytes=TARGET_PACKED_BYTES)
+        batch, prompt = 1, 512
+    else:
+        shape = decode.LLAMA3_70B
+        counts_args = dict(seed=4321, lo=4, hi=12, target_bytes=None)
+        batch, prompt = 16, 256
+    if args.layers:
+        shape = decode.LlamaShape(shape.name + f"-{args.layers}L", args.layers, shape.hidden, shape.n_heads,
+                                  shape.n_kv_heads, shape.intermediate, shape.vocab, shape.rope_theta, shape.rms_eps)
+        if counts_args["target_bytes"]:
+            counts_args["target_bytes"] = counts_args["target_bytes"] * args.layers // 32
+    if args.prompt_len:
+        prompt = args.prompt_len
+    counts = decode.seeded_block_counts(shape, **counts_args)
+    return shape, counts, batch, prompt
+
+
+# ----------------------------------------------------------------------------- clocks
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index=0):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 8:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[4:8]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ----------------------------------------------------------------------------- CPU restatement
+def cpu_sample(shape, counts, budget_s, threads=None):
+    """Time the oracle's restatement of the reference's unfused forward on a bounded
+    sample of this workload's projections; returns extrapolated tokens/s."""
+    from oracle import bitstack_oracle as orc
+    from bitstack_b200 import decode
+    if threads:
+        torch.set_num_threads(threads)
+    shapes = shape.proj_shapes()
+    total_bytes = sum(c * decode.block_bytes(*shapes[n.split(".", 2)[2]]) for n, c in counts.items())
+    # smallest projections first so that a tiny budget still covers a few of them
+    order = sorted(counts, key=lambda n: counts[n] * decode.block_bytes(*shapes[n.split(".", 2)[2]]))
+    picked, t_used, bytes_done, rate = [], 0.0, 0, 0.06e9  # first guess: 0.06 GB/s
+    rng = np.random.default_rng(0)
+    i = 0
+    t_wall = time.perf_counter()
+    while i < len(order):
+        # stride through the sorted list so that small and large projections are both sampled
+        name = order[(i * 37) % len(order)]
+        i += 1
+        out_f, in_f = shapes[name.split(".", 2)[2]]
+        nb = counts[name]
+        b = nb * decode.block_bytes(out_f, in_f)
+        if picked and t_used + b / rate > budget_s:
+            continue
+        if time.perf_counter() - t_wall > 3 * budget_s + 20:
+            break
+        q = torch.from_numpy(rng.integers(0, 256, size=(nb, out_f * in_f // 8), dtype=np.uint8))
+        u = (torch.randn(nb, out_f, 16) * 0.05).abs().half()
+        vt = (torch.randn(nb, 16, in_f) * 0.05).abs().half()
+        x = torch.randn(1, in_f).half()
+        t0 = time.perf_counter()
+        orc.forward_l0(x, q, u, vt, nb)
+        dt = time.perf_counter() - t0
+        picked.append(name)
+        t_used += dt
+        bytes_done += b
+        rate = bytes_done / t_used
+        if t_used >= budget_s:
+            break
+    sec_per_token = t_used * total_bytes / max(bytes_done, 1)
+    return {"value": 1.0 / sec_per_token, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{len(picked)} of {len(counts)} projections ({bytes_done/1e6:.0f} MB of {total_bytes/1e6:.0f} MB packed "
+                      f"blocks per token) in {t_used:.1f} s, extrapolated by packed bytes; attention/head glue not included",
+            "gb_per_s": bytes_done / t_used / 1e9, "host_cpus": os.cpu_count()}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    shape, counts, batch, prompt = workload_spec(args)
+    per_step = max(0.5, min(20.0, 150.0 / max(args.steps + args.warmup, 1)))
+    vals = []
+    info = None
+    for s in range(args.warmup + args.steps):
+        info = cpu_sample(shape, counts, per_step)
+        if s >= args.warmup:
+            vals.append(info["value"])
+    v = float(np.mean(vals)) * batch
+    line = {"impl": "reference", "metric": "decode_tokens_per_s", "value": v, "unit": "tokens/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * batch / v, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "fp16 (reference level-0 forward on host cores)",
+            "data": "synthetic", "config": config_dict(args, shape, counts, batch, prompt),
+            "cpu_baseline": dict(info, value=v),
+            "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def config_dict(args, shape, counts, batch, prompt):
+    from bitstack_b200 import decode
+    return {"workload": f"{shape.name}-architecture BitStack greedy decode, batch {batch}: {prompt}-token random prompt "
+                        f"then {args.steps} steps; {len(counts)} BitStack projections, k=16, seeded block counts "
+                        f"{min(counts.values())}-{max(counts.values())}",
+            "packed_block_bytes": decode.packed_bytes(shape, counts), "batch": batch, "prompt_len": prompt,
+            "l2": "per-step working set (packed blocks + fp16 head) is far larger than the 126 MB L2; no flush needed",
+            "parallelism": f"tp{args.gpus}" if args.gpus > 1 else "single GPU"}
+
+
+# ----------------------------------------------------------------------------- ours
+def run_ours(args):
+    from bitstack_b200 import _lib, decode
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the BitStack kernels have no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    group = None
+    if world > 1:
+        torch.distributed.init_process_group("nccl", device_id=dev)
+        group = torch.distributed.group.WORLD
+    lib = _lib.load()
+    shape, counts, batch, prompt = workload_spec(args)
+    max_len = prompt + args.steps + args.warmup + 16
+    max_len = (max_len + 127) // 128 * 128
+    model = decode.BitStackLlamaDecoder(shape, counts, dev, seed=7, max_len=max_len, batch=batch,
+                                        rank=rank, world_size=world, group=group)
+    gen = torch.Generator().manual_seed(11)
+    prompt_host = torch.randint(0, shape.vocab, (batch, prompt), generator=gen).pin_memory()
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-timed value ------------------------------------------------------------
+    model.prefill(prompt_host.to(dev))
+    n0 = lib.bsb_debug_launch_count()
+    model.decode_step()
+    launches_per_step = lib.bsb_debug_launch_count() - n0
+    if not args.no_graph:
+        model.capture()
+    for _ in range(max(args.warmup, 3)):
+        model.step()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        model.step()
+    e1.record()
+    barrier()
+    ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if world > 1:
+        torch.distributed.all_reduce(ms, op=torch.distributed.ReduceOp.MAX)
+    ms = float(ms.item())
+    clocks = sampler.stop() if rank == 0 else None
+    value = args.steps * batch / (ms / 1000.0)
+
+    # ---- end to end through the host-facing API ------------------------------------------
+    pinned = torch.empty(args.steps, batch, dtype=torch.long).pin_memory()
+    model.generate(prompt_host, min(4, args.steps), pinned)     # warm-up of the host loop
+    model.prefill(prompt_host.to(dev))                          # timed region = decode steps, as for `value`
+    barrier()
+    t0 = time.perf_counter()
+    for t in range(args.steps):
+        toks = model.step()
+        pinned[t].copy_(toks, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        model.tokens.copy_(pinned[t], non_blocking=True)        # host feeds the token back, as a sampling loop would
+    torch.cuda.synchronize()
+    e2e_s = torch.tensor([time.perf_counter() - t0], device=dev)
+    if world > 1:
+        torch.distributed.all_reduce(e2e_s, op=torch.distributed.ReduceOp.MAX)
+    e2e = args.steps * batch / float(e2e_s.item())
+
+    # ---- roofline of the dominant kernel (eager step, events around each launch) -----------
+    roof = None
+    if rank == 0:
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except Exception:
+            pass
+        peak, which = (peaks["hbm_gbs"], "measured") if "hbm_gbs" in peaks else (6650.0, "fallback")
+        model._graph, g = None, model._graph
+        torch.cuda.synchronize()
+        lib.bsb_debug_profile_start(4096)
+        model.decode_step()
+        buf = (C.c_float * 4096)()
+        n = C.c_int32(0)
+        lib.bsb_debug_profile_stop(buf, 4096, C.byref(n))
+        model._graph = g
+        durs = np.array(buf[: n.value], dtype=np.float64)
+        shapes = shape.proj_shapes()
+        launch_bytes = []
+        for i in range(shape.n_layers):
+            for grp in (("self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj"), ("self_attn.o_proj",),
+                        ("mlp.gate_proj", "mlp.up_proj"), ("mlp.down_proj",)):
+                b = 0
+                for p in grp:
+                    out_f, in_f = shapes[p]
+                    if p in ("self_attn.o_proj", "mlp.down_proj"):
+                        in_f //= world
+                    else:
+                        out_f //= world
+                    b += counts[f"layer.{i}.{p}"] * decode.block_bytes(out_f, in_f) + 2 * out_f
+                out_f, in_f = shapes[grp[0]]
+                b += 2 * (in_f // world if grp[0] in ("self_attn.o_proj", "mlp.down_proj") else in_f)
+                launch_bytes.append(b * batch if batch > 1 else b)
+        if n.value == len(launch_bytes) and n.value > 0:
+            achieved = sum(launch_bytes) / (durs.sum() / 1000.0) / 1e9
+            roof = {"bound": "hbm", "kernel": "gemv_tc5_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                    "frac": achieved / peak, "peak_source": which + " (of measured copy bandwidth)" if which == "measured" else "fallback",
+                    "traffic": None, "launches": int(n.value), "avg_launch_us": float(durs.mean() * 1000.0),
+                    "algorithmic_bytes_per_launch": float(np.mean(launch_bytes))}
+        else:
+            roof = {"bound": "hbm", "kernel": "gemv_tc5_kernel", "achieved": None, "peak": peak, "unit": "GB/s", "frac": None,
+                    "traffic": None, "note": f"{n.value} profiled launches, {len(launch_bytes)} expected (batch path in use?)"}
+
+    # ---- CPU restatement on a bounded sample ---------------------------------------------
+    cpu = None
+    if rank == 0 and world == 1:
+        cpu = cpu_sample(shape, counts, args.cpu_seconds)
+        cpu["value"] *= batch
+    if rank == 0:
+        line = {"metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+                "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": "e4m3 tensor-core operands, f32 accumulate, fp16 storage/outputs",
+                "data": "synthetic", "config": config_dict(args, shape, counts, batch, prompt),
+                "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": 8 * batch, "d2h_bytes_per_step": 8 * batch},
+                "gpu_launches": int(launches_per_step * args.steps), "roofline": roof, "cpu_baseline": cpu, "clocks": clocks,
+                "graph": not args.no_graph}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        torch.distributed.destroy_process_group()
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -17,6 +17,26 @@ void set_error(const char* fmt, ...) {
   va_end(ap);
 }
 
+static unsigned long long g_launches = 0;
+void count_launch() { __atomic_fetch_add(&g_launches, 1ull, __ATOMIC_RELAXED); }
+
+// profiling hook: a bounded list of event pairs recorded around the tcgen05 decode kernel
+static const int kMaxProfile = 4096;
+static cudaEvent_t g_prof_ev[2 * kMaxProfile];
+static int g_prof_cap = 0, g_prof_n = 0;
+static bool g_prof_on = false;
+void profile_mark(cudaStream_t s, bool after) {
+  if (!g_prof_on) return;
+  if (!after) {
+    if (g_prof_n >= g_prof_cap) return;
+    cudaEventRecord(g_prof_ev[2 * g_prof_n], s);
+  } else {
+    if (g_prof_n >= g_prof_cap) return;
+    cudaEventRecord(g_prof_ev[2 * g_prof_n + 1], s);
+    ++g_prof_n;
+  }
+}
+
 int sm_count() {
   static int cached[64] = {0};
   int dev = 0;
@@ -249,6 +269,31 @@ int bsb_debug_gemv_status(const bsb_weight* ws, int32_t n_weights, const void* w
   const int64_t off = gemv_tc5_status_offset(ws, n_weights);
   BSB_CHECK_ARG(off >= 0, "bad group size");
   BSB_CUDA(cudaMemcpy(status_out, (const uint8_t*)workspace + off, 4, cudaMemcpyDeviceToHost));
+  return BSB_OK;
+}
+
+int64_t bsb_debug_launch_count(void) { return (int64_t)g_launches; }
+
+int bsb_debug_profile_start(int32_t max_launches) {
+  BSB_CHECK_ARG(max_launches >= 1 && max_launches <= kMaxProfile, "1..%d launches can be profiled", kMaxProfile);
+  BSB_CHECK_ARG(!g_prof_on, "profiling already on");
+  for (int i = g_prof_cap * 2; i < max_launches * 2; ++i) BSB_CUDA(cudaEventCreate(&g_prof_ev[i]));
+  if (max_launches > g_prof_cap) g_prof_cap = max_launches;
+  g_prof_n = 0;
+  g_prof_on = true;
+  return BSB_OK;
+}
+
+int bsb_debug_profile_stop(float* ms_out, int32_t capacity, int32_t* n_out) {
+  BSB_CHECK_ARG(g_prof_on, "profiling is not on");
+  g_prof_on = false;
+  BSB_CHECK_ARG(ms_out && n_out, "NULL output");
+  const int n = g_prof_n < capacity ? g_prof_n : capacity;
+  for (int i = 0; i < n; ++i) {
+    BSB_CUDA(cudaEventSynchronize(g_prof_ev[2 * i + 1]));
+    BSB_CUDA(cudaEventElapsedTime(&ms_out[i], g_prof_ev[2 * i], g_prof_ev[2 * i + 1]));
+  }
+  *n_out = n;
   return BSB_OK;
 }
 

@@ -30,7 +30,13 @@ void set_error(const char* fmt, ...);
     }                                                                         \
   } while (0)
 
+// number of kernels this library has launched from the calling process
+void count_launch();
+// optional timing of the dominant decode kernel: events around each of its launches
+void profile_mark(cudaStream_t s, bool after);
+
 inline int check_launch(const char* what) {
+  count_launch();
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_error("launch of %s failed: %s", what, cudaGetErrorString(e));

@@ -607,7 +607,9 @@ int launch_gemv_tc5(const bsb_weight* ws, int n_weights, const __half* x, __half
   }
   zprep_tc5_kernel<<<dim3(P.n_chunks, pl.total_blocks), 256, 0, s>>>(P, x);
   if (int rc = check_launch("zprep_tc5_kernel")) return rc;
+  profile_mark(s, false);
   gemv_tc5_kernel<<<pl.total_items, kThreads, sizeof(SmemLayout) + 128, s>>>(P);
+  profile_mark(s, true);
   return check_launch("gemv_tc5_kernel");
 }
 

@@ -1,0 +1,249 @@
+"""Greedy decode harness around the BitStack linear kernels.
+
+The reference has no generation loop (its only model calls are full-sequence
+forwards inside perplexity evaluation, bitstack/utils/model_utils.py:116-133), so
+this is measurement scaffolding, not a mirror of reference code: a Llama-architecture
+decoder (RMSNorm, rotary embedding, grouped-query attention over a static KV
+cache, SwiGLU MLP) whose seven projections per layer are `BitStackLinear` modules
+named like the reference names them (`layer.{i}.self_attn.q_proj`, ...,
+bitstack/utils/decompose.py:14).  The glue ops are plain torch calls; one decode
+step can be captured in a CUDA graph (device-side position and token feedback).
+
+With `world_size > 1` the projections are sharded for tensor parallelism: output
+rows for q/k/v/gate/up, input columns for o/down, one all-reduce after each of the
+two column-sharded projections of a layer.
+"""
+from __future__ import annotations
+
+import dataclasses
+import random
+from typing import Dict, Optional
+
+import torch
+import torch.nn.functional as F
+
+from .linear import BitStackLinear, forward_grouped
+
+PROJ_NAMES = ("self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj", "self_attn.o_proj",
+              "mlp.gate_proj", "mlp.up_proj", "mlp.down_proj")
+
+
+@dataclasses.dataclass
+class LlamaShape:
+    name: str
+    n_layers: int
+    hidden: int
+    n_heads: int
+    n_kv_heads: int
+    intermediate: int
+    vocab: int = 128256
+    rope_theta: float = 500000.0
+    rms_eps: float = 1e-5
+
+    @property
+    def head_dim(self):
+        return self.hidden // self.n_heads
+
+    def proj_shapes(self) -> Dict[str, tuple]:
+        kv = self.n_kv_heads * self.head_dim
+        return {"self_attn.q_proj": (self.hidden, self.hidden), "self_attn.k_proj": (kv, self.hidden),
+                "self_attn.v_proj": (kv, self.hidden), "self_attn.o_proj": (self.hidden, self.hidden),
+                "mlp.gate_proj": (self.intermediate, self.hidden), "mlp.up_proj": (self.intermediate, self.hidden),
+                "mlp.down_proj": (self.hidden, self.intermediate)}
+
+
+LLAMA3_8B = LlamaShape("llama3-8b", 32, 4096, 32, 8, 14336)
+LLAMA3_70B = LlamaShape("llama3-70b", 80, 8192, 64, 8, 28672)
+
+
+def block_bytes(out_features, in_features, k=16):
+    return (out_features * in_features) // 8 + 2 * k * (out_features + in_features)
+
+
+def seeded_block_counts(shape: LlamaShape, seed: int, lo: int, hi: int, target_bytes: Optional[int] = None):
+    """A compression config `{layer.i.proj: blocks}`: uniform draws in [lo, hi] from a
+    seeded generator; when `target_bytes` is given, seeded single-block removals
+    (never below `lo`) bring the packed total down to the target."""
+    rng = random.Random(seed)
+    shapes = shape.proj_shapes()
+    names = [f"layer.{i}.{p}" for i in range(shape.n_layers) for p in PROJ_NAMES]
+    counts = {n: rng.randint(lo, hi) for n in names}
+    per_block = {n: block_bytes(*shapes[n.split(".", 2)[2]]) for n in names}
+    if target_bytes is not None:
+        total = sum(counts[n] * per_block[n] for n in names)
+        while total > target_bytes:
+            n = names[rng.randrange(len(names))]
+            if counts[n] > lo:
+                counts[n] -= 1
+                total -= per_block[n]
+            elif all(counts[m] <= lo for m in names):
+                break
+    return counts
+
+
+def packed_bytes(shape: LlamaShape, counts: Dict[str, int]) -> int:
+    shapes = shape.proj_shapes()
+    return sum(c * block_bytes(*shapes[n.split(".", 2)[2]]) for n, c in counts.items())
+
+
+def _random_bitstack(out_f, in_f, blocks, device, gen, name, fused_level):
+    """Random-init module with the storage format of a loaded, stacked checkpoint:
+    Bernoulli(0.5) packed signs, |N(0, 0.05)| fp16 factors."""
+    m = BitStackLinear(w_bit=0, in_features=in_f, out_features=out_f, k=16, bias=False, no_avd=False,
+                       dev=device, fused_level=fused_level)
+    m.name = name
+    m.qweight = torch.randint(0, 256, (blocks, out_f * in_f // 8), dtype=torch.uint8, device=device, generator=gen)
+    m.u = (torch.randn(blocks, out_f, 16, device=device, generator=gen) * 0.05).abs().half()
+    m.vt = (torch.randn(blocks, 16, in_f, device=device, generator=gen) * 0.05).abs().half()
+    m.w_bit = blocks
+    m._stacked_blocks = blocks
+    return m
+
+
+class BitStackLlamaDecoder:
+    """Random-init Llama-architecture decoder whose linears are BitStack modules."""
+
+    def __init__(self, shape: LlamaShape, block_counts: Dict[str, int], device, seed=0, max_len=1024,
+                 batch=1, fused_level=6, rank=0, world_size=1, group=None):
+        self.shape, self.device, self.max_len, self.batch = shape, torch.device(device), max_len, batch
+        self.rank, self.world, self.group = rank, world_size, group
+        s = shape
+        assert s.n_kv_heads % world_size == 0 and s.intermediate % (128 * world_size) == 0
+        gen = torch.Generator(device=self.device).manual_seed(seed)  # same seed on every rank: replicated tensors agree
+        self.embed = (torch.randn(s.vocab, s.hidden, device=self.device, generator=gen) * 0.02).half()
+        self.lm_head = (torch.randn(s.vocab, s.hidden, device=self.device, generator=gen) * 0.02).half()
+        self.final_norm = torch.ones(s.hidden, dtype=torch.float16, device=self.device)
+        self.layers = []
+        shapes = s.proj_shapes()
+        W = world_size
+        for i in range(s.n_layers):
+            lay = {"in_norm": torch.ones(s.hidden, dtype=torch.float16, device=self.device),
+                   "post_norm": torch.ones(s.hidden, dtype=torch.float16, device=self.device)}
+            for p in PROJ_NAMES:
+                out_f, in_f = shapes[p]
+                if p in ("self_attn.o_proj", "mlp.down_proj"):
+                    in_f //= W      # input-column shard: partial sums, all-reduced
+                else:
+                    out_f //= W     # output-row shard
+                lgen = torch.Generator(device=self.device).manual_seed(seed * 1000003 + i * 16 + PROJ_NAMES.index(p) + 7919 * rank)
+                lay[p] = _random_bitstack(out_f, in_f, block_counts[f"layer.{i}.{p}"], self.device, lgen,
+                                          f"layer.{i}.{p}", fused_level)
+            self.layers.append(lay)
+        hd = s.head_dim
+        self.kv_local = s.n_kv_heads // W
+        self.q_local = s.n_heads // W
+        self.k_cache = [torch.zeros(batch, self.kv_local, max_len, hd, dtype=torch.float16, device=self.device) for _ in range(s.n_layers)]
+        self.v_cache = [torch.zeros(batch, self.kv_local, max_len, hd, dtype=torch.float16, device=self.device) for _ in range(s.n_layers)]
+        inv_freq = 1.0 / (s.rope_theta ** (torch.arange(0, hd, 2, device=self.device, dtype=torch.float32) / hd))
+        t = torch.arange(max_len, device=self.device, dtype=torch.float32)
+        freqs = torch.outer(t, inv_freq)
+        self.cos = torch.cat([freqs, freqs], dim=-1).cos().half()
+        self.sin = torch.cat([freqs, freqs], dim=-1).sin().half()
+        self.pos = torch.zeros(1, dtype=torch.long, device=self.device)      # next position to write
+        self.tokens = torch.zeros(batch, dtype=torch.long, device=self.device)  # token fed to the next step
+        self.arange = torch.arange(max_len, device=self.device)
+        self._graph = None
+
+    # ------------------------------------------------------------------ pieces
+    def weight_bytes(self):
+        return sum(l[p].qweight.numel() + 2 * l[p].u.numel() + 2 * l[p].vt.numel() for l in self.layers for p in PROJ_NAMES)
+
+    @staticmethod
+    def _rope(x, cos, sin):
+        half = x.shape[-1] // 2
+        rot = torch.cat([-x[..., half:], x[..., :half]], dim=-1)
+        return x * cos + rot * sin
+
+    def _allreduce(self, t):
+        if self.world > 1:
+            torch.distributed.all_reduce(t, group=self.group)
+        return t
+
+    def _layer(self, i, h, positions, pos_index, mask):
+        """h: [B, T, hidden]; positions: [T] long tensor of absolute positions."""
+        s, lay = self.shape, self.layers[i]
+        B, T, _ = h.shape
+        x = F.rms_norm(h, (s.hidden,), lay["in_norm"], s.rms_eps)
+        q, k, v = forward_grouped([lay["self_attn.q_proj"], lay["self_attn.k_proj"], lay["self_attn.v_proj"]], x)
+        hd = s.head_dim
+        q = q.view(B, T, self.q_local, hd).transpose(1, 2)
+        k = k.view(B, T, self.kv_local, hd).transpose(1, 2)
+        v = v.view(B, T, self.kv_local, hd).transpose(1, 2)
+        cos, sin = self.cos.index_select(0, positions), self.sin.index_select(0, positions)
+        q, k = self._rope(q, cos, sin), self._rope(k, cos, sin)
+        self.k_cache[i].index_copy_(2, pos_index, k)
+        self.v_cache[i].index_copy_(2, pos_index, v)
+        att = F.scaled_dot_product_attention(q, self.k_cache[i], self.v_cache[i], attn_mask=mask, enable_gqa=True)
+        att = att.transpose(1, 2).reshape(B, T, self.q_local * hd)
+        h = h + self._allreduce(lay["self_attn.o_proj"](att))
+        x = F.rms_norm(h, (s.hidden,), lay["post_norm"], s.rms_eps)
+        g, u = forward_grouped([lay["mlp.gate_proj"], lay["mlp.up_proj"]], x)
+        h = h + self._allreduce(lay["mlp.down_proj"](F.silu(g) * u))
+        return h
+
+    def _forward(self, token_ids, positions):
+        """token_ids: [B, T]; returns last-position logits [B, vocab] and advances nothing."""
+        h = self.embed.index_select(0, token_ids.reshape(-1)).view(*token_ids.shape, -1)
+        mask = (self.arange.view(1, -1) <= positions.view(-1, 1)).view(1, 1, positions.numel(), self.max_len)
+        for i in range(self.shape.n_layers):
+            h = self._layer(i, h, positions, positions, mask)
+        h = F.rms_norm(h[:, -1], (self.shape.hidden,), self.final_norm, self.shape.rms_eps)
+        return h @ self.lm_head.t()
+
+    # ------------------------------------------------------------------ public API
+    @torch.no_grad()
+    def prefill(self, prompt_ids: torch.Tensor):
+        """prompt_ids: [B, T] on the device.  Fills the KV cache and sets the first decode token."""
+        B, T = prompt_ids.shape
+        positions = torch.arange(T, device=self.device)
+        logits = self._forward(prompt_ids, positions)
+        self.tokens.copy_(logits.argmax(-1))
+        self.pos.fill_(T)
+        return self.tokens.clone()
+
+    @torch.no_grad()
+    def decode_step(self):
+        """One greedy token for every sequence; position and token feedback stay on the device."""
+        logits = self._forward(self.tokens.view(-1, 1), self.pos)
+        self.tokens.copy_(logits.argmax(-1))
+        self.pos.add_(1)
+        return self.tokens
+
+    def capture(self, stream=None):
+        """Capture decode_step in a CUDA graph (call after prefill and a few eager steps)."""
+        stream = stream or torch.cuda.Stream(self.device)
+        pos0, tok0 = self.pos.clone(), self.tokens.clone()
+        stream.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(stream):
+            for _ in range(2):
+                self.decode_step()
+        torch.cuda.current_stream(self.device).wait_stream(stream)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            self.decode_step()
+        self.pos.copy_(pos0)
+        self.tokens.copy_(tok0)
+        self._graph = g
+        return g
+
+    @torch.no_grad()
+    def step(self):
+        if self._graph is not None:
+            self._graph.replay()
+        else:
+            self.decode_step()
+        return self.tokens
+
+    @torch.no_grad()
+    def generate(self, prompt_ids_host: torch.Tensor, steps: int, pinned_out: Optional[torch.Tensor] = None):
+        """Host-facing greedy generation: prompt on the host, every generated token read
+        back to the host before the next step is issued (the call a user makes).
+        Returns a [B, steps] CPU tensor."""
+        prompt = prompt_ids_host.to(self.device, non_blocking=True)
+        self.prefill(prompt)
+        out = pinned_out if pinned_out is not None else torch.empty(steps, self.batch, dtype=torch.long).pin_memory()
+        for t in range(steps):
+            toks = self.step()
+            out[t].copy_(toks, non_blocking=True)
+            torch.cuda.current_stream(self.device).synchronize()
+        return out[:steps].t().contiguous()

@@ -126,6 +126,15 @@ int64_t bsb_linear_grouped_workspace_bytes(const bsb_weight* ws, int32_t n_weigh
  * time-bounded wait that gave up.  Synchronises the device. */
 int bsb_debug_gemv_status(const bsb_weight* ws, int32_t n_weights, const void* workspace, int32_t* status_out);
 
+/* Measurement aids (no reference counterpart).  bsb_debug_launch_count: kernels this
+ * library has launched so far in the process.  bsb_debug_profile_start/stop: while
+ * on, a CUDA event pair is recorded on the launching stream around every launch of
+ * the tcgen05 decode kernel (at most max_launches); stop waits for them and writes
+ * the per-launch durations in milliseconds. */
+int64_t bsb_debug_launch_count(void);
+int bsb_debug_profile_start(int32_t max_launches);
+int bsb_debug_profile_stop(float* ms_out, int32_t capacity, int32_t* n_out);
+
 /* Same forward with HOST x and y buffers: copies x to the device, runs the
  * forward, copies y back and waits for it -- the call a host-only user makes.
  * dev_x / dev_y are caller-provided device staging buffers of rows*in and
