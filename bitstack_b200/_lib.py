@@ -9,7 +9,7 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libbitstack_b200.so")
+LIB_PATH = os.environ.get("BITSTACK_B200_LIB") or os.path.join(_HERE, "libbitstack_b200.so")
 
 ALGO_AUTO, ALGO_GENERAL, ALGO_GEMV_MMA, ALGO_REBUILD_GEMM, ALGO_GEMV_TC5 = 0, 1, 2, 3, 4
 
@@ -47,6 +47,8 @@ SIGNATURES = {
     "bsb_linear_grouped_workspace_bytes": (_I64, [_WP, _I32, _I64, C.c_int]),
     "bsb_debug_gemv_status": (C.c_int, [_WP, _I32, _P, C.POINTER(C.c_int32)]),
     "bsb_debug_launch_count": (_I64, []),
+    "bsb_debug_set_trace": (C.c_int, [_P]),
+    "bsb_debug_set_mode": (C.c_int, [_I32]),
     "bsb_debug_profile_start": (C.c_int, [_I32]),
     "bsb_debug_profile_stop": (C.c_int, [C.POINTER(C.c_float), _I32, C.POINTER(_I32)]),
     "bsb_linear_forward_host": (C.c_int, [_WP, _P, _I64, _P, _P, _P, _P, _I64, C.c_int, _P]),

@@ -35,9 +35,10 @@ def _stale(target: str, deps) -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
+def build(force: bool = False, verbose: bool = False, extra_flags=None, lib_path: str = LIB, objdir_name: str = "build") -> str:
+    """`extra_flags` / `lib_path` / `objdir_name` build a tuning variant beside the product library."""
     nvcc = _nvcc()
-    objdir = os.path.join(HERE, "build")
+    objdir = os.path.join(HERE, objdir_name)
     os.makedirs(objdir, exist_ok=True)
     objs = []
     procs = []
@@ -46,7 +47,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         obj = os.path.join(objdir, src.replace(".cu", ".o"))
         objs.append(obj)
         if force or _stale(obj, [path] + HEADERS):
-            cmd = [nvcc, "-c", path, "-o", obj] + FLAGS + (["-Xptxas", "-v"] if verbose else [])
+            cmd = [nvcc, "-c", path, "-o", obj] + FLAGS + list(extra_flags or []) + (["-Xptxas", "-v"] if verbose else [])
             procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
     failed = False
     for src, p in procs:
@@ -56,10 +57,10 @@ def build(force: bool = False, verbose: bool = False) -> str:
         failed |= p.returncode != 0
     if failed:
         raise RuntimeError("nvcc failed")
-    if force or procs or _stale(LIB, objs):
-        cmd = [nvcc, "-shared", "-o", LIB] + objs + ["-gencode", "arch=compute_100a,code=sm_100a", "-lcudart"]
+    if force or procs or _stale(lib_path, objs):
+        cmd = [nvcc, "-shared", "-o", lib_path] + objs + ["-gencode", "arch=compute_100a,code=sm_100a", "-lcudart"]
         subprocess.check_call(cmd)
-    return LIB
+    return lib_path
 
 
 if __name__ == "__main__":

@@ -272,6 +272,16 @@ int bsb_debug_gemv_status(const bsb_weight* ws, int32_t n_weights, const void* w
   return BSB_OK;
 }
 
+int bsb_debug_set_trace(void* device_buffer) {
+  gemv_tc5_set_trace((unsigned long long*)device_buffer);
+  return BSB_OK;
+}
+
+int bsb_debug_set_mode(int32_t mode) {
+  gemv_tc5_set_dbg(mode);
+  return BSB_OK;
+}
+
 int64_t bsb_debug_launch_count(void) { return (int64_t)g_launches; }
 
 int bsb_debug_profile_start(int32_t max_launches) {

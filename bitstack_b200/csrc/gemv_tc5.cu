@@ -15,9 +15,10 @@
 // as two e4m3 pieces (rows 0-15 "hi", 16-31 "lo") in the same K order, so
 //     T[m,r] = D_hi + D_lo = C_r + 2 s_r sum_n b Z,    D_j[m,r] = (T - C_r)/s_r - sum_n Z.
 //
-// CTA = 192 threads: warps 0-3 stream sign bytes (cp.async FIFO in shared memory, one
-// row per thread), expand, feed tensor memory, and run the epilogue; warp 4 issues the
-// MMAs; warp 5 owns tensor-memory allocation and the Z' bulk copies.  All hand-offs
+// CTA = 320 threads: two groups of four producer warps stream sign bytes (cp.async FIFO
+// in shared memory, one row per thread, alternate 128-column stages per group), expand
+// them and feed tensor memory; group 0 also runs the epilogue; warp 8 issues the MMAs;
+// warp 9 owns tensor-memory allocation and the Z' bulk copies.  All hand-offs
 // are mbarriers with time-bounded waits: on a timeout the kernel raises a status word
 // and leaves, it never spins forever.
 #include <cuda_fp8.h>
@@ -31,11 +32,18 @@ namespace {
 constexpr int kChunkCols = 512;                 // columns per Z' slab / per 64 B of a sign row
 constexpr int kChunkBytes = kChunkCols * 32;    // 16 words x 1 KB operand tile
 constexpr int kTileRows = 128;
-constexpr int kThreads = 192;
-constexpr int kNA = 6;                          // A-operand ring stages (32 tensor-memory columns each)
-constexpr int kNZ = 3;                          // Z' slabs resident in shared memory
-constexpr int kNP = 4;                          // sign chunks in the per-thread FIFO
-constexpr int kTmemCols = 256;                  // 32 (D) + kNA*32 (A ring) rounded up to a power of two
+constexpr int kSets = 2;                        // producer warp groups; set s expands stage s of every chunk
+constexpr int kThreads = (kSets * 4 + 2 + 4) * 32; // producers, MMA warp, loader warp, 4 epilogue warps
+constexpr int kNA = 3;                          // A-operand ring stages (64 tensor-memory columns = 8 MMAs each)
+#ifndef BSB_NZ
+#define BSB_NZ 3
+#endif
+#ifndef BSB_NP
+#define BSB_NP 4
+#endif
+constexpr int kNZ = BSB_NZ;                          // Z' slabs resident in shared memory
+constexpr int kNP = BSB_NP;                          // sign chunks in the per-thread FIFO
+constexpr int kTmemCols = 256;                  // 2 x 32 (D, double buffered) + kNA*64 (A ring)
 constexpr int kMaxGroup = 4;
 constexpr float kTargetMax = 320.f;
 constexpr float kMinD = 0.75f;
@@ -64,6 +72,8 @@ struct TcParams {
   float* inv_scale;  // [(weight,block)][16]
   int* counters;     // [row tile]
   int* status;       // 0 = fine, else the code of the wait that gave up
+  unsigned long long* trace;  // optional [CTA][16] cycle counters (debug), or nullptr
+  int dbg;           // 0 = normal; 1 = MMA side only, 2 = producer side only (timing experiments, wrong results)
   float* partials;
   int64_t part_base[kMaxGroup];
 };
@@ -277,15 +287,28 @@ __global__ void __launch_bounds__(256) zprep_tc5_kernel(TcParams P, const __half
   }
 }
 
+// cycle accounting for the optional trace (one elected lane per role writes)
+#define TR_BEGIN(var) const long long var = tr ? clock64() : 0
+#define TR_ADD(slot, var) do { if (tr) S.trace[slot] += (unsigned long long)(clock64() - var); } while (0)
+
 // ------------------------------------------------------------------ main kernel
+// One CTA = one 128-row tile x one column split of one weight, ALL active blocks:
+// the block loop runs inside the CTA so that set-up, pipeline fill and the final
+// reduction are paid once, and the fp32 output of a row is accumulated over blocks in
+// a register of its epilogue thread.  The accumulator D is double buffered in tensor
+// memory: while the epilogue warps read block j, the MMAs of block j+1 run.
 struct __align__(16) SmemLayout {
   uint8_t zs[kNZ][kChunkBytes];         // Z' operand slabs (bulk-copied)
-  uint4 fifo[kNP][4][kTileRows];        // per-thread sign FIFO: [slot][16-byte piece][thread]
-  uint64_t afull[kNA], aempty[kNA], zfull[kNZ], zempty[kNZ], dfull;
-  float ksum[16], inv[16];
+  uint4 fifo[kNP][4][kTileRows];        // per-thread sign FIFO: [slot][16-byte piece][row]
+  uint64_t afull[kNA], aempty[kNA], zfull[kNZ], zempty[kNZ], dfull[2], dempty[2];
+  unsigned long long trace[16];
   uint32_t tmem_base;
-  int last, abort_flag;
+  int last;
 };
+
+constexpr int kWarpMma = kSets * 4;
+constexpr int kWarpLoad = kSets * 4 + 1;
+constexpr int kWarpEpi = kSets * 4 + 2;   // four epilogue warps follow
 
 __global__ void __launch_bounds__(kThreads) gemv_tc5_kernel(TcParams P) {
   extern __shared__ uint8_t smem_raw[];
@@ -295,181 +318,263 @@ __global__ void __launch_bounds__(kThreads) gemv_tc5_kernel(TcParams P) {
   while (wi + 1 < P.n_weights && (int)blockIdx.x >= P.item_base[wi + 1]) ++wi;
   const bsb_weight& w = P.w[wi];
   const int nsplit = P.splits[wi];
-  int item = blockIdx.x - P.item_base[wi];
+  const int item = blockIdx.x - P.item_base[wi];
   const int split = item % nsplit;
-  item /= nsplit;
-  const int j = item % w.blocks;
-  const int rt = item / w.blocks;
-  const int N = w.in_features, M = w.out_features;
+  const int rt = item / nsplit;
+  const int N = w.in_features, M = w.out_features, NB = w.blocks;
   const int c_lo = split * P.chunks_per_item[wi];
   const int c_hi = min(P.n_chunks, c_lo + P.chunks_per_item[wi]);
   const int nch = c_hi - c_lo;
-  const int jb = P.blk_base[wi] + j;
+  const int total = NB * nch;                 // chunks this CTA streams, block-major
+  const int jb0 = P.blk_base[wi];
+  // every row tile walks the blocks in a different rotation, so that co-running CTAs do not
+  // all pull the same Z' slab out of the same L2 lines at the same moment
+  const int j_rot = rt % NB;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // trace slots: 0-3 producer (total, fifo wait, ring wait, expand+store), 4-8 MMA (total, Z' wait,
+  // operand wait, accumulator wait, issue), 9-10 epilogue (accumulator wait, total), 11 loader wait,
+  // 12 CTA total, 13 set-up
+  unsigned long long* tr = (P.trace && lane == 0 && (warp == 0 || warp == kWarpMma || warp == kWarpLoad || warp == kWarpEpi))
+                               ? P.trace + (int64_t)blockIdx.x * 16 : nullptr;
+  TR_BEGIN(t_cta);
 
   // ---- set-up ---------------------------------------------------------------------
-  if (warp == 5) {
+  if (warp == kWarpLoad) {
     tmem_alloc(&S.tmem_base, kTmemCols);
     tmem_relinquish();
   }
+  if (tid < 16) S.trace[tid] = 0;
   if (tid == 0) {
     for (int i = 0; i < kNA; ++i) { mbar_init(&S.afull[i], kTileRows); mbar_init(&S.aempty[i], 1); }
     for (int i = 0; i < kNZ; ++i) { mbar_init(&S.zfull[i], 1); mbar_init(&S.zempty[i], 1); }
-    mbar_init(&S.dfull, 1);
-    S.abort_flag = 0;
+    for (int i = 0; i < 2; ++i) { mbar_init(&S.dfull[i], 1); mbar_init(&S.dempty[i], kTileRows); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (tid < 16) {
-    float kk = 0.f;
-    for (int c = c_lo; c < c_hi; ++c) kk += P.kconst[((int64_t)jb * P.n_chunks + c) * 16 + tid];
-    S.ksum[tid] = kk;
-    S.inv[tid] = P.inv_scale[(int64_t)jb * 16 + tid];
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tbase = S.tmem_base;
-  const uint32_t colD = 0, colA = 32;
+  const uint32_t colA = 64;   // D buffers occupy columns [0,32) and [32,64)
+  if (warp == 0) TR_ADD(13, t_cta);
 
-  if (warp == 5) {
+  if (warp == kWarpLoad) {
+    if (P.dbg == 2 || P.dbg == 3) goto teardown;
     // ---- Z' loader -------------------------------------------------------------------
     if (lane == 0) {
-      const uint8_t* zsrc = P.zops + ((int64_t)jb * P.n_chunks + c_lo) * kChunkBytes;
-      for (int ci = 0; ci < nch; ++ci) {
-        const int slot = ci % kNZ, n = ci / kNZ;
-        if (n >= 1 && !mbar_wait(&S.zempty[slot], (n - 1) & 1)) { atomicExch(P.status, 1); S.abort_flag = 1; break; }
+      for (int g = 0; g < total; ++g) {
+        const int js = g / nch, ci = g - js * nch;
+        const int j = (js + j_rot) % NB;
+        const int slot = g % kNZ, n = g / kNZ;
+        TR_BEGIN(t0);
+        if (n >= 1 && !mbar_wait(&S.zempty[slot], (n - 1) & 1)) { atomicExch(P.status, 1); break; }
+        TR_ADD(11, t0);
+        const uint8_t* zsrc = P.zops + ((int64_t)(jb0 + j) * P.n_chunks + c_lo + ci) * kChunkBytes;
         mbar_expect_tx(&S.zfull[slot], kChunkBytes);
-        bulk_g2s(S.zs[slot], zsrc + (int64_t)ci * kChunkBytes, kChunkBytes, &S.zfull[slot]);
+        bulk_g2s(S.zs[slot], zsrc, kChunkBytes, &S.zfull[slot]);
       }
     }
-  } else if (warp == 4) {
+  } else if (warp == kWarpMma) {
+    if (P.dbg == 2) goto teardown;
     // ---- MMA issuer ------------------------------------------------------------------
     if (lane == 0) {
       const uint32_t idesc = make_idesc_f8(128, 32);
       int it = 0;
       bool ok = true;
-      for (int ci = 0; ci < nch && ok; ++ci) {
-        const int slot = ci % kNZ, n = ci / kNZ;
-        if (!mbar_wait(&S.zfull[slot], n & 1)) { atomicExch(P.status, 2); S.abort_flag = 1; ok = false; break; }
+      TR_BEGIN(t_mma);
+      for (int g = 0; g < total && ok; ++g) {
+        const int j = g / nch, ci = g - j * nch;
+        const int b = j & 1;
+        if (ci == 0 && j >= 2 && P.dbg != 4) {
+          TR_BEGIN(t0);
+          if (!mbar_wait(&S.dempty[b], ((j >> 1) - 1) & 1)) { atomicExch(P.status, 6); ok = false; break; }
+          TR_ADD(7, t0);
+          tc_fence_after();
+        }
+        const int slot = g % kNZ, n = g / kNZ;
+        TR_BEGIN(t1);
+        if (P.dbg != 3 && !mbar_wait(&S.zfull[slot], n & 1)) { atomicExch(P.status, 2); ok = false; break; }
+        TR_ADD(5, t1);
         const uint32_t zaddr = smem_u32(S.zs[slot]);
 #pragma unroll 1
-        for (int q = 0; q < 4; ++q, ++it) {
+        for (int q = 0; q < 2; ++q, ++it) {
           const int a = it % kNA, na = it / kNA;
-          if (!mbar_wait(&S.afull[a], na & 1)) { atomicExch(P.status, 3); S.abort_flag = 1; ok = false; break; }
+          TR_BEGIN(t2);
+          if (P.dbg != 1 && P.dbg != 3 && P.dbg != 4 && !mbar_wait(&S.afull[a], na & 1)) { atomicExch(P.status, 3); ok = false; break; }
+          TR_ADD(6, t2);
+          TR_BEGIN(t3);
           tc_fence_after();
+          // one commit per eight MMAs: the issuing thread, not the tensor pipe, is the scarce resource
+          uint64_t bdesc = make_smem_desc(zaddr + (uint32_t)(q * 8) * 1024u, 128, 256);
+          const uint32_t acol = tbase + colA + a * 64;
 #pragma unroll
-          for (int ww = 0; ww < 4; ++ww) {
-            const uint64_t bdesc = make_smem_desc(zaddr + (uint32_t)(q * 4 + ww) * 1024u, 128, 256);
-            mma_ts_f8(tbase + colD, tbase + colA + a * 32 + ww * 8, bdesc, idesc, (it > 0 || ww > 0) ? 1u : 0u);
+          for (int ww = 0; ww < 8; ++ww) {
+            mma_ts_f8(tbase + b * 32, acol + ww * 8, bdesc, idesc, (ci > 0 || q > 0 || ww > 0) ? 1u : 0u);
+            bdesc += 1024u >> 4;   // next 1 KB operand tile (address field counts 16-byte units)
           }
           mma_commit(&S.aempty[a]);
+          TR_ADD(8, t3);
         }
-        if (ok) mma_commit(&S.zempty[slot]);
+        if (!ok) break;
+        mma_commit(&S.zempty[slot]);
+        if (ci == nch - 1) mma_commit(&S.dfull[b]);
       }
-      if (ok) mma_commit(&S.dfull);
+      TR_ADD(4, t_mma);
     }
-  } else {
-    // ---- producers: one sign row per thread ---------------------------------------------
-    const int row = min(rt * kTileRows + tid, M - 1);
-    const uint8_t* rowp = w.qweight + (int64_t)j * w.q_block_stride + (int64_t)row * (N / 8);
-    const uint32_t lane_base = tbase + ((uint32_t)(warp * 32) << 16);
-    auto issue = [&](int ci) {
-      const int slot = ci % kNP;
+  } else if (warp < kWarpMma) {
+    // ---- producers: one sign row per thread; group s expands stage s of every chunk -------
+    if (P.dbg == 1 || P.dbg == 3 || P.dbg == 4) goto teardown;
+    const int set = warp >> 2;
+    const int rtid = tid & (kTileRows - 1);
+    const int row = min(rt * kTileRows + rtid, M - 1);
+    const uint8_t* rowp = w.qweight + (int64_t)row * (N / 8);
+    const uint32_t lane_base = tbase + ((uint32_t)((warp & 3) * 32) << 16);
+    auto issue = [&](int g) {
+      const int js = g / nch, ci = g - js * nch;
+      const int j = (js + j_rot) % NB;
+      const int slot = g % kNP;
 #pragma unroll
-      for (int p = 0; p < 4; ++p) {
+      for (int pp = 0; pp < 2; ++pp) {
+        const int p = set * 2 + pp;      // this group's 32 bytes (256 columns) of the 64-byte chunk
         const int byte = (c_lo + ci) * (kChunkCols / 8) + p * 16;
-        if (byte * 8 < N) cp_async16(&S.fifo[slot][p][tid], rowp + byte);
-        else S.fifo[slot][p][tid] = make_uint4(0, 0, 0, 0);
+        if (byte * 8 < N) cp_async16(&S.fifo[slot][p][rtid], rowp + (int64_t)j * w.q_block_stride + byte);
+        else S.fifo[slot][p][rtid] = make_uint4(0, 0, 0, 0);
       }
     };
 #pragma unroll
-    for (int ci = 0; ci < kNP - 1; ++ci) {
-      if (ci < nch) issue(ci);
+    for (int g = 0; g < kNP - 1; ++g) {
+      if (g < total) issue(g);
       asm volatile("cp.async.commit_group;\n" ::: "memory");
     }
-    int it = 0;
     bool ok = true;
+    TR_BEGIN(t_prod);
 #pragma unroll 1
-    for (int ci = 0; ci < nch && ok; ++ci) {
-      if (ci + kNP - 1 < nch) issue(ci + kNP - 1);
+    for (int g = 0; g < total && ok; ++g) {
+      if (g + kNP - 1 < total) issue(g + kNP - 1);
       asm volatile("cp.async.commit_group;\n" ::: "memory");
+      TR_BEGIN(t0);
       asm volatile("cp.async.wait_group %0;\n" ::"n"(kNP - 1) : "memory");
-      const int slot = ci % kNP;
-#pragma unroll 1
-      for (int p = 0; p < 4; ++p, ++it) {
-        const uint4 v = S.fifo[slot][p][tid];
-        const int a = it % kNA, na = it / kNA;
-        if (na >= 1) {
-          // warp-uniform decision: the tensor-memory store below is a warp-wide instruction
-          const bool got = __all_sync(0xFFFFFFFFu, mbar_wait(&S.aempty[a], (na - 1) & 1) ? 1 : 0);
-          if (!got) { atomicExch(P.status, 4); S.abort_flag = 1; ok = false; break; }
-          tc_fence_after();
-        }
-        uint32_t r[32];
-        expand_word(v.x, r);
-        expand_word(v.y, r + 8);
-        expand_word(v.z, r + 16);
-        expand_word(v.w, r + 24);
-        tmem_st32(lane_base + colA + a * 32, r);
-        tmem_wait_st();
-        tc_fence_before();
-        mbar_arrive(&S.afull[a]);
+      TR_ADD(1, t0);
+      const int slot = g % kNP;
+      const int it = g * 2 + set;        // stage index: two stages of eight MMAs per chunk
+      const int a = it % kNA, na = it / kNA;
+      const uint4 v0 = S.fifo[slot][set * 2][rtid];
+      const uint4 v1 = S.fifo[slot][set * 2 + 1][rtid];
+      if (na >= 1 && P.dbg != 2) {
+        // warp-uniform decision: the tensor-memory stores below are warp-wide instructions
+        TR_BEGIN(t1);
+        const bool got = __all_sync(0xFFFFFFFFu, mbar_wait(&S.aempty[a], (na - 1) & 1) ? 1 : 0);
+        TR_ADD(2, t1);
+        if (!got) { atomicExch(P.status, 4); ok = false; break; }
+        tc_fence_after();
       }
+      TR_BEGIN(t2);
+      uint32_t r[32];
+      expand_word(v0.x, r);
+      expand_word(v0.y, r + 8);
+      expand_word(v0.z, r + 16);
+      expand_word(v0.w, r + 24);
+      tmem_st32(lane_base + colA + a * 64, r);
+      expand_word(v1.x, r);
+      expand_word(v1.y, r + 8);
+      expand_word(v1.z, r + 16);
+      expand_word(v1.w, r + 24);
+      tmem_st32(lane_base + colA + a * 64 + 32, r);
+      tmem_wait_st();
+      tc_fence_before();
+      if (P.dbg != 2) mbar_arrive(&S.afull[a]);
+      TR_ADD(3, t2);
     }
+    TR_ADD(0, t_prod);
     asm volatile("cp.async.wait_group 0;\n" ::: "memory");
-
-    // ---- epilogue: y_part[m] = sum_r U[m,r] ((D_hi + D_lo)[m,r] / s_r - K_r) -------------
-    // every lane of the warp takes the same branch: the tensor-memory load is warp-wide
-    const int mine = ok ? (mbar_wait(&S.dfull, 0) ? 1 : 0) : 0;
-    const bool done = __all_sync(0xFFFFFFFFu, mine);
-    if (!done && lane == 0) atomicExch(P.status, 5);
-    float ypart = 0.f;
-    if (done) {
-      tc_fence_after();
-      uint32_t d[32];
-      tmem_ld32(lane_base + colD, d);
-      tmem_wait_ld();
+  } else {
+    if (P.dbg == 2 || P.dbg == 4) goto teardown;
+    // ---- epilogue warps: y[m] += sum_r U_j[m,r] ((D_hi + D_lo)[m,r] / s_r - K_r) per block ----
+    const int quarter = warp & 3;                     // tensor-memory lanes this warp may read
+    const int rtid = quarter * 32 + lane;
+    const int row = min(rt * kTileRows + rtid, M - 1);
+    const uint32_t lane_base = tbase + ((uint32_t)(quarter * 32) << 16);
+    float yacc = 0.f;
+    bool ok = true;
+    TR_BEGIN(t_epi);
+#pragma unroll 1
+    for (int js = 0; js < NB; ++js) {
+      const int j = (js + j_rot) % NB;
+      const int b = js & 1;
+      // operands of this block's epilogue, fetched while its MMAs run
       const __half* u = reinterpret_cast<const __half*>(w.u) + (int64_t)j * w.u_block_stride + (int64_t)row * 16;
       const uint4 u0 = __ldg(reinterpret_cast<const uint4*>(u));
       const uint4 u1 = __ldg(reinterpret_cast<const uint4*>(u) + 1);
+      float inv_mine = 0.f, k_mine = 0.f;
+      if (lane < 16) {
+        inv_mine = P.inv_scale[(int64_t)(jb0 + j) * 16 + lane];
+        const float* kc = P.kconst + ((int64_t)(jb0 + j) * P.n_chunks + c_lo) * 16 + lane;
+        for (int c = 0; c < nch; ++c) k_mine += kc[c * 16];
+      }
+      TR_BEGIN(t0);
+      const int mine = mbar_wait(&S.dfull[b], (js >> 1) & 1) ? 1 : 0;
+      TR_ADD(9, t0);
+      if (!__all_sync(0xFFFFFFFFu, mine)) { if (lane == 0) atomicExch(P.status, 5); ok = false; break; }
+      tc_fence_after();
+      uint32_t d[32];
+      tmem_ld32(lane_base + b * 32, d);
+      tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(&S.dempty[b]);
       const uint32_t uw[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
 #pragma unroll
       for (int rr = 0; rr < 8; ++rr) {
         const __half2 h2 = *reinterpret_cast<const __half2*>(&uw[rr]);
         const float t0 = __uint_as_float(d[2 * rr]) + __uint_as_float(d[16 + 2 * rr]);
         const float t1 = __uint_as_float(d[2 * rr + 1]) + __uint_as_float(d[16 + 2 * rr + 1]);
-        ypart = fmaf(__low2float(h2), t0 * S.inv[2 * rr] - S.ksum[2 * rr], ypart);
-        ypart = fmaf(__high2float(h2), t1 * S.inv[2 * rr + 1] - S.ksum[2 * rr + 1], ypart);
+        const float i0 = __shfl_sync(0xFFFFFFFFu, inv_mine, 2 * rr), i1 = __shfl_sync(0xFFFFFFFFu, inv_mine, 2 * rr + 1);
+        const float k0 = __shfl_sync(0xFFFFFFFFu, k_mine, 2 * rr), k1 = __shfl_sync(0xFFFFFFFFu, k_mine, 2 * rr + 1);
+        yacc = fmaf(__low2float(h2), t0 * i0 - k0, yacc);
+        yacc = fmaf(__high2float(h2), t1 * i1 - k1, yacc);
       }
     }
-    float* part = P.partials + P.part_base[wi] + ((int64_t)rt * (w.blocks * nsplit) + (j * nsplit + split)) * kTileRows;
-    part[tid] = done ? ypart : __int_as_float(0x7FC00000);  // NaN marks a tile that was given up
-    __threadfence();
+    TR_ADD(10, t_epi);
+    const int m = rt * kTileRows + rtid;
+    if (nsplit == 1) {
+      if (m < M) {
+        float v = ok ? yacc : __int_as_float(0x7FC00000);   // NaN marks a tile that was given up
+        if (w.bias) v += __half2float(reinterpret_cast<const __half*>(w.bias)[m]);
+        P.y[wi][m] = __float2half_rn(v);
+      }
+    } else {
+      float* part = P.partials + P.part_base[wi] + ((int64_t)rt * nsplit + split) * kTileRows;
+      part[rtid] = ok ? yacc : __int_as_float(0x7FC00000);
+      __threadfence();
+    }
   }
 
+teardown:
   // ---- tear-down: tensor memory is released only after every role is done ---------------
   tc_fence_before();
   __syncthreads();
-  if (tid == 0) {
-    const int expected = w.blocks * nsplit;
-    const int old = atomicAdd(&P.counters[P.tile_base[wi] + rt], 1);
-    S.last = (old == expected - 1);
+  if (warp == 0) TR_ADD(12, t_cta);
+  if (P.trace) {
+    __syncthreads();
+    if (tid < 16) P.trace[(int64_t)blockIdx.x * 16 + tid] = S.trace[tid];
   }
-  if (warp == 5) {
+  if (warp == kWarpLoad) {
     __syncwarp();
     tmem_dealloc(tbase, kTmemCols);
   }
+  if (nsplit == 1) return;
+  if (tid == 0) {
+    const int old = atomicAdd(&P.counters[P.tile_base[wi] + rt], 1);
+    S.last = (old == nsplit - 1);
+  }
   __syncthreads();
   if (!S.last || tid >= kTileRows) return;
-  // the last CTA of this row tile adds all partial sums in a fixed order
+  // the last CTA of this row tile adds the column-split partial sums in a fixed order
   __threadfence();
   const int m = rt * kTileRows + tid;
   if (m >= M) return;
-  const int n_part = w.blocks * nsplit;
-  const float* all = P.partials + P.part_base[wi] + (int64_t)rt * n_part * kTileRows;
+  const float* all = P.partials + P.part_base[wi] + (int64_t)rt * nsplit * kTileRows;
   float sum = 0.f;
-  for (int i = 0; i < n_part; ++i) sum += __ldcg(all + (int64_t)i * kTileRows + tid);
+  for (int i = 0; i < nsplit; ++i) sum += __ldcg(all + (int64_t)i * kTileRows + tid);
   if (w.bias) sum += __half2float(reinterpret_cast<const __half*>(w.bias)[m]);
   P.y[wi][m] = __float2half_rn(sum);
 }
@@ -488,30 +593,31 @@ void make_tc_plan(const bsb_weight* ws, int n, TcPlan& pl) {
   P.n_weights = n;
   const int N = ws[0].in_features;
   P.n_chunks = (int)ceil_div64(N, kChunkCols);
-  const int target = sm_count() * 6;   // items wanted: a few per resident CTA slot
-  int total_tile_blocks = 0;
-  for (int i = 0; i < n; ++i) total_tile_blocks += (int)ceil_div64(ws[i].out_features, kTileRows) * ws[i].blocks;
+  // CTAs wanted: about two per multiprocessor (both stay resident and share its tensor pipe)
+  const int target = sm_count() * 2;
+  int total_tiles = 0;
+  for (int i = 0; i < n; ++i) total_tiles += (int)ceil_div64(ws[i].out_features, kTileRows);
+  int S = (int)ceil_div64(target, total_tiles > 0 ? total_tiles : 1);
+  if (S * total_tiles > target && S > 1) --S;          // round down: never more CTAs than slots
+  if (S > P.n_chunks) S = P.n_chunks;
+  if (S < 1) S = 1;
+  const int cpi = (int)ceil_div64(P.n_chunks, S);
+  S = (int)ceil_div64(P.n_chunks, cpi);
   int items = 0, tiles = 0, blks = 0;
   int64_t part_floats = 0;
   for (int i = 0; i < n; ++i) {
     P.w[i] = ws[i];
     const int n_rt = (int)ceil_div64(ws[i].out_features, kTileRows);
-    int S = (int)ceil_div64(target, total_tile_blocks > 0 ? total_tile_blocks : 1);
-    const int max_split = (P.n_chunks + 1) / 2;   // at least two chunks per item when possible
-    if (S > max_split) S = max_split;
-    if (S < 1) S = 1;
-    const int cpi = (int)ceil_div64(P.n_chunks, S);
-    S = (int)ceil_div64(P.n_chunks, cpi);
     P.splits[i] = S;
     P.chunks_per_item[i] = cpi;
     P.item_base[i] = items;
     P.tile_base[i] = tiles;
     P.blk_base[i] = blks;
     P.part_base[i] = part_floats;
-    items += n_rt * ws[i].blocks * S;
+    items += n_rt * S;
     tiles += n_rt;
     blks += ws[i].blocks;
-    part_floats += (int64_t)n_rt * ws[i].blocks * S * kTileRows;
+    part_floats += (int64_t)n_rt * S * kTileRows;
   }
   P.item_base[n] = items;
   P.tile_base[n] = tiles;
@@ -544,6 +650,11 @@ void make_tc_plan(const bsb_weight* ws, int n, TcPlan& pl) {
 }
 
 }  // namespace
+
+static unsigned long long* g_trace = nullptr;
+static int g_dbg = 0;
+void gemv_tc5_set_dbg(int m) { g_dbg = m; }
+void gemv_tc5_set_trace(unsigned long long* p) { g_trace = p; }
 
 bool gemv_tc5_supported(const bsb_weight& w) {
   return w.k == 16 && w.blocks >= 1 && w.in_features % 128 == 0 && w.out_features >= 1 &&
@@ -595,6 +706,8 @@ int launch_gemv_tc5(const bsb_weight* ws, int n_weights, const __half* x, __half
   P.counters = (int*)(base + (int64_t)(uintptr_t)P.counters);
   P.partials = (float*)(base + (int64_t)(uintptr_t)P.partials);
   P.status = (int*)(base + pl.status_off);
+  P.trace = g_trace;
+  P.dbg = g_dbg;
   for (int i = 0; i < n_weights; ++i) {
     P.y[i] = ys[i];
     if (ws[i].vt_absmax) {

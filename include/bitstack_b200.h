@@ -132,6 +132,12 @@ int bsb_debug_gemv_status(const bsb_weight* ws, int32_t n_weights, const void* w
  * the tcgen05 decode kernel (at most max_launches); stop waits for them and writes
  * the per-launch durations in milliseconds. */
 int64_t bsb_debug_launch_count(void);
+/* device_buffer: zeroed uint64 [CTAs][16] that the tcgen05 decode kernel fills with per-role
+ * cycle counts (waits, issue, totals) for performance analysis; NULL switches it off. */
+int bsb_debug_set_trace(void* device_buffer);
+/* Timing experiments on the tcgen05 decode kernel: 0 = normal, 1 = tensor-core side only,
+ * 2 = sign-streaming side only.  Modes 1 and 2 produce WRONG outputs by design. */
+int bsb_debug_set_mode(int32_t mode);
 int bsb_debug_profile_start(int32_t max_launches);
 int bsb_debug_profile_stop(float* ms_out, int32_t capacity, int32_t* n_out);
 
