@@ -21,6 +21,7 @@
 // warp 9 owns tensor-memory allocation and the Z' bulk copies.  All hand-offs
 // are mbarriers with time-bounded waits: on a timeout the kernel raises a status word
 // and leaves, it never spins forever.
+#include <cuda.h>
 #include <cuda_fp8.h>
 
 #include "common.cuh"
@@ -39,10 +40,11 @@ constexpr int kNA = 3;                          // A-operand ring stages (64 ten
 #define BSB_NZ 3
 #endif
 #ifndef BSB_NP
-#define BSB_NP 4
+#define BSB_NP 6
 #endif
 constexpr int kNZ = BSB_NZ;                          // Z' slabs resident in shared memory
-constexpr int kNP = BSB_NP;                          // sign chunks in the per-thread FIFO
+constexpr int kNP = BSB_NP;                          // sign tiles (128 rows x 64 B, TMA) resident in shared memory
+constexpr int kSignTileBytes = kTileRows * 64;
 constexpr int kTmemCols = 256;                  // 2 x 32 (D, double buffered) + kNA*64 (A ring)
 constexpr int kMaxGroup = 4;
 constexpr float kTargetMax = 320.f;
@@ -56,7 +58,8 @@ __host__ __device__ constexpr uint32_t class_byte(int i) {
        : i == 4 ? 0x2Cu : i == 5 ? 0x1Cu : i == 6 ? 0x00u : 0x38u;
 }
 
-struct TcParams {
+struct alignas(64) TcParams {
+  CUtensorMap sign_map[kMaxGroup];   // u8 [blocks][out][in/8], box 1 x 128 x 64, 64-byte swizzle
   bsb_weight w[kMaxGroup];
   const float* vt_absmax[kMaxGroup];
   __half* y[kMaxGroup];
@@ -179,6 +182,12 @@ __device__ __forceinline__ void bulk_g2s(void* smem, const void* gmem, uint32_t 
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(smem_u32(smem)), "l"(gmem), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
+// 3-D tiled TMA load (no multicast): box lands in shared memory, bytes are counted on `bar`
+__device__ __forceinline__ void tma_load_3d(void* smem, const CUtensorMap* map, int c0, int c1, int c2, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(smem_u32(smem)), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar)) : "memory");
+}
 __device__ __forceinline__ float e4m3_to_float(uint8_t v) {
   const __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)v, __NV_E4M3);
   return __half2float(__half(h));
@@ -196,7 +205,7 @@ __device__ __forceinline__ void expand_word(uint32_t word, uint32_t* r) {
 // grid = (n_chunks, total blocks), 256 threads.  Operand tile of word w (32 columns):
 // byte offset (n%8)*16 + (n/8)*256 + (k%16) + (k/16)*128 with n = 16*piece + rank and
 // k = 4*i + c for the column 8c+7-i of the word.
-__global__ void __launch_bounds__(256) zprep_tc5_kernel(TcParams P, const __half* __restrict__ x) {
+__global__ void __launch_bounds__(256) zprep_tc5_kernel(const __grid_constant__ TcParams P, const __half* __restrict__ x) {
   __shared__ __align__(16) __half vt_s[16][kChunkCols + 8];
   __shared__ float x_s[kChunkCols];
   __shared__ float red[8];
@@ -297,10 +306,10 @@ __global__ void __launch_bounds__(256) zprep_tc5_kernel(TcParams P, const __half
 // reduction are paid once, and the fp32 output of a row is accumulated over blocks in
 // a register of its epilogue thread.  The accumulator D is double buffered in tensor
 // memory: while the epilogue warps read block j, the MMAs of block j+1 run.
-struct __align__(16) SmemLayout {
+struct __align__(1024) SmemLayout {
   uint8_t zs[kNZ][kChunkBytes];         // Z' operand slabs (bulk-copied)
-  uint4 fifo[kNP][4][kTileRows];        // per-thread sign FIFO: [slot][16-byte piece][row]
-  uint64_t afull[kNA], aempty[kNA], zfull[kNZ], zempty[kNZ], dfull[2], dempty[2];
+  uint8_t sg[kNP][kSignTileBytes];      // sign tiles: row r at r*64, 16-byte piece p at ((p ^ ((r>>1)&3)) * 16)
+  uint64_t afull[kNA], aempty[kNA], zfull[kNZ], zempty[kNZ], sfull[kNP], sempty[kNP], dfull[2], dempty[2];
   unsigned long long trace[16];
   uint32_t tmem_base;
   int last;
@@ -310,9 +319,9 @@ constexpr int kWarpMma = kSets * 4;
 constexpr int kWarpLoad = kSets * 4 + 1;
 constexpr int kWarpEpi = kSets * 4 + 2;   // four epilogue warps follow
 
-__global__ void __launch_bounds__(kThreads) gemv_tc5_kernel(TcParams P) {
+__global__ void __launch_bounds__(kThreads) gemv_tc5_kernel(const __grid_constant__ TcParams P) {
   extern __shared__ uint8_t smem_raw[];
-  SmemLayout& S = *reinterpret_cast<SmemLayout*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~(uintptr_t)127);
+  SmemLayout& S = *reinterpret_cast<SmemLayout*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
 
   int wi = 0;
   while (wi + 1 < P.n_weights && (int)blockIdx.x >= P.item_base[wi + 1]) ++wi;
@@ -348,6 +357,7 @@ __global__ void __launch_bounds__(kThreads) gemv_tc5_kernel(TcParams P) {
   if (tid == 0) {
     for (int i = 0; i < kNA; ++i) { mbar_init(&S.afull[i], kTileRows); mbar_init(&S.aempty[i], 1); }
     for (int i = 0; i < kNZ; ++i) { mbar_init(&S.zfull[i], 1); mbar_init(&S.zempty[i], 1); }
+    for (int i = 0; i < kNP; ++i) { mbar_init(&S.sfull[i], 1); mbar_init(&S.sempty[i], kSets * kTileRows); }
     for (int i = 0; i < 2; ++i) { mbar_init(&S.dfull[i], 1); mbar_init(&S.dempty[i], kTileRows); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -359,23 +369,32 @@ __global__ void __launch_bounds__(kThreads) gemv_tc5_kernel(TcParams P) {
   if (warp == 0) TR_ADD(13, t_cta);
 
   if (warp == kWarpLoad) {
-    if (P.dbg == 2 || P.dbg == 3) goto teardown;
-    // ---- Z' loader -------------------------------------------------------------------
+    if (P.dbg == 1 || P.dbg == 3 || P.dbg == 4) goto teardown;   // experiments without the sign side also skip Z'
+    // ---- loader: Z' slabs (bulk copy) and sign tiles (tiled TMA), each with its own ring ----
     if (lane == 0) {
+      const CUtensorMap* map = &P.sign_map[wi];
       for (int g = 0; g < total; ++g) {
         const int js = g / nch, ci = g - js * nch;
         const int j = (js + j_rot) % NB;
-        const int slot = g % kNZ, n = g / kNZ;
-        TR_BEGIN(t0);
-        if (n >= 1 && !mbar_wait(&S.zempty[slot], (n - 1) & 1)) { atomicExch(P.status, 1); break; }
-        TR_ADD(11, t0);
-        const uint8_t* zsrc = P.zops + ((int64_t)(jb0 + j) * P.n_chunks + c_lo + ci) * kChunkBytes;
-        mbar_expect_tx(&S.zfull[slot], kChunkBytes);
-        bulk_g2s(S.zs[slot], zsrc, kChunkBytes, &S.zfull[slot]);
+        {
+          const int slot = g % kNP, n = g / kNP;
+          TR_BEGIN(t0);
+          if (n >= 1 && !mbar_wait(&S.sempty[slot], (n - 1) & 1)) { atomicExch(P.status, 7); break; }
+          TR_ADD(11, t0);
+          mbar_expect_tx(&S.sfull[slot], kSignTileBytes);
+          tma_load_3d(S.sg[slot], map, (c_lo + ci) * (kChunkCols / 8), rt * kTileRows, j, &S.sfull[slot]);
+        }
+        if (P.dbg != 2 && P.dbg != 5) {
+          const int slot = g % kNZ, n = g / kNZ;
+          if (n >= 1 && !mbar_wait(&S.zempty[slot], (n - 1) & 1)) { atomicExch(P.status, 1); break; }
+          const uint8_t* zsrc = P.zops + ((int64_t)(jb0 + j) * P.n_chunks + c_lo + ci) * kChunkBytes;
+          mbar_expect_tx(&S.zfull[slot], kChunkBytes);
+          bulk_g2s(S.zs[slot], zsrc, kChunkBytes, &S.zfull[slot]);
+        }
       }
     }
   } else if (warp == kWarpMma) {
-    if (P.dbg == 2) goto teardown;
+    if (P.dbg == 2 || P.dbg == 5) goto teardown;
     // ---- MMA issuer ------------------------------------------------------------------
     if (lane == 0) {
       const uint32_t idesc = make_idesc_f8(128, 32);
@@ -426,40 +445,26 @@ __global__ void __launch_bounds__(kThreads) gemv_tc5_kernel(TcParams P) {
     if (P.dbg == 1 || P.dbg == 3 || P.dbg == 4) goto teardown;
     const int set = warp >> 2;
     const int rtid = tid & (kTileRows - 1);
-    const int row = min(rt * kTileRows + rtid, M - 1);
-    const uint8_t* rowp = w.qweight + (int64_t)row * (N / 8);
     const uint32_t lane_base = tbase + ((uint32_t)((warp & 3) * 32) << 16);
-    auto issue = [&](int g) {
-      const int js = g / nch, ci = g - js * nch;
-      const int j = (js + j_rot) % NB;
-      const int slot = g % kNP;
-#pragma unroll
-      for (int pp = 0; pp < 2; ++pp) {
-        const int p = set * 2 + pp;      // this group's 32 bytes (256 columns) of the 64-byte chunk
-        const int byte = (c_lo + ci) * (kChunkCols / 8) + p * 16;
-        if (byte * 8 < N) cp_async16(&S.fifo[slot][p][rtid], rowp + (int64_t)j * w.q_block_stride + byte);
-        else S.fifo[slot][p][rtid] = make_uint4(0, 0, 0, 0);
-      }
-    };
-#pragma unroll
-    for (int g = 0; g < kNP - 1; ++g) {
-      if (g < total) issue(g);
-      asm volatile("cp.async.commit_group;\n" ::: "memory");
-    }
+    // this thread's 32 bytes (256 columns) of every 64-byte tile row, after the 64-byte swizzle
+    const int sw = (rtid >> 1) & 3;
+    const int off0 = rtid * 64 + (((set * 2) ^ sw) << 4), off1 = rtid * 64 + (((set * 2 + 1) ^ sw) << 4);
     bool ok = true;
+    int prev_a = -1;
     TR_BEGIN(t_prod);
 #pragma unroll 1
     for (int g = 0; g < total && ok; ++g) {
-      if (g + kNP - 1 < total) issue(g + kNP - 1);
-      asm volatile("cp.async.commit_group;\n" ::: "memory");
-      TR_BEGIN(t0);
-      asm volatile("cp.async.wait_group %0;\n" ::"n"(kNP - 1) : "memory");
-      TR_ADD(1, t0);
       const int slot = g % kNP;
+      TR_BEGIN(t0);
+      const bool landed = __all_sync(0xFFFFFFFFu, mbar_wait(&S.sfull[slot], (g / kNP) & 1) ? 1 : 0);
+      TR_ADD(1, t0);
+      if (!landed) { atomicExch(P.status, 8); ok = false; break; }
+      const uint4 v0 = *reinterpret_cast<const uint4*>(&S.sg[slot][off0]);
+      const uint4 v1 = *reinterpret_cast<const uint4*>(&S.sg[slot][off1]);
+      mbar_arrive(&S.sempty[slot]);      // the tile slot may be refilled once all 256 readers have their words
+      if (P.dbg == 5) continue;          // experiment: stream the tiles, do nothing with them
       const int it = g * 2 + set;        // stage index: two stages of eight MMAs per chunk
       const int a = it % kNA, na = it / kNA;
-      const uint4 v0 = S.fifo[slot][set * 2][rtid];
-      const uint4 v1 = S.fifo[slot][set * 2 + 1][rtid];
       if (na >= 1 && P.dbg != 2) {
         // warp-uniform decision: the tensor-memory stores below are warp-wide instructions
         TR_BEGIN(t1);
@@ -474,21 +479,30 @@ __global__ void __launch_bounds__(kThreads) gemv_tc5_kernel(TcParams P) {
       expand_word(v0.y, r + 8);
       expand_word(v0.z, r + 16);
       expand_word(v0.w, r + 24);
+      // hand over the PREVIOUS stage only now: its tensor-memory stores completed behind the
+      // expansion above, so the wait costs nothing
+      if (prev_a >= 0) {
+        tmem_wait_st();
+        tc_fence_before();
+        if (P.dbg != 2) mbar_arrive(&S.afull[prev_a]);
+      }
       tmem_st32(lane_base + colA + a * 64, r);
       expand_word(v1.x, r);
       expand_word(v1.y, r + 8);
       expand_word(v1.z, r + 16);
       expand_word(v1.w, r + 24);
       tmem_st32(lane_base + colA + a * 64 + 32, r);
-      tmem_wait_st();
-      tc_fence_before();
-      if (P.dbg != 2) mbar_arrive(&S.afull[a]);
+      prev_a = a;
       TR_ADD(3, t2);
     }
+    if (prev_a >= 0) {
+      tmem_wait_st();
+      tc_fence_before();
+      if (P.dbg != 2) mbar_arrive(&S.afull[prev_a]);
+    }
     TR_ADD(0, t_prod);
-    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
   } else {
-    if (P.dbg == 2 || P.dbg == 4) goto teardown;
+    if (P.dbg == 2 || P.dbg == 4 || P.dbg == 5) goto teardown;
     // ---- epilogue warps: y[m] += sum_r U_j[m,r] ((D_hi + D_lo)[m,r] / s_r - K_r) per block ----
     const int quarter = warp & 3;                     // tensor-memory lanes this warp may read
     const int rtid = quarter * 32 + lane;
@@ -651,6 +665,45 @@ void make_tc_plan(const bsb_weight* ws, int n, TcPlan& pl) {
 
 }  // namespace
 
+// cuTensorMapEncodeTiled is a driver-API symbol; it is looked up through the runtime so that
+// the library links against cudart only
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// packed signs of one weight as a 3-D byte tensor [blocks][out][in/8]; one box = 128 rows x 64 bytes
+static int make_sign_map(const bsb_weight& w, CUtensorMap* map) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) {
+    set_error("cuTensorMapEncodeTiled is not available from this driver");
+    return BSB_ECUDA;
+  }
+  const cuuint64_t dims[3] = {(cuuint64_t)(w.in_features / 8), (cuuint64_t)w.out_features, (cuuint64_t)w.blocks};
+  const cuuint64_t strides[2] = {(cuuint64_t)(w.in_features / 8), (cuuint64_t)(w.blocks > 1 ? w.q_block_stride : (int64_t)w.out_features * (w.in_features / 8))};
+  const cuuint32_t box[3] = {64, (cuuint32_t)kTileRows, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, (void*)w.qweight, dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed with code %d (out=%d in=%d blocks=%d stride=%lld)", (int)r, w.out_features,
+              w.in_features, w.blocks, (long long)w.q_block_stride);
+    return BSB_ECUDA;
+  }
+  return BSB_OK;
+}
+
 static unsigned long long* g_trace = nullptr;
 static int g_dbg = 0;
 void gemv_tc5_set_dbg(int m) { g_dbg = m; }
@@ -695,7 +748,7 @@ int launch_gemv_tc5(const bsb_weight* ws, int n_weights, const __half* x, __half
   int dev = 0;
   BSB_CUDA(cudaGetDevice(&dev));
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    BSB_CUDA(cudaFuncSetAttribute(gemv_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SmemLayout) + 128));
+    BSB_CUDA(cudaFuncSetAttribute(gemv_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SmemLayout) + 1024));
     attr_set[dev] = true;
   }
   TcParams& P = pl.P;
@@ -710,6 +763,7 @@ int launch_gemv_tc5(const bsb_weight* ws, int n_weights, const __half* x, __half
   P.dbg = g_dbg;
   for (int i = 0; i < n_weights; ++i) {
     P.y[i] = ys[i];
+    if (int rc = make_sign_map(ws[i], &P.sign_map[i])) return rc;
     if (ws[i].vt_absmax) {
       P.vt_absmax[i] = ws[i].vt_absmax;
     } else {
@@ -721,7 +775,7 @@ int launch_gemv_tc5(const bsb_weight* ws, int n_weights, const __half* x, __half
   zprep_tc5_kernel<<<dim3(P.n_chunks, pl.total_blocks), 256, 0, s>>>(P, x);
   if (int rc = check_launch("zprep_tc5_kernel")) return rc;
   profile_mark(s, false);
-  gemv_tc5_kernel<<<pl.total_items, kThreads, sizeof(SmemLayout) + 128, s>>>(P);
+  gemv_tc5_kernel<<<pl.total_items, kThreads, sizeof(SmemLayout) + 1024, s>>>(P);
   profile_mark(s, true);
   return check_launch("gemv_tc5_kernel");
 }
