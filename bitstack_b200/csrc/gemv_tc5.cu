@@ -369,7 +369,7 @@ __global__ void __launch_bounds__(kThreads) gemv_tc5_kernel(const __grid_constan
   if (warp == 0) TR_ADD(13, t_cta);
 
   if (warp == kWarpLoad) {
-    if (P.dbg == 1 || P.dbg == 3 || P.dbg == 4) goto teardown;   // experiments without the sign side also skip Z'
+    if (P.dbg == 1 || P.dbg == 3 || P.dbg == 4 || P.dbg == 6 || P.dbg == 7) goto teardown;   // experiments without the sign side also skip Z'
     // ---- loader: Z' slabs (bulk copy) and sign tiles (tiled TMA), each with its own ring ----
     if (lane == 0) {
       const CUtensorMap* map = &P.sign_map[wi];
@@ -404,7 +404,7 @@ __global__ void __launch_bounds__(kThreads) gemv_tc5_kernel(const __grid_constan
       for (int g = 0; g < total && ok; ++g) {
         const int j = g / nch, ci = g - j * nch;
         const int b = j & 1;
-        if (ci == 0 && j >= 2 && P.dbg != 4) {
+        if (ci == 0 && j >= 2 && P.dbg != 4 && P.dbg != 6 && P.dbg != 7) {
           TR_BEGIN(t0);
           if (!mbar_wait(&S.dempty[b], ((j >> 1) - 1) & 1)) { atomicExch(P.status, 6); ok = false; break; }
           TR_ADD(7, t0);
@@ -412,17 +412,17 @@ __global__ void __launch_bounds__(kThreads) gemv_tc5_kernel(const __grid_constan
         }
         const int slot = g % kNZ, n = g / kNZ;
         TR_BEGIN(t1);
-        if (P.dbg != 3 && !mbar_wait(&S.zfull[slot], n & 1)) { atomicExch(P.status, 2); ok = false; break; }
+        if (P.dbg != 3 && P.dbg != 4 && P.dbg != 6 && P.dbg != 7 && !mbar_wait(&S.zfull[slot], n & 1)) { atomicExch(P.status, 2); ok = false; break; }
         TR_ADD(5, t1);
         const uint32_t zaddr = smem_u32(S.zs[slot]);
 #pragma unroll 1
         for (int q = 0; q < 2; ++q, ++it) {
           const int a = it % kNA, na = it / kNA;
           TR_BEGIN(t2);
-          if (P.dbg != 1 && P.dbg != 3 && P.dbg != 4 && !mbar_wait(&S.afull[a], na & 1)) { atomicExch(P.status, 3); ok = false; break; }
+          if (P.dbg != 1 && P.dbg != 3 && P.dbg != 4 && P.dbg != 6 && P.dbg != 7 && !mbar_wait(&S.afull[a], na & 1)) { atomicExch(P.status, 3); ok = false; break; }
           TR_ADD(6, t2);
           TR_BEGIN(t3);
-          tc_fence_after();
+          if (P.dbg != 6) tc_fence_after();
           // one commit per eight MMAs: the issuing thread, not the tensor pipe, is the scarce resource
           uint64_t bdesc = make_smem_desc(zaddr + (uint32_t)(q * 8) * 1024u, 128, 256);
           const uint32_t acol = tbase + colA + a * 64;
@@ -431,7 +431,7 @@ __global__ void __launch_bounds__(kThreads) gemv_tc5_kernel(const __grid_constan
             mma_ts_f8(tbase + b * 32, acol + ww * 8, bdesc, idesc, (ci > 0 || q > 0 || ww > 0) ? 1u : 0u);
             bdesc += 1024u >> 4;   // next 1 KB operand tile (address field counts 16-byte units)
           }
-          mma_commit(&S.aempty[a]);
+          if (P.dbg != 7) mma_commit(&S.aempty[a]);
           TR_ADD(8, t3);
         }
         if (!ok) break;
@@ -442,7 +442,7 @@ __global__ void __launch_bounds__(kThreads) gemv_tc5_kernel(const __grid_constan
     }
   } else if (warp < kWarpMma) {
     // ---- producers: one sign row per thread; group s expands stage s of every chunk -------
-    if (P.dbg == 1 || P.dbg == 3 || P.dbg == 4) goto teardown;
+    if (P.dbg == 1 || P.dbg == 3 || P.dbg == 4 || P.dbg == 6 || P.dbg == 7) goto teardown;
     const int set = warp >> 2;
     const int rtid = tid & (kTileRows - 1);
     const uint32_t lane_base = tbase + ((uint32_t)((warp & 3) * 32) << 16);
@@ -502,7 +502,7 @@ __global__ void __launch_bounds__(kThreads) gemv_tc5_kernel(const __grid_constan
     }
     TR_ADD(0, t_prod);
   } else {
-    if (P.dbg == 2 || P.dbg == 4 || P.dbg == 5) goto teardown;
+    if (P.dbg == 2 || P.dbg == 4 || P.dbg == 5 || P.dbg == 6 || P.dbg == 7) goto teardown;
     // ---- epilogue warps: y[m] += sum_r U_j[m,r] ((D_hi + D_lo)[m,r] / s_r - K_r) per block ----
     const int quarter = warp & 3;                     // tensor-memory lanes this warp may read
     const int rtid = quarter * 32 + lane;
