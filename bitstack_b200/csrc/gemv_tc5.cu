@@ -33,9 +33,7 @@ namespace {
 constexpr int kChunkCols = 512;                 // columns per Z' slab / per 64 B of a sign row
 constexpr int kChunkBytes = kChunkCols * 32;    // 16 words x 1 KB operand tile
 constexpr int kTileRows = 128;
-constexpr int kSets = 2;                        // producer warp groups; set s expands stage s of every chunk
-constexpr int kThreads = (kSets * 4 + 2 + 4) * 32; // producers, MMA warp, loader warp, 4 epilogue warps
-constexpr int kNA = 3;                          // A-operand ring stages (64 tensor-memory columns = 8 MMAs each)
+constexpr int kThreads = 512;                    // 8 producer warps, 2 MMA issuers, loader, (idle), 4 epilogue warps
 #ifndef BSB_NZ
 #define BSB_NZ 3
 #endif
@@ -45,7 +43,7 @@ constexpr int kNA = 3;                          // A-operand ring stages (64 ten
 constexpr int kNZ = BSB_NZ;                          // Z' slabs resident in shared memory
 constexpr int kNP = BSB_NP;                          // sign tiles (128 rows x 64 B, TMA) resident in shared memory
 constexpr int kSignTileBytes = kTileRows * 64;
-constexpr int kTmemCols = 256;                  // 2 x 32 (D, double buffered) + kNA*64 (A ring)
+constexpr int kTmemCols = 256;                  // 4 x 32 (D: 2 issuers x 2 buffers) + 4 x 32 (A: 2 issuers x 2 stages)
 constexpr int kMaxGroup = 4;
 constexpr float kTargetMax = 320.f;
 constexpr float kMinD = 0.75f;
@@ -152,6 +150,13 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr) : "memory");
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr) : "memory");
+}
 // D[tmem] (+)= A[tmem] . B[smem]^T, e4m3 x e4m3 -> f32
 __device__ __forceinline__ void mma_ts_f8(uint32_t d, uint32_t a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
@@ -195,6 +200,17 @@ __device__ __forceinline__ float e4m3_to_float(uint8_t v) {
 template <int I>
 __device__ __forceinline__ uint32_t expand(uint32_t word) {
   return (word & (0x01010101u << I)) | (class_byte(I) * 0x01010101u);
+}
+// (word & mask_I) | c  in one LOP3: the mask is an immediate, the OR-constant a register
+template <int I>
+__device__ __forceinline__ uint32_t expand_c(uint32_t word, uint32_t c) {
+  uint32_t out;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(out) : "r"(word), "n"(0x01010101u << I), "r"(c));
+  return out;
+}
+__device__ __forceinline__ void expand_word_c(uint32_t word, const uint32_t (&c)[8], uint32_t* r) {
+  r[0] = expand_c<0>(word, c[0]); r[1] = expand_c<1>(word, c[1]); r[2] = expand_c<2>(word, c[2]); r[3] = expand_c<3>(word, c[3]);
+  r[4] = expand_c<4>(word, c[4]); r[5] = expand_c<5>(word, c[5]); r[6] = expand_c<6>(word, c[6]); r[7] = expand_c<7>(word, c[7]);
 }
 __device__ __forceinline__ void expand_word(uint32_t word, uint32_t* r) {
   r[0] = expand<0>(word); r[1] = expand<1>(word); r[2] = expand<2>(word); r[3] = expand<3>(word);
@@ -301,25 +317,31 @@ __global__ void __launch_bounds__(256) zprep_tc5_kernel(const __grid_constant__ 
 #define TR_ADD(slot, var) do { if (tr) S.trace[slot] += (unsigned long long)(clock64() - var); } while (0)
 
 // ------------------------------------------------------------------ main kernel
-// One CTA = one 128-row tile x one column split of one weight, ALL active blocks:
-// the block loop runs inside the CTA so that set-up, pipeline fill and the final
-// reduction are paid once, and the fp32 output of a row is accumulated over blocks in
-// a register of its epilogue thread.  The accumulator D is double buffered in tensor
-// memory: while the epilogue warps read block j, the MMAs of block j+1 run.
+// One CTA = one 128-row tile x one column split of one weight, ALL active blocks: set-up,
+// pipeline fill and the final reduction are paid once and the fp32 output of a row is
+// accumulated over blocks in a register of its epilogue thread.
+//
+// A single thread can only issue a tcgen05.mma every ~28 ns (and a commit costs it ~60 ns)
+// while the tensor pipe itself accepts several such streams side by side, so the CTA runs TWO
+// independent operand pipelines: producer group e (4 warps) expands the e-th 32 bytes of every
+// 64-byte sign row and feeds MMA issuer e, which accumulates into its own D (the epilogue adds
+// the two).  Every D is double buffered across blocks.  Tensor-memory columns:
+//   D(e, b) = e*64 + b*32           (4 x 32)
+//   A(e, s) = 128 + e*64 + s*32     (2 issuers x 2 stages x 4 MMAs)
 struct __align__(1024) SmemLayout {
   uint8_t zs[kNZ][kChunkBytes];         // Z' operand slabs (bulk-copied)
   uint8_t sg[kNP][kSignTileBytes];      // sign tiles: row r at r*64, 16-byte piece p at ((p ^ ((r>>1)&3)) * 16)
-  uint64_t afull[kNA], aempty[kNA], zfull[kNZ], zempty[kNZ], sfull[kNP], sempty[kNP], dfull[2], dempty[2];
+  uint64_t afull[2][2], aempty[2][2], zfull[kNZ], zempty[kNZ], sfull[kNP], sempty[kNP], dfull[2][2], dempty[2];
   unsigned long long trace[16];
   uint32_t tmem_base;
   int last;
 };
 
-constexpr int kWarpMma = kSets * 4;
-constexpr int kWarpLoad = kSets * 4 + 1;
-constexpr int kWarpEpi = kSets * 4 + 2;   // four epilogue warps follow
+constexpr int kWarpMma = 8;     // warps 8, 9: MMA issuers 0, 1
+constexpr int kWarpLoad = 10;   // tensor-memory allocation, TMA / bulk loads
+constexpr int kWarpEpi = 12;    // warps 12-15: epilogue (tensor-memory lane quarters 0-3)
 
-__global__ void __launch_bounds__(kThreads) gemv_tc5_kernel(const __grid_constant__ TcParams P) {
+__global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_constant__ TcParams P) {
   extern __shared__ uint8_t smem_raw[];
   SmemLayout& S = *reinterpret_cast<SmemLayout*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
 
@@ -330,7 +352,7 @@ __global__ void __launch_bounds__(kThreads) gemv_tc5_kernel(const __grid_constan
   const int item = blockIdx.x - P.item_base[wi];
   const int split = item % nsplit;
   const int rt = item / nsplit;
-  const int N = w.in_features, M = w.out_features, NB = w.blocks;
+  const int M = w.out_features, NB = w.blocks;
   const int c_lo = split * P.chunks_per_item[wi];
   const int c_hi = min(P.n_chunks, c_lo + P.chunks_per_item[wi]);
   const int nch = c_hi - c_lo;
@@ -341,9 +363,9 @@ __global__ void __launch_bounds__(kThreads) gemv_tc5_kernel(const __grid_constan
   const int j_rot = rt % NB;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  // trace slots: 0-3 producer (total, fifo wait, ring wait, expand+store), 4-8 MMA (total, Z' wait,
-  // operand wait, accumulator wait, issue), 9-10 epilogue (accumulator wait, total), 11 loader wait,
-  // 12 CTA total, 13 set-up
+  // trace slots: 0-3 producer group 0 (total, tile wait, ring wait, expand+store), 4-8 issuer 0 (total,
+  // Z' wait, operand wait, accumulator wait, issue), 9-10 epilogue (accumulator wait, total), 11 loader
+  // wait, 12 CTA total, 13 set-up
   unsigned long long* tr = (P.trace && lane == 0 && (warp == 0 || warp == kWarpMma || warp == kWarpLoad || warp == kWarpEpi))
                                ? P.trace + (int64_t)blockIdx.x * 16 : nullptr;
   TR_BEGIN(t_cta);
@@ -355,28 +377,32 @@ __global__ void __launch_bounds__(kThreads) gemv_tc5_kernel(const __grid_constan
   }
   if (tid < 16) S.trace[tid] = 0;
   if (tid == 0) {
-    for (int i = 0; i < kNA; ++i) { mbar_init(&S.afull[i], kTileRows); mbar_init(&S.aempty[i], 1); }
-    for (int i = 0; i < kNZ; ++i) { mbar_init(&S.zfull[i], 1); mbar_init(&S.zempty[i], 1); }
-    for (int i = 0; i < kNP; ++i) { mbar_init(&S.sfull[i], 1); mbar_init(&S.sempty[i], kSets * kTileRows); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&S.dfull[i], 1); mbar_init(&S.dempty[i], kTileRows); }
+    for (int e = 0; e < 2; ++e)
+      for (int i = 0; i < 2; ++i) {
+        mbar_init(&S.afull[e][i], kTileRows);
+        mbar_init(&S.aempty[e][i], 1);
+        mbar_init(&S.dfull[e][i], 1);
+      }
+    for (int i = 0; i < kNZ; ++i) { mbar_init(&S.zfull[i], 1); mbar_init(&S.zempty[i], 2); }
+    for (int i = 0; i < kNP; ++i) { mbar_init(&S.sfull[i], 1); mbar_init(&S.sempty[i], 2 * kTileRows); }
+    for (int i = 0; i < 2; ++i) mbar_init(&S.dempty[i], kTileRows);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tbase = S.tmem_base;
-  const uint32_t colA = 64;   // D buffers occupy columns [0,32) and [32,64)
+  const uint32_t colA = 128;
   if (warp == 0) TR_ADD(13, t_cta);
 
   if (warp == kWarpLoad) {
-    if (P.dbg == 1 || P.dbg == 3 || P.dbg == 4 || P.dbg == 6 || P.dbg == 7) goto teardown;   // experiments without the sign side also skip Z'
     // ---- loader: Z' slabs (bulk copy) and sign tiles (tiled TMA), each with its own ring ----
     if (lane == 0) {
       const CUtensorMap* map = &P.sign_map[wi];
       for (int g = 0; g < total; ++g) {
         const int js = g / nch, ci = g - js * nch;
         const int j = (js + j_rot) % NB;
-        {
+        if (P.dbg != 1) {
           const int slot = g % kNP, n = g / kNP;
           TR_BEGIN(t0);
           if (n >= 1 && !mbar_wait(&S.sempty[slot], (n - 1) & 1)) { atomicExch(P.status, 7); break; }
@@ -384,7 +410,7 @@ __global__ void __launch_bounds__(kThreads) gemv_tc5_kernel(const __grid_constan
           mbar_expect_tx(&S.sfull[slot], kSignTileBytes);
           tma_load_3d(S.sg[slot], map, (c_lo + ci) * (kChunkCols / 8), rt * kTileRows, j, &S.sfull[slot]);
         }
-        if (P.dbg != 2 && P.dbg != 5) {
+        if (P.dbg != 2) {
           const int slot = g % kNZ, n = g / kNZ;
           if (n >= 1 && !mbar_wait(&S.zempty[slot], (n - 1) & 1)) { atomicExch(P.status, 1); break; }
           const uint8_t* zsrc = P.zops + ((int64_t)(jb0 + j) * P.n_chunks + c_lo + ci) * kChunkBytes;
@@ -393,117 +419,118 @@ __global__ void __launch_bounds__(kThreads) gemv_tc5_kernel(const __grid_constan
         }
       }
     }
-  } else if (warp == kWarpMma) {
-    if (P.dbg == 2 || P.dbg == 5) goto teardown;
-    // ---- MMA issuer ------------------------------------------------------------------
-    if (lane == 0) {
+  } else if (warp == kWarpMma || warp == kWarpMma + 1) {
+    // ---- MMA issuer e: words 8e .. 8e+7 of every chunk, accumulator D(e, block parity) --------
+    if (lane == 0 && P.dbg != 2) {
+      const int e = warp - kWarpMma;
+      if (e != 0) tr = nullptr;
       const uint32_t idesc = make_idesc_f8(128, 32);
       int it = 0;
       bool ok = true;
       TR_BEGIN(t_mma);
       for (int g = 0; g < total && ok; ++g) {
-        const int j = g / nch, ci = g - j * nch;
-        const int b = j & 1;
-        if (ci == 0 && j >= 2 && P.dbg != 4 && P.dbg != 6 && P.dbg != 7) {
+        const int js = g / nch, ci = g - js * nch;
+        const int b = js & 1;
+        if (ci == 0 && js >= 2) {
           TR_BEGIN(t0);
-          if (!mbar_wait(&S.dempty[b], ((j >> 1) - 1) & 1)) { atomicExch(P.status, 6); ok = false; break; }
+          if (!mbar_wait(&S.dempty[b], ((js >> 1) - 1) & 1)) { atomicExch(P.status, 6); ok = false; break; }
           TR_ADD(7, t0);
           tc_fence_after();
         }
-        const int slot = g % kNZ, n = g / kNZ;
+        const int zslot = g % kNZ;
         TR_BEGIN(t1);
-        if (P.dbg != 3 && P.dbg != 4 && P.dbg != 6 && P.dbg != 7 && !mbar_wait(&S.zfull[slot], n & 1)) { atomicExch(P.status, 2); ok = false; break; }
+        if (!mbar_wait(&S.zfull[zslot], (g / kNZ) & 1)) { atomicExch(P.status, 2); ok = false; break; }
         TR_ADD(5, t1);
-        const uint32_t zaddr = smem_u32(S.zs[slot]);
+        const uint32_t zaddr = smem_u32(S.zs[zslot]) + (uint32_t)e * 8u * 1024u;
+        const uint32_t dcol = tbase + e * 64 + b * 32;
 #pragma unroll 1
-        for (int q = 0; q < 2; ++q, ++it) {
-          const int a = it % kNA, na = it / kNA;
+        for (int pp = 0; pp < 2; ++pp, ++it) {
+          const int slot = it & 1;
           TR_BEGIN(t2);
-          if (P.dbg != 1 && P.dbg != 3 && P.dbg != 4 && P.dbg != 6 && P.dbg != 7 && !mbar_wait(&S.afull[a], na & 1)) { atomicExch(P.status, 3); ok = false; break; }
+          if (P.dbg != 1 && !mbar_wait(&S.afull[e][slot], (it >> 1) & 1)) { atomicExch(P.status, 3); ok = false; break; }
           TR_ADD(6, t2);
           TR_BEGIN(t3);
-          if (P.dbg != 6) tc_fence_after();
-          // one commit per eight MMAs: the issuing thread, not the tensor pipe, is the scarce resource
-          uint64_t bdesc = make_smem_desc(zaddr + (uint32_t)(q * 8) * 1024u, 128, 256);
-          const uint32_t acol = tbase + colA + a * 64;
+          tc_fence_after();
+          uint64_t bdesc = make_smem_desc(zaddr + (uint32_t)(pp * 4) * 1024u, 128, 256);
+          const uint32_t acol = tbase + colA + e * 64 + slot * 32;
 #pragma unroll
-          for (int ww = 0; ww < 8; ++ww) {
-            mma_ts_f8(tbase + b * 32, acol + ww * 8, bdesc, idesc, (ci > 0 || q > 0 || ww > 0) ? 1u : 0u);
+          for (int ww = 0; ww < 4; ++ww) {
+            mma_ts_f8(dcol, acol + ww * 8, bdesc, idesc, (ci > 0 || pp > 0 || ww > 0) ? 1u : 0u);
             bdesc += 1024u >> 4;   // next 1 KB operand tile (address field counts 16-byte units)
           }
-          if (P.dbg != 7) mma_commit(&S.aempty[a]);
+          mma_commit(&S.aempty[e][slot]);
           TR_ADD(8, t3);
         }
         if (!ok) break;
-        mma_commit(&S.zempty[slot]);
-        if (ci == nch - 1) mma_commit(&S.dfull[b]);
+        mma_commit(&S.zempty[zslot]);
+        if (ci == nch - 1) mma_commit(&S.dfull[e][b]);
       }
       TR_ADD(4, t_mma);
     }
   } else if (warp < kWarpMma) {
-    // ---- producers: one sign row per thread; group s expands stage s of every chunk -------
-    if (P.dbg == 1 || P.dbg == 3 || P.dbg == 4 || P.dbg == 6 || P.dbg == 7) goto teardown;
-    const int set = warp >> 2;
-    const int rtid = tid & (kTileRows - 1);
-    const uint32_t lane_base = tbase + ((uint32_t)((warp & 3) * 32) << 16);
-    // this thread's 32 bytes (256 columns) of every 64-byte tile row, after the 64-byte swizzle
-    const int sw = (rtid >> 1) & 3;
-    const int off0 = rtid * 64 + (((set * 2) ^ sw) << 4), off1 = rtid * 64 + (((set * 2 + 1) ^ sw) << 4);
-    bool ok = true;
-    int prev_a = -1;
-    TR_BEGIN(t_prod);
+    // ---- producer group e: one sign row per thread, bytes 32e .. 32e+31 of every tile row ------
+    if (P.dbg != 1) {
+      const int e = warp >> 2;
+      if (e != 0) tr = nullptr;
+      const int rtid = tid & (kTileRows - 1);
+      const uint32_t lane_base = tbase + ((uint32_t)((warp & 3) * 32) << 16) + colA + e * 64;
+      const int sw = (rtid >> 1) & 3;   // 64-byte swizzle of the TMA tile
+      const int off0 = rtid * 64 + (((e * 2) ^ sw) << 4), off1 = rtid * 64 + (((e * 2 + 1) ^ sw) << 4);
+      // OR-constants of the eight bit classes, held in registers so that one LOP3 expands four signs
+      uint32_t cc[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) asm volatile("mov.u32 %0, %1;" : "=r"(cc[i]) : "r"(class_byte(i) * 0x01010101u));
+      bool ok = true;
+      int prev_slot = -1;
+      TR_BEGIN(t_prod);
 #pragma unroll 1
-    for (int g = 0; g < total && ok; ++g) {
-      const int slot = g % kNP;
-      TR_BEGIN(t0);
-      const bool landed = __all_sync(0xFFFFFFFFu, mbar_wait(&S.sfull[slot], (g / kNP) & 1) ? 1 : 0);
-      TR_ADD(1, t0);
-      if (!landed) { atomicExch(P.status, 8); ok = false; break; }
-      const uint4 v0 = *reinterpret_cast<const uint4*>(&S.sg[slot][off0]);
-      const uint4 v1 = *reinterpret_cast<const uint4*>(&S.sg[slot][off1]);
-      mbar_arrive(&S.sempty[slot]);      // the tile slot may be refilled once all 256 readers have their words
-      if (P.dbg == 5) continue;          // experiment: stream the tiles, do nothing with them
-      const int it = g * 2 + set;        // stage index: two stages of eight MMAs per chunk
-      const int a = it % kNA, na = it / kNA;
-      if (na >= 1 && P.dbg != 2) {
-        // warp-uniform decision: the tensor-memory stores below are warp-wide instructions
-        TR_BEGIN(t1);
-        const bool got = __all_sync(0xFFFFFFFFu, mbar_wait(&S.aempty[a], (na - 1) & 1) ? 1 : 0);
-        TR_ADD(2, t1);
-        if (!got) { atomicExch(P.status, 4); ok = false; break; }
-        tc_fence_after();
+      for (int g = 0; g < total && ok; ++g) {
+        const int slot_s = g % kNP;
+        TR_BEGIN(t0);
+        const bool landed = __all_sync(0xFFFFFFFFu, mbar_wait(&S.sfull[slot_s], (g / kNP) & 1) ? 1 : 0);
+        TR_ADD(1, t0);
+        if (!landed) { atomicExch(P.status, 8); ok = false; break; }
+        const uint4 v0 = *reinterpret_cast<const uint4*>(&S.sg[slot_s][off0]);
+        const uint4 v1 = *reinterpret_cast<const uint4*>(&S.sg[slot_s][off1]);
+        mbar_arrive(&S.sempty[slot_s]);   // the tile slot may be refilled once all 256 readers have their words
+#pragma unroll
+        for (int pp = 0; pp < 2; ++pp) {
+          const uint4 v = pp ? v1 : v0;
+          const int it = g * 2 + pp, slot = it & 1;
+          TR_BEGIN(t2);
+          uint32_t r[32];
+          const uint32_t wd[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+          for (int q = 0; q < 4; ++q) expand_word_c(wd[q], cc, r + q * 8);
+          TR_ADD(3, t2);
+          // hand over the previous stage only now: its stores completed behind the expansion above
+          if (prev_slot >= 0) {
+            tmem_wait_st();
+            tc_fence_before();
+            if (P.dbg != 2) mbar_arrive(&S.afull[e][prev_slot]);
+          }
+          if (it >= 2 && P.dbg != 2) {
+            TR_BEGIN(t1);
+            const bool got = __all_sync(0xFFFFFFFFu, mbar_wait(&S.aempty[e][slot], ((it >> 1) - 1) & 1) ? 1 : 0);
+            TR_ADD(2, t1);
+            if (!got) { atomicExch(P.status, 4); ok = false; break; }
+            tc_fence_after();
+          }
+          tmem_st32(lane_base + slot * 32, r);
+          prev_slot = slot;
+        }
       }
-      TR_BEGIN(t2);
-      uint32_t r[32];
-      expand_word(v0.x, r);
-      expand_word(v0.y, r + 8);
-      expand_word(v0.z, r + 16);
-      expand_word(v0.w, r + 24);
-      // hand over the PREVIOUS stage only now: its tensor-memory stores completed behind the
-      // expansion above, so the wait costs nothing
-      if (prev_a >= 0) {
+      if (prev_slot >= 0) {
         tmem_wait_st();
         tc_fence_before();
-        if (P.dbg != 2) mbar_arrive(&S.afull[prev_a]);
+        if (P.dbg != 2 && ok) mbar_arrive(&S.afull[e][prev_slot]);
       }
-      tmem_st32(lane_base + colA + a * 64, r);
-      expand_word(v1.x, r);
-      expand_word(v1.y, r + 8);
-      expand_word(v1.z, r + 16);
-      expand_word(v1.w, r + 24);
-      tmem_st32(lane_base + colA + a * 64 + 32, r);
-      prev_a = a;
-      TR_ADD(3, t2);
+      TR_ADD(0, t_prod);
     }
-    if (prev_a >= 0) {
-      tmem_wait_st();
-      tc_fence_before();
-      if (P.dbg != 2) mbar_arrive(&S.afull[prev_a]);
-    }
-    TR_ADD(0, t_prod);
-  } else {
-    if (P.dbg == 2 || P.dbg == 4 || P.dbg == 5 || P.dbg == 6 || P.dbg == 7) goto teardown;
-    // ---- epilogue warps: y[m] += sum_r U_j[m,r] ((D_hi + D_lo)[m,r] / s_r - K_r) per block ----
+  } else if (warp >= kWarpEpi) {
+    // ---- epilogue warps: y[m] += sum_r U_j[m,r] (T[m,r] / s_r - K_r) per block, T = sum of the
+    //      hi and lo pieces of both issuers' accumulators ------------------------------------
+    if (P.dbg == 0) {
     const int quarter = warp & 3;                     // tensor-memory lanes this warp may read
     const int rtid = quarter * 32 + lane;
     const int row = min(rt * kTileRows + rtid, M - 1);
@@ -526,25 +553,41 @@ __global__ void __launch_bounds__(kThreads) gemv_tc5_kernel(const __grid_constan
         for (int c = 0; c < nch; ++c) k_mine += kc[c * 16];
       }
       TR_BEGIN(t0);
-      const int mine = mbar_wait(&S.dfull[b], (js >> 1) & 1) ? 1 : 0;
+      const int mine = (mbar_wait(&S.dfull[0][b], (js >> 1) & 1) && mbar_wait(&S.dfull[1][b], (js >> 1) & 1)) ? 1 : 0;
       TR_ADD(9, t0);
       if (!__all_sync(0xFFFFFFFFu, mine)) { if (lane == 0) atomicExch(P.status, 5); ok = false; break; }
       tc_fence_after();
-      uint32_t d[32];
-      tmem_ld32(lane_base + b * 32, d);
-      tmem_wait_ld();
+      // T[r] = hi + lo pieces of both issuers: four 16-column loads, summed as they arrive
+      float T[16];
+      {
+        uint32_t d[16];
+        tmem_ld16(lane_base + b * 32, d);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) T[i] = __uint_as_float(d[i]);
+        tmem_ld16(lane_base + b * 32 + 16, d);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) T[i] += __uint_as_float(d[i]);
+        tmem_ld16(lane_base + 64 + b * 32, d);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) T[i] += __uint_as_float(d[i]);
+        tmem_ld16(lane_base + 64 + b * 32 + 16, d);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) T[i] += __uint_as_float(d[i]);
+      }
       tc_fence_before();
       mbar_arrive(&S.dempty[b]);
       const uint32_t uw[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
 #pragma unroll
       for (int rr = 0; rr < 8; ++rr) {
         const __half2 h2 = *reinterpret_cast<const __half2*>(&uw[rr]);
-        const float t0 = __uint_as_float(d[2 * rr]) + __uint_as_float(d[16 + 2 * rr]);
-        const float t1 = __uint_as_float(d[2 * rr + 1]) + __uint_as_float(d[16 + 2 * rr + 1]);
         const float i0 = __shfl_sync(0xFFFFFFFFu, inv_mine, 2 * rr), i1 = __shfl_sync(0xFFFFFFFFu, inv_mine, 2 * rr + 1);
         const float k0 = __shfl_sync(0xFFFFFFFFu, k_mine, 2 * rr), k1 = __shfl_sync(0xFFFFFFFFu, k_mine, 2 * rr + 1);
-        yacc = fmaf(__low2float(h2), t0 * i0 - k0, yacc);
-        yacc = fmaf(__high2float(h2), t1 * i1 - k1, yacc);
+        yacc = fmaf(__low2float(h2), T[2 * rr] * i0 - k0, yacc);
+        yacc = fmaf(__high2float(h2), T[2 * rr + 1] * i1 - k1, yacc);
       }
     }
     TR_ADD(10, t_epi);
@@ -560,9 +603,9 @@ __global__ void __launch_bounds__(kThreads) gemv_tc5_kernel(const __grid_constan
       part[rtid] = ok ? yacc : __int_as_float(0x7FC00000);
       __threadfence();
     }
+    }
   }
 
-teardown:
   // ---- tear-down: tensor memory is released only after every role is done ---------------
   tc_fence_before();
   __syncthreads();
