@@ -45,6 +45,8 @@ SIGNATURES = {
     "bsb_linear_forward": (C.c_int, [_WP, _P, _I64, _I64, _P, _I64, _P, _I64, C.c_int, _P]),
     "bsb_linear_forward_grouped": (C.c_int, [_WP, _I32, _P, _I64, _I64, C.POINTER(_P), C.POINTER(_I64), _P, _I64, C.c_int, _P]),
     "bsb_linear_grouped_workspace_bytes": (_I64, [_WP, _I32, _I64, C.c_int]),
+    "bsb_noalloc_scratch_bytes": (_I64, []),
+    "bsb_linear_forward_noalloc": (C.c_int, [_WP, _P, _I64, _I64, _P, _I64, _P]),
     "bsb_debug_gemv_status": (C.c_int, [_WP, _I32, _P, C.POINTER(C.c_int32)]),
     "bsb_debug_launch_count": (_I64, []),
     "bsb_debug_set_trace": (C.c_int, [_P]),

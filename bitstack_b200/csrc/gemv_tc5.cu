@@ -824,3 +824,45 @@ int launch_gemv_tc5(const bsb_weight* ws, int n_weights, const __half* x, __half
 }
 
 }  // namespace bsb
+
+// ------------------------------------------------------------------ allocation-free entry point
+// Scratch for bsb_linear_forward_noalloc: lives in the library image, so every GPU that loads
+// the library holds these bytes until the process exits.
+static constexpr int64_t kNoAllocScratchBytes = 16ll << 20;
+static __device__ __align__(256) uint8_t g_noalloc_scratch[kNoAllocScratchBytes];
+
+extern "C" int64_t bsb_noalloc_scratch_bytes(void) { return kNoAllocScratchBytes; }
+
+extern "C" int bsb_linear_forward_noalloc(const bsb_weight* w, const uint16_t* x, int64_t rows, int64_t x_stride,
+                                          uint16_t* y, int64_t y_stride, void* stream) {
+  using namespace bsb;
+  BSB_CHECK_ARG(w != nullptr && x != nullptr && y != nullptr, "NULL argument");
+  BSB_CHECK_ARG(rows >= 1, "at least one input row is needed");
+  BSB_CHECK_ARG(w->blocks >= 1 && gemv_tc5_supported(*w),
+                "noalloc forward: needs k == 16, in_features %% 128 == 0, 16-byte aligned tensors, >= 1 active block");
+  BSB_CHECK_ARG(x_stride >= w->in_features && y_stride >= w->out_features, "row stride smaller than the row");
+  const int64_t need = gemv_tc5_workspace_bytes(w, 1);
+  if (need > kNoAllocScratchBytes) {
+    set_error("noalloc forward: this weight needs %lld bytes of scratch, the built-in area holds %lld "
+              "(use bsb_linear_forward with a caller-provided workspace)", (long long)need, (long long)kNoAllocScratchBytes);
+    return BSB_ELIMIT;
+  }
+  // device address of the built-in scratch: looked up once per device, with that device current
+  static void* scratch_ptr[64] = {nullptr};
+  int dev = 0;
+  BSB_CUDA(cudaGetDevice(&dev));
+  BSB_CHECK_ARG(dev >= 0 && dev < 64, "device index %d out of range", dev);
+  if (scratch_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    BSB_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+    scratch_ptr[dev] = p;
+  }
+  for (int64_t r = 0; r < rows; ++r) {
+    __half* yr = reinterpret_cast<__half*>(y) + r * y_stride;
+    if (int rc = launch_gemv_tc5(w, 1, reinterpret_cast<const __half*>(x) + r * x_stride, &yr, scratch_ptr[dev],
+                                 kNoAllocScratchBytes, (cudaStream_t)stream))
+      return rc;
+  }
+  return BSB_OK;
+}
+

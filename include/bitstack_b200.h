@@ -120,6 +120,29 @@ int bsb_linear_forward_grouped(const bsb_weight* ws, int32_t n_weights, const ui
 /* Scratch bytes bsb_linear_forward_grouped needs. */
 int64_t bsb_linear_grouped_workspace_bytes(const bsb_weight* ws, int32_t n_weights, int64_t rows, int algo);
 
+/* Forward for callers that may not allocate device memory.  It has no counterpart in the
+ * reference.  Some hosts hand a plug-in a fixed set of buffers and forbid any device
+ * allocation once they are running -- an inference server with a frozen memory plan, a
+ * framework whose own pool already owns the whole GPU, a latency-critical loop that must not
+ * take the driver's allocator lock (cudaMalloc stalls the device) -- and such a host has no
+ * workspace to lend either.  This entry point therefore brings its scratch with it: a
+ * 16 MiB array inside the library image (bsb_noalloc_scratch_bytes()), which every GPU that
+ * loads the library keeps until the process ends.  Same math and kernel as the single-row
+ * decode path of bsb_linear_forward (rows are processed one after another); it calls no
+ * cudaMalloc, cudaFree or allocating library routine.
+ *   - Weights whose scratch need exceeds the built-in area (more than 16 MiB: about 32 active
+ *     blocks x 16384 input features) are rejected with BSB_ELIMIT; so are shapes the decode
+ *     kernel does not take (k != 16, in_features % 128 != 0, unaligned tensors) with BSB_EINVAL.
+ *   - The first call on each device looks up the device address of the built-in area (with
+ *     that device current); make that first call before starting any stream capture.
+ *   - All calls share the one area, which keeps whatever the last call left there; the kernels
+ *     re-initialise the counters and the status word they depend on at the start of every call.
+ *     Two calls that overlap on the GPU (different streams, or different host threads without
+ *     ordering) would overwrite each other's scratch: serialise them. */
+int64_t bsb_noalloc_scratch_bytes(void);
+int bsb_linear_forward_noalloc(const bsb_weight* w, const uint16_t* x, int64_t rows, int64_t x_stride,
+                               uint16_t* y, int64_t y_stride, void* stream);
+
 /* Debug aid (no reference counterpart): after the work queued by a tcgen05 decode
  * call on `workspace` has finished, copies that call's device status word to
  * *status_out (host): 0 = every hand-off completed, otherwise the code of the
