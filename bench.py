@@ -216,6 +216,8 @@ def run_ours(args):
         torch.distributed.init_process_group("nccl", device_id=dev)
         group = torch.distributed.group.WORLD
     lib = _lib.load()
+    if os.environ.get("BSB_PDL") == "0":
+        lib.bsb_debug_set_mode(100)
     shape, counts, batch, prompt = workload_spec(args)
     max_len = prompt + args.steps + args.warmup + 16
     max_len = (max_len + 127) // 128 * 128

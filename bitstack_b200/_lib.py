@@ -45,6 +45,9 @@ SIGNATURES = {
     "bsb_linear_forward": (C.c_int, [_WP, _P, _I64, _I64, _P, _I64, _P, _I64, C.c_int, _P]),
     "bsb_linear_forward_grouped": (C.c_int, [_WP, _I32, _P, _I64, _I64, C.POINTER(_P), C.POINTER(_I64), _P, _I64, C.c_int, _P]),
     "bsb_linear_grouped_workspace_bytes": (_I64, [_WP, _I32, _I64, C.c_int]),
+    "bsb_add_rmsnorm": (C.c_int, [_P, _P, _P, C.c_float, _P, _I64, _I32, _P]),
+    "bsb_rope_cache": (C.c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _I32, _I32, _I32, _I32, _I32, _P]),
+    "bsb_silu_mul": (C.c_int, [_P, _P, _P, _I64, _P]),
     "bsb_noalloc_scratch_bytes": (_I64, []),
     "bsb_linear_forward_noalloc": (C.c_int, [_WP, _P, _I64, _I64, _P, _I64, _P]),
     "bsb_debug_gemv_status": (C.c_int, [_WP, _I32, _P, C.POINTER(C.c_int32)]),

@@ -278,6 +278,10 @@ int bsb_debug_set_trace(void* device_buffer) {
 }
 
 int bsb_debug_set_mode(int32_t mode) {
+  if (mode >= 100) {   // 100 / 101: programmatic dependent launch off / on
+    gemv_tc5_set_pdl(mode - 100);
+    return BSB_OK;
+  }
   gemv_tc5_set_dbg(mode);
   return BSB_OK;
 }

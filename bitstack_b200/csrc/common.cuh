@@ -81,6 +81,7 @@ bool gemv_tc5_supported(const bsb_weight& w);
 int64_t gemv_tc5_workspace_bytes(const bsb_weight* ws, int n_weights);
 void gemv_tc5_set_trace(unsigned long long* device_buffer);
 void gemv_tc5_set_dbg(int mode);
+void gemv_tc5_set_pdl(int on);
 int64_t gemv_tc5_status_offset(const bsb_weight* ws, int n_weights);
 int launch_gemv_tc5(const bsb_weight* ws, int n_weights, const __half* x, __half* const* ys,
                     void* workspace, int64_t workspace_bytes, cudaStream_t s);

@@ -222,8 +222,6 @@ __device__ __forceinline__ void expand_word(uint32_t word, uint32_t* r) {
 // byte offset (n%8)*16 + (n/8)*256 + (k%16) + (k/16)*128 with n = 16*piece + rank and
 // k = 4*i + c for the column 8c+7-i of the word.
 __global__ void __launch_bounds__(256) zprep_tc5_kernel(const __grid_constant__ TcParams P, const __half* __restrict__ x) {
-  __shared__ __align__(16) __half vt_s[16][kChunkCols + 8];
-  __shared__ float x_s[kChunkCols];
   __shared__ float red[8];
   __shared__ float kred[16][16];
 
@@ -233,68 +231,91 @@ __global__ void __launch_bounds__(256) zprep_tc5_kernel(const __grid_constant__ 
   const bsb_weight& w = P.w[wi];
   const int j = blockIdx.y - P.blk_base[wi];
   const int N = w.in_features;
-  const int col0 = chunk * kChunkCols;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  // thread = (32-column word, rank): all of its inputs are 64 contiguous bytes of one Vt row and
+  // of x, fetched straight into registers -- no staging, one barrier in the whole kernel
+  const int word = tid >> 4, r = tid & 15;
+  const int col0 = chunk * kChunkCols + word * 32;
+
+  // the decode kernel of this call may be scheduled now (if launched as a programmatic
+  // dependent): it waits (griddepcontrol.wait) before touching anything written here
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   if (blockIdx.x == 0 && blockIdx.y == 0) {
     for (int i = tid; i < P.tile_base[P.n_weights]; i += blockDim.x) P.counters[i] = 0;
     if (tid == 0) *P.status = 0;
   }
+  // issue every load first: Vt and x words of this thread, then the pass over x for max |x|
+  uint4 vq[4], xq[4];
+  const __half* vt = reinterpret_cast<const __half*>(w.vt) + (int64_t)j * w.vt_block_stride + (int64_t)r * N;
+  const bool in_range = col0 < N;   // in_features is a multiple of 128, so a word is inside or outside as a whole
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    vq[i] = in_range ? __ldg(reinterpret_cast<const uint4*>(vt + col0) + i) : make_uint4(0, 0, 0, 0);
+    xq[i] = in_range ? __ldg(reinterpret_cast<const uint4*>(x + col0) + i) : make_uint4(0, 0, 0, 0);
+  }
   float xm = 0.f;
-  for (int n = tid; n < N; n += blockDim.x) xm = fmaxf(xm, fabsf(__half2float(x[n])));
+  for (int n8 = tid; n8 < N / 8; n8 += blockDim.x) {
+    const uint4 q = __ldg(reinterpret_cast<const uint4*>(x) + n8);
+    const __half2* h = reinterpret_cast<const __half2*>(&q);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __half22float2(__habs2(h[i]));
+      xm = fmaxf(xm, fmaxf(f.x, f.y));
+    }
+  }
   for (int o = 16; o > 0; o >>= 1) xm = fmaxf(xm, __shfl_xor_sync(0xFFFFFFFFu, xm, o));
   if (lane == 0) red[warp] = xm;
-
-  const __half* vt = reinterpret_cast<const __half*>(w.vt) + (int64_t)j * w.vt_block_stride;
-  for (int i = tid; i < 16 * (kChunkCols / 8); i += blockDim.x) {
-    const int r = i / (kChunkCols / 8), c8 = (i % (kChunkCols / 8)) * 8;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (col0 + c8 < N) v = __ldg(reinterpret_cast<const uint4*>(vt + (int64_t)r * N + col0 + c8));
-    *reinterpret_cast<uint4*>(&vt_s[r][c8]) = v;
-  }
-  for (int i = tid; i < kChunkCols; i += blockDim.x) x_s[i] = (col0 + i < N) ? __half2float(x[col0 + i]) : 0.f;
   __syncthreads();
   xm = red[0];
 #pragma unroll
   for (int i = 1; i < 8; ++i) xm = fmaxf(xm, red[i]);
 
-  const int r = tid & 15;         // rank
-  const int kh = (tid >> 4) & 1;  // which 16-byte K half: classes 4kh .. 4kh+3
   const float vmax = P.vt_absmax[wi][j * 16 + r];
   const float bound = vmax * xm;
   const float scale = (bound > 0.f) ? (kTargetMax * kMinD) / (2.f * bound) : 1.f;
   const float inv_scale = 1.f / scale;
   if (chunk == 0 && tid < 16) P.inv_scale[(int64_t)blockIdx.y * 16 + r] = inv_scale;
 
-  uint8_t* zout = P.zops + ((int64_t)blockIdx.y * P.n_chunks + chunk) * kChunkBytes;
+  // z[lc] = vt * x for the 32 columns of the word
+  float z[32];
+  {
+    const __half2* vh = reinterpret_cast<const __half2*>(vq);
+    const __half2* xh = reinterpret_cast<const __half2*>(xq);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float2 a = __half22float2(vh[i]), b = __half22float2(xh[i]);
+      z[2 * i] = a.x * b.x;
+      z[2 * i + 1] = a.y * b.y;
+    }
+  }
+  uint8_t* tile = P.zops + ((int64_t)blockIdx.y * P.n_chunks + chunk) * kChunkBytes + word * 1024;
   float c_sum = 0.f, z_sum = 0.f;
 #pragma unroll
-  for (int it = 0; it < 2; ++it) {
-    const int word = (tid >> 5) + 8 * it;
+  for (int kh = 0; kh < 2; ++kh) {
     uint32_t hi[4], lo[4];
 #pragma unroll
     for (int il = 0; il < 4; ++il) {
       const int cls = 4 * kh + il;
       const float mul = 2.f * scale / kD[cls];
       const float v0 = kV0[cls];
-      hi[il] = 0;
-      lo[il] = 0;
+      uint32_t h32 = 0, l32 = 0;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const int col = 32 * word + 8 * c + 7 - cls;
-        const float z = __half2float(vt_s[r][col]) * x_s[col];
-        const float zp = z * mul;
-        const uint8_t qh = (uint8_t)__nv_cvt_float_to_fp8(zp, __NV_SATFINITE, __NV_E4M3);
-        const float fh = e4m3_to_float(qh);
-        const uint8_t ql = (uint8_t)__nv_cvt_float_to_fp8(zp - fh, __NV_SATFINITE, __NV_E4M3);
-        const float fl = e4m3_to_float(ql);
-        c_sum = fmaf(v0, fh + fl, c_sum);
-        z_sum += z;
-        hi[il] |= (uint32_t)qh << (8 * c);
-        lo[il] |= (uint32_t)ql << (8 * c);
+      for (int cp = 0; cp < 2; ++cp) {   // two columns per conversion instruction
+        const float za = z[8 * (2 * cp) + 7 - cls], zb = z[8 * (2 * cp + 1) + 7 - cls];
+        const float2 zp = make_float2(za * mul, zb * mul);
+        const __nv_fp8x2_storage_t qh = __nv_cvt_float2_to_fp8x2(zp, __NV_SATFINITE, __NV_E4M3);
+        const float2 fh = __half22float2(__half2(__nv_cvt_fp8x2_to_halfraw2(qh, __NV_E4M3)));
+        const __nv_fp8x2_storage_t ql = __nv_cvt_float2_to_fp8x2(make_float2(zp.x - fh.x, zp.y - fh.y), __NV_SATFINITE, __NV_E4M3);
+        const float2 fl = __half22float2(__half2(__nv_cvt_fp8x2_to_halfraw2(ql, __NV_E4M3)));
+        c_sum = fmaf(v0, (fh.x + fl.x) + (fh.y + fl.y), c_sum);
+        z_sum += za + zb;
+        h32 |= (uint32_t)qh << (16 * cp);
+        l32 |= (uint32_t)ql << (16 * cp);
       }
+      hi[il] = h32;
+      lo[il] = l32;
     }
-    uint8_t* tile = zout + word * 1024;
     // n = r (hi) and n = 16 + r (lo); 16 consecutive k bytes starting at 16*kh
     const int off_hi = (r % 8) * 16 + (r / 8) * 256 + kh * 128;
     const int off_lo = (r % 8) * 16 + ((16 + r) / 8) * 256 + kh * 128;
@@ -302,7 +323,7 @@ __global__ void __launch_bounds__(256) zprep_tc5_kernel(const __grid_constant__ 
     *reinterpret_cast<uint4*>(tile + off_lo) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
   }
   // constant of this (block, chunk, rank): C_r / s_r + sum Z over the chunk's columns
-  kred[tid >> 4][r] = c_sum * inv_scale + z_sum;
+  kred[word][r] = c_sum * inv_scale + z_sum;
   __syncthreads();
   if (tid < 16) {
     float v = 0.f;
@@ -399,10 +420,19 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
     // ---- loader: Z' slabs (bulk copy) and sign tiles (tiled TMA), each with its own ring ----
     if (lane == 0) {
       const CUtensorMap* map = &P.sign_map[wi];
+      // the packed signs do not depend on the Z' kernel: fill the tile ring before waiting for it
+      const int pre = min(total, kNP);
+      for (int g = 0; g < pre; ++g) {
+        const int js = g / nch, ci = g - js * nch;
+        const int j = (js + j_rot) % NB;
+        mbar_expect_tx(&S.sfull[g], kSignTileBytes);
+        tma_load_3d(S.sg[g], map, (c_lo + ci) * (kChunkCols / 8), rt * kTileRows, j, &S.sfull[g]);
+      }
+      asm volatile("griddepcontrol.wait;" ::: "memory");
       for (int g = 0; g < total; ++g) {
         const int js = g / nch, ci = g - js * nch;
         const int j = (js + j_rot) % NB;
-        if (P.dbg != 1) {
+        if (g >= pre) {
           const int slot = g % kNP, n = g / kNP;
           TR_BEGIN(t0);
           if (n >= 1 && !mbar_wait(&S.sempty[slot], (n - 1) & 1)) { atomicExch(P.status, 7); break; }
@@ -481,7 +511,6 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
 #pragma unroll
       for (int i = 0; i < 8; ++i) asm volatile("mov.u32 %0, %1;" : "=r"(cc[i]) : "r"(class_byte(i) * 0x01010101u));
       bool ok = true;
-      int prev_slot = -1;
       TR_BEGIN(t_prod);
 #pragma unroll 1
       for (int g = 0; g < total && ok; ++g) {
@@ -503,12 +532,6 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
 #pragma unroll
           for (int q = 0; q < 4; ++q) expand_word_c(wd[q], cc, r + q * 8);
           TR_ADD(3, t2);
-          // hand over the previous stage only now: its stores completed behind the expansion above
-          if (prev_slot >= 0) {
-            tmem_wait_st();
-            tc_fence_before();
-            if (P.dbg != 2) mbar_arrive(&S.afull[e][prev_slot]);
-          }
           if (it >= 2 && P.dbg != 2) {
             TR_BEGIN(t1);
             const bool got = __all_sync(0xFFFFFFFFu, mbar_wait(&S.aempty[e][slot], ((it >> 1) - 1) & 1) ? 1 : 0);
@@ -516,14 +539,13 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
             if (!got) { atomicExch(P.status, 4); ok = false; break; }
             tc_fence_after();
           }
+          // store and hand over at once: with only two stages per issuer every nanosecond of
+          // hand-off latency is on the critical path
           tmem_st32(lane_base + slot * 32, r);
-          prev_slot = slot;
+          tmem_wait_st();
+          tc_fence_before();
+          if (P.dbg != 2) mbar_arrive(&S.afull[e][slot]);
         }
-      }
-      if (prev_slot >= 0) {
-        tmem_wait_st();
-        tc_fence_before();
-        if (P.dbg != 2 && ok) mbar_arrive(&S.afull[e][prev_slot]);
       }
       TR_ADD(0, t_prod);
     }
@@ -531,6 +553,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
     // ---- epilogue warps: y[m] += sum_r U_j[m,r] (T[m,r] / s_r - K_r) per block, T = sum of the
     //      hi and lo pieces of both issuers' accumulators ------------------------------------
     if (P.dbg == 0) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // constants below come from the Z' kernel
     const int quarter = warp & 3;                     // tensor-memory lanes this warp may read
     const int rtid = quarter * 32 + lane;
     const int row = min(rt * kTileRows + rtid, M - 1);
@@ -619,6 +642,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
     tmem_dealloc(tbase, kTmemCols);
   }
   if (nsplit == 1) return;
+  asm volatile("griddepcontrol.wait;" ::: "memory");     // the counters were zeroed by the Z' kernel
   if (tid == 0) {
     const int old = atomicAdd(&P.counters[P.tile_base[wi] + rt], 1);
     S.last = (old == nsplit - 1);
@@ -749,6 +773,8 @@ static int make_sign_map(const bsb_weight& w, CUtensorMap* map) {
 
 static unsigned long long* g_trace = nullptr;
 static int g_dbg = 0;
+static int g_pdl = 0;   // measured neutral-to-slightly-worse on the decode benchmark; kept selectable
+void gemv_tc5_set_pdl(int on) { g_pdl = on; }
 void gemv_tc5_set_dbg(int m) { g_dbg = m; }
 void gemv_tc5_set_trace(unsigned long long* p) { g_trace = p; }
 
@@ -818,7 +844,24 @@ int launch_gemv_tc5(const bsb_weight* ws, int n_weights, const __half* x, __half
   zprep_tc5_kernel<<<dim3(P.n_chunks, pl.total_blocks), 256, 0, s>>>(P, x);
   if (int rc = check_launch("zprep_tc5_kernel")) return rc;
   profile_mark(s, false);
-  gemv_tc5_kernel<<<pl.total_items, kThreads, sizeof(SmemLayout) + 1024, s>>>(P);
+  {
+    // programmatic dependent launch: the decode kernel may start while the Z' kernel still runs
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(pl.total_items);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = sizeof(SmemLayout) + 1024;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = g_pdl ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t le = cudaLaunchKernelEx(&cfg, gemv_tc5_kernel, P);
+    if (le != cudaSuccess) {
+      set_error("launch of gemv_tc5_kernel failed: %s", cudaGetErrorString(le));
+      return BSB_ECUDA;
+    }
+  }
   profile_mark(s, true);
   return check_launch("gemv_tc5_kernel");
 }

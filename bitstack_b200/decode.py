@@ -22,6 +22,7 @@ from typing import Dict, Optional
 import torch
 import torch.nn.functional as F
 
+from . import glue
 from .linear import BitStackLinear, forward_grouped
 
 PROJ_NAMES = ("self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj", "self_attn.o_proj",
@@ -104,8 +105,9 @@ class BitStackLlamaDecoder:
     """Random-init Llama-architecture decoder whose linears are BitStack modules."""
 
     def __init__(self, shape: LlamaShape, block_counts: Dict[str, int], device, seed=0, max_len=1024,
-                 batch=1, fused_level=6, rank=0, world_size=1, group=None):
+                 batch=1, fused_level=6, rank=0, world_size=1, group=None, fused_glue=True):
         self.shape, self.device, self.max_len, self.batch = shape, torch.device(device), max_len, batch
+        self.fused_glue = fused_glue
         self.rank, self.world, self.group = rank, world_size, group
         s = shape
         assert s.n_kv_heads % world_size == 0 and s.intermediate % (128 * world_size) == 0
@@ -190,6 +192,29 @@ class BitStackLlamaDecoder:
         h = F.rms_norm(h[:, -1], (self.shape.hidden,), self.final_norm, self.shape.rms_eps)
         return h @ self.lm_head.t()
 
+    def _decode_fused(self):
+        """One decode step (one new token per sequence) with the fused glue kernels: per layer
+        13 launches instead of ~30.  Same math as `_forward` on a single position."""
+        s = self.shape
+        B = self.batch
+        hd = s.head_dim
+        h = self.embed.index_select(0, self.tokens).contiguous()            # [B, hidden], residual stream
+        mask = (self.arange <= self.pos).view(1, 1, 1, self.max_len)
+        x = glue.add_rmsnorm(h, None, self.layers[0]["in_norm"], s.rms_eps)
+        for i, lay in enumerate(self.layers):
+            q, k, v = forward_grouped([lay["self_attn.q_proj"], lay["self_attn.k_proj"], lay["self_attn.v_proj"]], x)
+            glue.rope_cache(q, k, v, self.cos, self.sin, self.pos, self.k_cache[i], self.v_cache[i],
+                            self.q_local, self.kv_local, hd)
+            att = F.scaled_dot_product_attention(q.view(B, self.q_local, 1, hd), self.k_cache[i], self.v_cache[i],
+                                                 attn_mask=mask, enable_gqa=True)
+            o = self._allreduce(lay["self_attn.o_proj"](att.reshape(B, self.q_local * hd)))
+            x = glue.add_rmsnorm(h, o, lay["post_norm"], s.rms_eps)
+            g, u = forward_grouped([lay["mlp.gate_proj"], lay["mlp.up_proj"]], x)
+            d = self._allreduce(lay["mlp.down_proj"](glue.silu_mul(g, u)))
+            nxt = self.layers[i + 1]["in_norm"] if i + 1 < len(self.layers) else self.final_norm
+            x = glue.add_rmsnorm(h, d, nxt, s.rms_eps)
+        return x @ self.lm_head.t()
+
     # ------------------------------------------------------------------ public API
     @torch.no_grad()
     def prefill(self, prompt_ids: torch.Tensor):
@@ -204,7 +229,7 @@ class BitStackLlamaDecoder:
     @torch.no_grad()
     def decode_step(self):
         """One greedy token for every sequence; position and token feedback stay on the device."""
-        logits = self._forward(self.tokens.view(-1, 1), self.pos)
+        logits = self._decode_fused() if self.fused_glue else self._forward(self.tokens.view(-1, 1), self.pos)
         self.tokens.copy_(logits.argmax(-1))
         self.pos.add_(1)
         return self.tokens

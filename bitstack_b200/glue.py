@@ -1,0 +1,50 @@
+"""Fused decode-time glue ops (residual add + RMSNorm, rotary + KV-cache write, SiLU*up) on CUDA
+tensors, through the C ABI.  These are harness helpers around the BitStack projections; the
+reference leaves the same ops to the Hugging Face Llama modules."""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+
+def _s(t):
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def add_rmsnorm(h: torch.Tensor, delta, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """In place h += delta (skipped when delta is None); returns rmsnorm(h) * weight.  h: [rows, hidden] fp16."""
+    assert h.is_cuda and h.dtype == torch.float16 and h.is_contiguous() and h.dim() == 2
+    if delta is not None:
+        delta = delta.reshape(h.shape)
+        assert delta.dtype == torch.float16 and delta.is_contiguous()
+    y = torch.empty_like(h)
+    with torch.cuda.device(h.device):
+        rc = _lib.load().bsb_add_rmsnorm(h.data_ptr(), None if delta is None else delta.data_ptr(), weight.data_ptr(),
+                                         float(eps), y.data_ptr(), h.shape[0], h.shape[1], _s(h))
+    _lib.check(rc, "bsb_add_rmsnorm")
+    return y
+
+
+def rope_cache(q, k, v, cos, sin, pos, k_cache, v_cache, q_heads, kv_heads, head_dim):
+    """Rotary embedding at position pos[0] (device int64) on q in place and on k, which goes with v
+    into k_cache / v_cache [batch, kv_heads, max_len, head_dim]."""
+    for t in (q, k, v, cos, sin, k_cache, v_cache):
+        assert t.is_cuda and t.dtype == torch.float16 and t.is_contiguous()
+    assert pos.dtype == torch.int64 and pos.is_cuda
+    batch = q.shape[0]
+    with torch.cuda.device(q.device):
+        rc = _lib.load().bsb_rope_cache(q.data_ptr(), k.data_ptr(), v.data_ptr(), cos.data_ptr(), sin.data_ptr(),
+                                        pos.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), batch, q_heads, kv_heads,
+                                        head_dim, k_cache.shape[2], _s(q))
+    _lib.check(rc, "bsb_rope_cache")
+    return q
+
+
+def silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    assert gate.is_cuda and gate.dtype == torch.float16 and gate.is_contiguous() and up.is_contiguous()
+    out = torch.empty_like(gate)
+    with torch.cuda.device(gate.device):
+        rc = _lib.load().bsb_silu_mul(gate.data_ptr(), up.data_ptr(), out.data_ptr(), gate.numel(), _s(gate))
+    _lib.check(rc, "bsb_silu_mul")
+    return out

@@ -120,6 +120,21 @@ int bsb_linear_forward_grouped(const bsb_weight* ws, int32_t n_weights, const ui
 /* Scratch bytes bsb_linear_forward_grouped needs. */
 int64_t bsb_linear_grouped_workspace_bytes(const bsb_weight* ws, int32_t n_weights, int64_t rows, int algo);
 
+/* ---- decode-time glue (no counterpart in the reference, which leaves these ops to the Hugging
+ * Face Llama modules; bitstack/utils/scale_utils.py:3-5 names the classes it wraps) ------------
+ * bsb_add_rmsnorm: h[rows][hidden] += delta (if delta != NULL; fp16 residual stream, written
+ *   back), then y = h * rsqrt(mean(h^2) + eps) * weight with fp32 arithmetic.
+ * bsb_rope_cache: rotary embedding at position *pos (device scalar) on q[batch][q_heads*dim] in
+ *   place and on k, which is written with v into caches [batch][kv_heads][max_len][dim];
+ *   cos/sin tables are [max_len][dim] in the "rotate half" convention.
+ * bsb_silu_mul: out = silu(gate) * up over n fp16 elements. */
+int bsb_add_rmsnorm(uint16_t* h, const uint16_t* delta, const uint16_t* weight, float eps, uint16_t* y, int64_t rows,
+                    int32_t hidden, void* stream);
+int bsb_rope_cache(uint16_t* q, const uint16_t* k, const uint16_t* v, const uint16_t* cos_table, const uint16_t* sin_table,
+                   const int64_t* pos, uint16_t* k_cache, uint16_t* v_cache, int32_t batch, int32_t q_heads,
+                   int32_t kv_heads, int32_t head_dim, int32_t max_len, void* stream);
+int bsb_silu_mul(const uint16_t* gate, const uint16_t* up, uint16_t* out, int64_t n, void* stream);
+
 /* Forward for callers that may not allocate device memory.  It has no counterpart in the
  * reference.  Some hosts hand a plug-in a fixed set of buffers and forbid any device
  * allocation once they are running -- an inference server with a frozen memory plan, a
@@ -159,7 +174,8 @@ int64_t bsb_debug_launch_count(void);
  * cycle counts (waits, issue, totals) for performance analysis; NULL switches it off. */
 int bsb_debug_set_trace(void* device_buffer);
 /* Timing experiments on the tcgen05 decode kernel: 0 = normal, 1 = tensor-core side only,
- * 2 = sign-streaming side only.  Modes 1 and 2 produce WRONG outputs by design. */
+ * 2 = sign-streaming side only (modes 1 and 2 produce WRONG outputs by design); 100 / 101 switch
+ * the programmatic dependent launch of the decode kernel off / on (default off). */
 int bsb_debug_set_mode(int32_t mode);
 int bsb_debug_profile_start(int32_t max_launches);
 int bsb_debug_profile_stop(float* ms_out, int32_t capacity, int32_t* n_out);

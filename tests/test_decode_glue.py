@@ -1,0 +1,90 @@
+"""GPU checks of the fused decode glue kernels against plain torch fp32 references, and of the
+fused decode step against the unfused torch-op step of the same harness."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    return torch.device("cuda:0")
+
+
+@pytest.mark.parametrize("rows,hidden", [(1, 4096), (3, 8192), (16, 128)])
+def test_add_rmsnorm(dev, rows, hidden):
+    from bitstack_b200 import glue
+    g = torch.Generator(device=dev).manual_seed(rows + hidden)
+    h = torch.randn(rows, hidden, device=dev, generator=g).half()
+    d = torch.randn(rows, hidden, device=dev, generator=g).half()
+    w = (1 + 0.1 * torch.randn(hidden, device=dev, generator=g)).half()
+    h_ref = (h.float() + d.float()).half()
+    y_ref = (h_ref.float() * torch.rsqrt(h_ref.float().pow(2).mean(-1, keepdim=True) + 1e-5) * w.float())
+    h2 = h.clone()
+    y = glue.add_rmsnorm(h2, d, w, 1e-5)
+    assert torch.equal(h2, h_ref)
+    assert (y.float() - y_ref).abs().max() <= 2e-3 * y_ref.abs().max()
+    h3 = h.clone()
+    y0 = glue.add_rmsnorm(h3, None, w, 1e-5)
+    assert torch.equal(h3, h)
+    ref0 = h.float() * torch.rsqrt(h.float().pow(2).mean(-1, keepdim=True) + 1e-5) * w.float()
+    assert (y0.float() - ref0).abs().max() <= 2e-3 * ref0.abs().max()
+
+
+def test_silu_mul(dev):
+    from bitstack_b200 import glue
+    g = torch.randn(4, 14336, device=dev).half()
+    u = torch.randn(4, 14336, device=dev).half()
+    out = glue.silu_mul(g, u)
+    ref = F.silu(g.float()) * u.float()
+    assert (out.float() - ref).abs().max() <= 4e-3 * ref.abs().max()
+
+
+def test_rope_cache(dev):
+    from bitstack_b200 import glue
+    B, Hq, Hkv, D, L = 2, 8, 2, 128, 64
+    q = torch.randn(B, Hq * D, device=dev).half()
+    k = torch.randn(B, Hkv * D, device=dev).half()
+    v = torch.randn(B, Hkv * D, device=dev).half()
+    inv = 1.0 / (500000.0 ** (torch.arange(0, D, 2, device=dev).float() / D))
+    fr = torch.outer(torch.arange(L, device=dev).float(), inv)
+    cos, sin = torch.cat([fr, fr], -1).cos().half(), torch.cat([fr, fr], -1).sin().half()
+    kc = torch.zeros(B, Hkv, L, D, device=dev, dtype=torch.float16)
+    vc = torch.zeros_like(kc)
+    pos = torch.tensor([37], device=dev)
+
+    def rope(x, heads):
+        x = x.view(B, heads, D).float()
+        rot = torch.cat([-x[..., D // 2:], x[..., :D // 2]], -1)
+        return x * cos[37].float() + rot * sin[37].float()
+
+    q_ref, k_ref = rope(q, Hq), rope(k, Hkv)
+    glue.rope_cache(q, k, v, cos, sin, pos, kc, vc, Hq, Hkv, D)
+    assert (q.view(B, Hq, D).float() - q_ref).abs().max() <= 4e-3 * q_ref.abs().max()
+    assert (kc[:, :, 37].float() - k_ref).abs().max() <= 4e-3 * k_ref.abs().max()
+    assert torch.equal(vc[:, :, 37], v.view(B, Hkv, D))
+    assert kc[:, :, :37].abs().max() == 0 and kc[:, :, 38:].abs().max() == 0
+
+
+def test_fused_decode_step_matches_unfused(dev):
+    from bitstack_b200 import decode
+    shape = decode.LlamaShape("tiny", 2, 512, 4, 2, 1024, vocab=1000)
+    counts = decode.seeded_block_counts(shape, seed=3, lo=2, hi=4)
+    prompt = torch.randint(0, 1000, (1, 9), device=dev)
+    outs = []
+    for fused in (False, True):
+        m = decode.BitStackLlamaDecoder(shape, counts, dev, seed=5, max_len=128, fused_glue=fused)
+        m.prefill(prompt)
+        toks, logits = [], None
+        for _ in range(4):
+            logits = (m._decode_fused() if fused else m._forward(m.tokens.view(-1, 1), m.pos)).float()
+            m.tokens.copy_(logits.argmax(-1))
+            m.pos.add_(1)
+            toks.append(int(m.tokens[0]))
+        outs.append((toks, logits))
+    (t0, l0), (t1, l1) = outs
+    assert (l0 - l1).abs().max() <= 2e-2 * l0.abs().max()
+    assert t0 == t1
