@@ -202,6 +202,11 @@ def config_dict(args, shape, counts, batch, prompt):
 
 
 # ----------------------------------------------------------------------------- ours
+def _progress(msg):
+    if os.environ.get("BSB_BENCH_VERBOSE"):
+        print(f"[rank {os.environ.get('RANK', '0')}] {msg}", file=sys.stderr, flush=True)
+
+
 def run_ours(args):
     from bitstack_b200 import _lib, decode
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -213,8 +218,11 @@ def run_ours(args):
     dev = torch.device("cuda", local)
     group = None
     if world > 1:
-        torch.distributed.init_process_group("nccl", device_id=dev)
+        import datetime
+        # a short collective timeout: a rank that leaves the common path aborts the job instead of hanging it
+        torch.distributed.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
         group = torch.distributed.group.WORLD
+    _progress("process group ready")
     lib = _lib.load()
     if os.environ.get("BSB_PDL") == "0":
         lib.bsb_debug_set_mode(100)
@@ -232,12 +240,18 @@ def run_ours(args):
         torch.cuda.synchronize()
 
     # ---- device-timed value ------------------------------------------------------------
+    _progress("model built")
     model.prefill(prompt_host.to(dev))
+    torch.cuda.synchronize()
+    _progress("prefill done")
     n0 = lib.bsb_debug_launch_count()
     model.decode_step()
     launches_per_step = lib.bsb_debug_launch_count() - n0
+    torch.cuda.synchronize()
+    _progress("eager step done")
     if not args.no_graph:
         model.capture()
+        _progress("graph captured")
     for _ in range(max(args.warmup, 3)):
         model.step()
     barrier()
@@ -257,6 +271,7 @@ def run_ours(args):
     ms = float(ms.item())
     clocks = sampler.stop() if rank == 0 else None
     value = args.steps * batch / (ms / 1000.0)
+    _progress("timed region done")
 
     # ---- end to end through the host-facing API ------------------------------------------
     pinned = torch.empty(args.steps, batch, dtype=torch.long).pin_memory()
@@ -274,24 +289,27 @@ def run_ours(args):
     if world > 1:
         torch.distributed.all_reduce(e2e_s, op=torch.distributed.ReduceOp.MAX)
     e2e = args.steps * batch / float(e2e_s.item())
+    _progress("e2e done")
 
     # ---- roofline of the dominant kernel (eager step, events around each launch) -----------
     roof = None
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    peak, which = (peaks["hbm_gbs"], "measured") if "hbm_gbs" in peaks else (6650.0, "fallback")
+    # every rank runs the profiled eager step (it contains the all-reduces); rank 0 reports its own timings
+    model._graph, g = None, model._graph
+    barrier()
+    lib.bsb_debug_profile_start(4096)
+    model.decode_step()
+    buf = (C.c_float * 4096)()
+    n = C.c_int32(0)
+    lib.bsb_debug_profile_stop(buf, 4096, C.byref(n))
+    model._graph = g
+    barrier()
     if rank == 0:
-        peaks = {}
-        try:
-            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-        except Exception:
-            pass
-        peak, which = (peaks["hbm_gbs"], "measured") if "hbm_gbs" in peaks else (6650.0, "fallback")
-        model._graph, g = None, model._graph
-        torch.cuda.synchronize()
-        lib.bsb_debug_profile_start(4096)
-        model.decode_step()
-        buf = (C.c_float * 4096)()
-        n = C.c_int32(0)
-        lib.bsb_debug_profile_stop(buf, 4096, C.byref(n))
-        model._graph = g
         durs = np.array(buf[: n.value], dtype=np.float64)
         shapes = shape.proj_shapes()
         launch_bytes = []
@@ -308,16 +326,16 @@ def run_ours(args):
                     b += counts[f"layer.{i}.{p}"] * decode.block_bytes(out_f, in_f) + 2 * out_f
                 out_f, in_f = shapes[grp[0]]
                 b += 2 * (in_f // world if grp[0] in ("self_attn.o_proj", "mlp.down_proj") else in_f)
-                launch_bytes.append(b * batch if batch > 1 else b)
-        if n.value == len(launch_bytes) and n.value > 0:
+                launch_bytes.append(b)
+        if batch == 1 and n.value == len(launch_bytes) and n.value > 0:
             achieved = sum(launch_bytes) / (durs.sum() / 1000.0) / 1e9
             roof = {"bound": "hbm", "kernel": "gemv_tc5_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                    "frac": achieved / peak, "peak_source": which + " (of measured copy bandwidth)" if which == "measured" else "fallback",
+                    "frac": achieved / peak, "peak_source": "measured copy bandwidth (of measured)" if which == "measured" else "fallback",
                     "traffic": None, "launches": int(n.value), "avg_launch_us": float(durs.mean() * 1000.0),
                     "algorithmic_bytes_per_launch": float(np.mean(launch_bytes))}
         else:
             roof = {"bound": "hbm", "kernel": "gemv_tc5_kernel", "achieved": None, "peak": peak, "unit": "GB/s", "frac": None,
-                    "traffic": None, "note": f"{n.value} profiled launches, {len(launch_bytes)} expected (batch path in use?)"}
+                    "traffic": None, "note": f"{n.value} decode-kernel launches profiled in one step (batch {batch}: rows > 4 use the rebuild+GEMM path)"}
 
     # ---- CPU restatement on a bounded sample ---------------------------------------------
     cpu = None
@@ -334,7 +352,15 @@ def run_ours(args):
                 "graph": not args.no_graph}
         print(json.dumps(line), flush=True)
     if world > 1:
-        torch.distributed.destroy_process_group()
+        # Tearing NCCL down while captured graphs still reference its kernels was seen to block
+        # forever at exit: drop the graph, drain the device, agree that everyone is done, then
+        # leave without running the communicator destructors.
+        model._graph = None
+        torch.cuda.synchronize()
+        torch.distributed.barrier()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def main():
