@@ -278,7 +278,7 @@ int bsb_debug_set_trace(void* device_buffer) {
 }
 
 int bsb_debug_set_mode(int32_t mode) {
-  if (mode >= 100) {   // 100 / 101: programmatic dependent launch off / on
+  if (mode == 100 || mode == 101) {   // programmatic dependent launch off / on
     gemv_tc5_set_pdl(mode - 100);
     return BSB_OK;
   }

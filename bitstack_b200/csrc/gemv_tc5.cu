@@ -15,12 +15,14 @@
 // as two e4m3 pieces (rows 0-15 "hi", 16-31 "lo") in the same K order, so
 //     T[m,r] = D_hi + D_lo = C_r + 2 s_r sum_n b Z,    D_j[m,r] = (T - C_r)/s_r - sum_n Z.
 //
-// CTA = 320 threads: two groups of four producer warps stream sign bytes (cp.async FIFO
-// in shared memory, one row per thread, alternate 128-column stages per group), expand
-// them and feed tensor memory; group 0 also runs the epilogue; warp 8 issues the MMAs;
-// warp 9 owns tensor-memory allocation and the Z' bulk copies.  All hand-offs
-// are mbarriers with time-bounded waits: on a timeout the kernel raises a status word
-// and leaves, it never spins forever.
+// CTA = 512 threads, two per multiprocessor: a loader thread streams sign tiles (tiled TMA) and
+// Z' slabs (bulk copies) into shared-memory rings; two groups of four producer warps expand
+// sign bytes into tensor memory, each feeding its own MMA-issuing thread and accumulators;
+// four epilogue warps apply U and accumulate y over blocks.  All hand-offs are mbarriers
+// with time-bounded waits: on a timeout the kernel raises a status word and leaves, it never
+// spins forever.  Roles with slack (loader, epilogue) poll with one lane and a growing sleep:
+// the polling of idle roles otherwise saturates the special-function issue path and slows the
+// warps on the critical path (measured 130 -> 114 us on a 14336 x 4096, 16-block weight).
 #include <cuda.h>
 #include <cuda_fp8.h>
 
@@ -117,6 +119,37 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     if (global_ns() - t0 > kWaitLimitNs) return false;
   }
 }
+// Wait for roles that have slack (epilogue, loader): one lane polls with a growing sleep, so the
+// barrier words, the issue slots and the special-register path stay free for the warps on the
+// critical path; the other lanes then observe the completed phase once (their own acquire).
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity) {
+  if (mbar_test(bar, parity)) return true;
+  uint32_t sleep_ns = 64;
+  uint64_t t0 = 0;
+#pragma unroll 1
+  for (int n = 1;; ++n) {
+    __nanosleep(sleep_ns);
+    if (mbar_test(bar, parity)) return true;
+    if (sleep_ns < 512) sleep_ns *= 2;
+    if ((n & 63) == 0) {
+      const uint64_t now = global_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > kWaitLimitNs) return false;
+    }
+  }
+}
+__device__ __forceinline__ bool mbar_wait_warp_relaxed(uint64_t* bar, uint32_t parity) {
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait_relaxed(bar, parity) ? 1 : 0;
+  ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+  if (ok) ok = mbar_test(bar, parity) ? 1 : 0;
+  return __all_sync(0xFFFFFFFFu, ok) != 0;
+}
+// producer-group wait: every lane polls for itself -- electing one poller per warp adds a
+// shuffle and a second test to the hand-off, which measured 25 % slower on the whole kernel
+__device__ __forceinline__ bool mbar_wait_group(uint64_t* bar, uint32_t parity) {
+  return __all_sync(0xFFFFFFFFu, mbar_wait(bar, parity) ? 1 : 0) != 0;
+}
 __device__ __forceinline__ void tmem_alloc(uint32_t* dst, int cols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst)), "r"(cols) : "memory");
 }
@@ -156,6 +189,11 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
         "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr) : "memory");
 }
 // D[tmem] (+)= A[tmem] . B[smem]^T, e4m3 x e4m3 -> f32
 __device__ __forceinline__ void mma_ts_f8(uint32_t d, uint32_t a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
@@ -211,10 +249,6 @@ __device__ __forceinline__ uint32_t expand_c(uint32_t word, uint32_t c) {
 __device__ __forceinline__ void expand_word_c(uint32_t word, const uint32_t (&c)[8], uint32_t* r) {
   r[0] = expand_c<0>(word, c[0]); r[1] = expand_c<1>(word, c[1]); r[2] = expand_c<2>(word, c[2]); r[3] = expand_c<3>(word, c[3]);
   r[4] = expand_c<4>(word, c[4]); r[5] = expand_c<5>(word, c[5]); r[6] = expand_c<6>(word, c[6]); r[7] = expand_c<7>(word, c[7]);
-}
-__device__ __forceinline__ void expand_word(uint32_t word, uint32_t* r) {
-  r[0] = expand<0>(word); r[1] = expand<1>(word); r[2] = expand<2>(word); r[3] = expand<3>(word);
-  r[4] = expand<4>(word); r[5] = expand<5>(word); r[6] = expand<6>(word); r[7] = expand<7>(word);
 }
 
 // ------------------------------------------------------------------ Z' preparation
@@ -334,25 +368,36 @@ __global__ void __launch_bounds__(256) zprep_tc5_kernel(const __grid_constant__ 
 }
 
 // cycle accounting for the optional trace (one elected lane per role writes)
+#ifdef BSB_TRACE
 #define TR_BEGIN(var) const long long var = tr ? clock64() : 0
 #define TR_ADD(slot, var) do { if (tr) S.trace[slot] += (unsigned long long)(clock64() - var); } while (0)
+#else
+#define TR_BEGIN(var) do { } while (0)
+#define TR_ADD(slot, var) do { } while (0)
+#endif
 
 // ------------------------------------------------------------------ main kernel
-// One CTA = one 128-row tile x one column split of one weight, ALL active blocks: set-up,
+// One CTA = RT 128-row tiles x one column split of one weight, ALL active blocks: set-up,
 // pipeline fill and the final reduction are paid once and the fp32 output of a row is
 // accumulated over blocks in a register of its epilogue thread.
 //
 // A single thread can only issue a tcgen05.mma every ~28 ns (and a commit costs it ~60 ns)
 // while the tensor pipe itself accepts several such streams side by side, so the CTA runs TWO
-// independent operand pipelines: producer group e (4 warps) expands the e-th 32 bytes of every
-// 64-byte sign row and feeds MMA issuer e, which accumulates into its own D (the epilogue adds
-// the two).  Every D is double buffered across blocks.  Tensor-memory columns:
+// independent operand pipelines, each a group of four producer warps feeding one MMA issuer
+// with its own accumulators:
+//   RT == 1: pipeline e takes the e-th 32 bytes of every 64-byte sign row (K halves of one row
+//            tile); the epilogue adds the two accumulators.
+//   RT == 2: pipeline e takes row tile e (all 64 bytes of a row); both pipelines read the SAME
+//            Z' slab, which halves the Z' traffic from L2 per sign byte -- with one tile per CTA
+//            that traffic is twice the sign traffic and bounds the kernel.
+// Every D is double buffered across blocks.  Tensor-memory columns:
 //   D(e, b) = e*64 + b*32           (4 x 32)
 //   A(e, s) = 128 + e*64 + s*32     (2 issuers x 2 stages x 4 MMAs)
+constexpr int kSignRingBytes = 6 * kSignTileBytes;
 struct __align__(1024) SmemLayout {
   uint8_t zs[kNZ][kChunkBytes];         // Z' operand slabs (bulk-copied)
-  uint8_t sg[kNP][kSignTileBytes];      // sign tiles: row r at r*64, 16-byte piece p at ((p ^ ((r>>1)&3)) * 16)
-  uint64_t afull[2][2], aempty[2][2], zfull[kNZ], zempty[kNZ], sfull[kNP], sempty[kNP], dfull[2][2], dempty[2];
+  uint8_t sg[kSignRingBytes];           // sign tiles: row r at r*64, 16-byte piece p at ((p ^ ((r>>1)&3)) * 16)
+  uint64_t afull[2][2], aempty[2][2], zfull[kNZ], zempty[kNZ], sfull[6], sempty[6], dfull[2][2], dempty[2];
   unsigned long long trace[16];
   uint32_t tmem_base;
   int last;
@@ -362,7 +407,11 @@ constexpr int kWarpMma = 8;     // warps 8, 9: MMA issuers 0, 1
 constexpr int kWarpLoad = 10;   // tensor-memory allocation, TMA / bulk loads
 constexpr int kWarpEpi = 12;    // warps 12-15: epilogue (tensor-memory lane quarters 0-3)
 
+template <int RT>
 __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_constant__ TcParams P) {
+  constexpr int kSlotBytes = RT * kSignTileBytes;   // one ring slot = the RT sign tiles of a chunk
+  constexpr int kNS = 6 / RT;                       // ring slots
+  constexpr int kPP = 2 * RT;                       // operand stages (4 MMAs each) per chunk and pipeline
   extern __shared__ uint8_t smem_raw[];
   SmemLayout& S = *reinterpret_cast<SmemLayout*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
 
@@ -372,14 +421,15 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
   const int nsplit = P.splits[wi];
   const int item = blockIdx.x - P.item_base[wi];
   const int split = item % nsplit;
-  const int rt = item / nsplit;
+  const int rt = item / nsplit;               // group of RT row tiles
+  const int row0 = rt * RT * kTileRows;
   const int M = w.out_features, NB = w.blocks;
   const int c_lo = split * P.chunks_per_item[wi];
   const int c_hi = min(P.n_chunks, c_lo + P.chunks_per_item[wi]);
   const int nch = c_hi - c_lo;
   const int total = NB * nch;                 // chunks this CTA streams, block-major
   const int jb0 = P.blk_base[wi];
-  // every row tile walks the blocks in a different rotation, so that co-running CTAs do not
+  // every row group walks the blocks in a different rotation, so that co-running CTAs do not
   // all pull the same Z' slab out of the same L2 lines at the same moment
   const int j_rot = rt % NB;
 
@@ -389,6 +439,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
   // wait, 12 CTA total, 13 set-up
   unsigned long long* tr = (P.trace && lane == 0 && (warp == 0 || warp == kWarpMma || warp == kWarpLoad || warp == kWarpEpi))
                                ? P.trace + (int64_t)blockIdx.x * 16 : nullptr;
+  (void)tr;
   TR_BEGIN(t_cta);
 
   // ---- set-up ---------------------------------------------------------------------
@@ -405,7 +456,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
         mbar_init(&S.dfull[e][i], 1);
       }
     for (int i = 0; i < kNZ; ++i) { mbar_init(&S.zfull[i], 1); mbar_init(&S.zempty[i], 2); }
-    for (int i = 0; i < kNP; ++i) { mbar_init(&S.sfull[i], 1); mbar_init(&S.sempty[i], 2 * kTileRows); }
+    for (int i = 0; i < kNS; ++i) { mbar_init(&S.sfull[i], 1); mbar_init(&S.sempty[i], 2 * kTileRows); }
     for (int i = 0; i < 2; ++i) mbar_init(&S.dempty[i], kTileRows);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -420,29 +471,32 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
     // ---- loader: Z' slabs (bulk copy) and sign tiles (tiled TMA), each with its own ring ----
     if (lane == 0) {
       const CUtensorMap* map = &P.sign_map[wi];
-      // the packed signs do not depend on the Z' kernel: fill the tile ring before waiting for it
-      const int pre = min(total, kNP);
-      for (int g = 0; g < pre; ++g) {
+      auto load_signs = [&](int g, int slot) {
         const int js = g / nch, ci = g - js * nch;
         const int j = (js + j_rot) % NB;
-        mbar_expect_tx(&S.sfull[g], kSignTileBytes);
-        tma_load_3d(S.sg[g], map, (c_lo + ci) * (kChunkCols / 8), rt * kTileRows, j, &S.sfull[g]);
-      }
+        mbar_expect_tx(&S.sfull[slot], kSlotBytes);
+#pragma unroll
+        for (int t = 0; t < RT; ++t)   // rows past the end of the weight read as zeros
+          tma_load_3d(S.sg + slot * kSlotBytes + t * kSignTileBytes, map, (c_lo + ci) * (kChunkCols / 8),
+                      row0 + t * kTileRows, j, &S.sfull[slot]);
+      };
+      // the packed signs do not depend on the Z' kernel: fill the tile ring before waiting for it
+      const int pre = min(total, kNS);
+      for (int g = 0; g < pre; ++g) load_signs(g, g);
       asm volatile("griddepcontrol.wait;" ::: "memory");
       for (int g = 0; g < total; ++g) {
         const int js = g / nch, ci = g - js * nch;
         const int j = (js + j_rot) % NB;
         if (g >= pre) {
-          const int slot = g % kNP, n = g / kNP;
+          const int slot = g % kNS, n = g / kNS;
           TR_BEGIN(t0);
-          if (n >= 1 && !mbar_wait(&S.sempty[slot], (n - 1) & 1)) { atomicExch(P.status, 7); break; }
+          if (n >= 1 && !mbar_wait_relaxed(&S.sempty[slot], (n - 1) & 1)) { atomicExch(P.status, 7); break; }
           TR_ADD(11, t0);
-          mbar_expect_tx(&S.sfull[slot], kSignTileBytes);
-          tma_load_3d(S.sg[slot], map, (c_lo + ci) * (kChunkCols / 8), rt * kTileRows, j, &S.sfull[slot]);
+          load_signs(g, slot);
         }
         if (P.dbg != 2) {
           const int slot = g % kNZ, n = g / kNZ;
-          if (n >= 1 && !mbar_wait(&S.zempty[slot], (n - 1) & 1)) { atomicExch(P.status, 1); break; }
+          if (n >= 1 && !mbar_wait_relaxed(&S.zempty[slot], (n - 1) & 1)) { atomicExch(P.status, 1); break; }
           const uint8_t* zsrc = P.zops + ((int64_t)(jb0 + j) * P.n_chunks + c_lo + ci) * kChunkBytes;
           mbar_expect_tx(&S.zfull[slot], kChunkBytes);
           bulk_g2s(S.zs[slot], zsrc, kChunkBytes, &S.zfull[slot]);
@@ -450,7 +504,8 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
       }
     }
   } else if (warp == kWarpMma || warp == kWarpMma + 1) {
-    // ---- MMA issuer e: words 8e .. 8e+7 of every chunk, accumulator D(e, block parity) --------
+    // ---- MMA issuer e: RT == 1: words 8e .. 8e+7 of every chunk; RT == 2: all 16 words for row
+    //      tile e; accumulator D(e, block parity) ------------------------------------------
     if (lane == 0 && P.dbg != 2) {
       const int e = warp - kWarpMma;
       if (e != 0) tr = nullptr;
@@ -471,10 +526,10 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
         TR_BEGIN(t1);
         if (!mbar_wait(&S.zfull[zslot], (g / kNZ) & 1)) { atomicExch(P.status, 2); ok = false; break; }
         TR_ADD(5, t1);
-        const uint32_t zaddr = smem_u32(S.zs[zslot]) + (uint32_t)e * 8u * 1024u;
+        const uint32_t zaddr = smem_u32(S.zs[zslot]) + (RT == 1 ? (uint32_t)e * 8u * 1024u : 0u);
         const uint32_t dcol = tbase + e * 64 + b * 32;
 #pragma unroll 1
-        for (int pp = 0; pp < 2; ++pp, ++it) {
+        for (int pp = 0; pp < kPP; ++pp, ++it) {
           const int slot = it & 1;
           TR_BEGIN(t2);
           if (P.dbg != 1 && !mbar_wait(&S.afull[e][slot], (it >> 1) & 1)) { atomicExch(P.status, 3); ok = false; break; }
@@ -498,14 +553,16 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
       TR_ADD(4, t_mma);
     }
   } else if (warp < kWarpMma) {
-    // ---- producer group e: one sign row per thread, bytes 32e .. 32e+31 of every tile row ------
+    // ---- producer group e: one sign row per thread.  RT == 1: bytes 32e .. 32e+31 of the row
+    //      of the only tile; RT == 2: all 64 bytes of the row of tile e ----------------------
     if (P.dbg != 1) {
       const int e = warp >> 2;
       if (e != 0) tr = nullptr;
       const int rtid = tid & (kTileRows - 1);
       const uint32_t lane_base = tbase + ((uint32_t)((warp & 3) * 32) << 16) + colA + e * 64;
       const int sw = (rtid >> 1) & 3;   // 64-byte swizzle of the TMA tile
-      const int off0 = rtid * 64 + (((e * 2) ^ sw) << 4), off1 = rtid * 64 + (((e * 2 + 1) ^ sw) << 4);
+      const int tile_off = (RT == 1 ? 0 : e * kSignTileBytes) + rtid * 64;
+      const int piece0 = (RT == 1 ? e * 2 : 0);
       // OR-constants of the eight bit classes, held in registers so that one LOP3 expands four signs
       uint32_t cc[8];
 #pragma unroll
@@ -514,27 +571,32 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
       TR_BEGIN(t_prod);
 #pragma unroll 1
       for (int g = 0; g < total && ok; ++g) {
-        const int slot_s = g % kNP;
+        const int slot_s = g % kNS;
         TR_BEGIN(t0);
-        const bool landed = __all_sync(0xFFFFFFFFu, mbar_wait(&S.sfull[slot_s], (g / kNP) & 1) ? 1 : 0);
+        const bool landed = mbar_wait_group(&S.sfull[slot_s], (g / kNS) & 1);
         TR_ADD(1, t0);
         if (!landed) { atomicExch(P.status, 8); ok = false; break; }
-        const uint4 v0 = *reinterpret_cast<const uint4*>(&S.sg[slot_s][off0]);
-        const uint4 v1 = *reinterpret_cast<const uint4*>(&S.sg[slot_s][off1]);
-        mbar_arrive(&S.sempty[slot_s]);   // the tile slot may be refilled once all 256 readers have their words
+        const uint8_t* srow = S.sg + slot_s * kSlotBytes + tile_off;
+        // two 16-byte pieces are in registers at a time; the slot may be refilled once all 256
+        // readers have taken their last piece
+        uint4 v[2];
 #pragma unroll
-        for (int pp = 0; pp < 2; ++pp) {
-          const uint4 v = pp ? v1 : v0;
-          const int it = g * 2 + pp, slot = it & 1;
+        for (int pp = 0; pp < kPP; ++pp) {
+          if ((pp & 1) == 0) {
+            v[0] = *reinterpret_cast<const uint4*>(srow + (((piece0 + pp) ^ sw) << 4));
+            v[1] = *reinterpret_cast<const uint4*>(srow + (((piece0 + pp + 1) ^ sw) << 4));
+            if (pp == kPP - 2) mbar_arrive(&S.sempty[slot_s]);
+          }
+          const int it = g * kPP + pp, slot = it & 1;
           TR_BEGIN(t2);
           uint32_t r[32];
-          const uint32_t wd[4] = {v.x, v.y, v.z, v.w};
+          const uint32_t wd[4] = {v[pp & 1].x, v[pp & 1].y, v[pp & 1].z, v[pp & 1].w};
 #pragma unroll
           for (int q = 0; q < 4; ++q) expand_word_c(wd[q], cc, r + q * 8);
           TR_ADD(3, t2);
           if (it >= 2 && P.dbg != 2) {
             TR_BEGIN(t1);
-            const bool got = __all_sync(0xFFFFFFFFu, mbar_wait(&S.aempty[e][slot], ((it >> 1) - 1) & 1) ? 1 : 0);
+            const bool got = mbar_wait_group(&S.aempty[e][slot], ((it >> 1) - 1) & 1);
             TR_ADD(2, t1);
             if (!got) { atomicExch(P.status, 4); ok = false; break; }
             tc_fence_after();
@@ -550,15 +612,16 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
       TR_ADD(0, t_prod);
     }
   } else if (warp >= kWarpEpi) {
-    // ---- epilogue warps: y[m] += sum_r U_j[m,r] (T[m,r] / s_r - K_r) per block, T = sum of the
-    //      hi and lo pieces of both issuers' accumulators ------------------------------------
+    // ---- epilogue warps: y[m] += sum_r U_j[m,r] (T[m,r] / s_r - K_r) per block; T = sum of the
+    //      hi and lo pieces (RT == 1: of both issuers' accumulators) -----------------------
     if (P.dbg == 0) {
     asm volatile("griddepcontrol.wait;" ::: "memory");   // constants below come from the Z' kernel
     const int quarter = warp & 3;                     // tensor-memory lanes this warp may read
     const int rtid = quarter * 32 + lane;
-    const int row = min(rt * kTileRows + rtid, M - 1);
     const uint32_t lane_base = tbase + ((uint32_t)(quarter * 32) << 16);
-    float yacc = 0.f;
+    float yacc[RT];
+#pragma unroll
+    for (int t = 0; t < RT; ++t) yacc[t] = 0.f;
     bool ok = true;
     TR_BEGIN(t_epi);
 #pragma unroll 1
@@ -566,9 +629,14 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
       const int j = (js + j_rot) % NB;
       const int b = js & 1;
       // operands of this block's epilogue, fetched while its MMAs run
-      const __half* u = reinterpret_cast<const __half*>(w.u) + (int64_t)j * w.u_block_stride + (int64_t)row * 16;
-      const uint4 u0 = __ldg(reinterpret_cast<const uint4*>(u));
-      const uint4 u1 = __ldg(reinterpret_cast<const uint4*>(u) + 1);
+      uint4 uq[RT][2];
+#pragma unroll
+      for (int t = 0; t < RT; ++t) {
+        const int row = min(row0 + t * kTileRows + rtid, M - 1);
+        const __half* u = reinterpret_cast<const __half*>(w.u) + (int64_t)j * w.u_block_stride + (int64_t)row * 16;
+        uq[t][0] = __ldg(reinterpret_cast<const uint4*>(u));
+        uq[t][1] = __ldg(reinterpret_cast<const uint4*>(u) + 1);
+      }
       float inv_mine = 0.f, k_mine = 0.f;
       if (lane < 16) {
         inv_mine = P.inv_scale[(int64_t)(jb0 + j) * 16 + lane];
@@ -576,56 +644,67 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
         for (int c = 0; c < nch; ++c) k_mine += kc[c * 16];
       }
       TR_BEGIN(t0);
-      const int mine = (mbar_wait(&S.dfull[0][b], (js >> 1) & 1) && mbar_wait(&S.dfull[1][b], (js >> 1) & 1)) ? 1 : 0;
-      TR_ADD(9, t0);
-      if (!__all_sync(0xFFFFFFFFu, mine)) { if (lane == 0) atomicExch(P.status, 5); ok = false; break; }
-      tc_fence_after();
-      // T[r] = hi + lo pieces of both issuers: four 16-column loads, summed as they arrive
-      float T[16];
-      {
-        uint32_t d[16];
-        tmem_ld16(lane_base + b * 32, d);
-        tmem_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 16; ++i) T[i] = __uint_as_float(d[i]);
-        tmem_ld16(lane_base + b * 32 + 16, d);
-        tmem_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 16; ++i) T[i] += __uint_as_float(d[i]);
-        tmem_ld16(lane_base + 64 + b * 32, d);
-        tmem_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 16; ++i) T[i] += __uint_as_float(d[i]);
-        tmem_ld16(lane_base + 64 + b * 32 + 16, d);
-        tmem_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 16; ++i) T[i] += __uint_as_float(d[i]);
+      if (RT == 1) {
+        const bool both = mbar_wait_warp_relaxed(&S.dfull[0][b], (js >> 1) & 1) && mbar_wait_warp_relaxed(&S.dfull[1][b], (js >> 1) & 1);
+        if (!both) { if (lane == 0) atomicExch(P.status, 5); ok = false; break; }
       }
+      TR_ADD(9, t0);
+#pragma unroll
+      for (int t = 0; t < RT; ++t) {
+        if (RT == 2) {
+          if (!mbar_wait_warp_relaxed(&S.dfull[t][b], (js >> 1) & 1)) { if (lane == 0) atomicExch(P.status, 5); ok = false; break; }
+        }
+        tc_fence_after();
+        const uint32_t* uw = reinterpret_cast<const uint32_t*>(&uq[t][0]);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {   // ranks 8h .. 8h+7
+          float T[8];
+          uint32_t d0[8], d1[8];
+          const uint32_t c0 = lane_base + (RT == 1 ? 0 : t * 64) + b * 32 + h * 8;
+          tmem_ld8(c0, d0);        // hi piece
+          tmem_ld8(c0 + 16, d1);   // lo piece
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) T[i] = __uint_as_float(d0[i]) + __uint_as_float(d1[i]);
+          if (RT == 1) {           // second issuer's accumulator (other K half)
+            tmem_ld8(c0 + 64, d0);
+            tmem_ld8(c0 + 64 + 16, d1);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 8; ++i) T[i] += __uint_as_float(d0[i]) + __uint_as_float(d1[i]);
+          }
+#pragma unroll
+          for (int rr = 0; rr < 4; ++rr) {
+            const int r0 = 8 * h + 2 * rr;
+            const __half2 h2 = *reinterpret_cast<const __half2*>(&uw[4 * h + rr]);
+            const float i0 = __shfl_sync(0xFFFFFFFFu, inv_mine, r0), i1 = __shfl_sync(0xFFFFFFFFu, inv_mine, r0 + 1);
+            const float k0 = __shfl_sync(0xFFFFFFFFu, k_mine, r0), k1 = __shfl_sync(0xFFFFFFFFu, k_mine, r0 + 1);
+            yacc[t] = fmaf(__low2float(h2), T[2 * rr] * i0 - k0, yacc[t]);
+            yacc[t] = fmaf(__high2float(h2), T[2 * rr + 1] * i1 - k1, yacc[t]);
+          }
+        }
+      }
+      if (!ok) break;
       tc_fence_before();
       mbar_arrive(&S.dempty[b]);
-      const uint32_t uw[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
-#pragma unroll
-      for (int rr = 0; rr < 8; ++rr) {
-        const __half2 h2 = *reinterpret_cast<const __half2*>(&uw[rr]);
-        const float i0 = __shfl_sync(0xFFFFFFFFu, inv_mine, 2 * rr), i1 = __shfl_sync(0xFFFFFFFFu, inv_mine, 2 * rr + 1);
-        const float k0 = __shfl_sync(0xFFFFFFFFu, k_mine, 2 * rr), k1 = __shfl_sync(0xFFFFFFFFu, k_mine, 2 * rr + 1);
-        yacc = fmaf(__low2float(h2), T[2 * rr] * i0 - k0, yacc);
-        yacc = fmaf(__high2float(h2), T[2 * rr + 1] * i1 - k1, yacc);
-      }
     }
     TR_ADD(10, t_epi);
-    const int m = rt * kTileRows + rtid;
-    if (nsplit == 1) {
-      if (m < M) {
-        float v = ok ? yacc : __int_as_float(0x7FC00000);   // NaN marks a tile that was given up
-        if (w.bias) v += __half2float(reinterpret_cast<const __half*>(w.bias)[m]);
-        P.y[wi][m] = __float2half_rn(v);
+#pragma unroll
+    for (int t = 0; t < RT; ++t) {
+      const int m = row0 + t * kTileRows + rtid;
+      const float v0 = ok ? yacc[t] : __int_as_float(0x7FC00000);   // NaN marks a tile that was given up
+      if (nsplit == 1) {
+        if (m < M) {
+          float v = v0;
+          if (w.bias) v += __half2float(reinterpret_cast<const __half*>(w.bias)[m]);
+          P.y[wi][m] = __float2half_rn(v);
+        }
+      } else {
+        float* part = P.partials + P.part_base[wi] + ((int64_t)rt * nsplit + split) * (RT * kTileRows);
+        part[t * kTileRows + rtid] = v0;
       }
-    } else {
-      float* part = P.partials + P.part_base[wi] + ((int64_t)rt * nsplit + split) * kTileRows;
-      part[rtid] = ok ? yacc : __int_as_float(0x7FC00000);
-      __threadfence();
     }
+    if (nsplit > 1) __threadfence();
     }
   }
 
@@ -648,14 +727,14 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
     S.last = (old == nsplit - 1);
   }
   __syncthreads();
-  if (!S.last || tid >= kTileRows) return;
-  // the last CTA of this row tile adds the column-split partial sums in a fixed order
+  if (!S.last || tid >= RT * kTileRows) return;
+  // the last CTA of this row group adds the column-split partial sums in a fixed order
   __threadfence();
-  const int m = rt * kTileRows + tid;
+  const int m = row0 + tid;
   if (m >= M) return;
-  const float* all = P.partials + P.part_base[wi] + (int64_t)rt * nsplit * kTileRows;
+  const float* all = P.partials + P.part_base[wi] + (int64_t)rt * nsplit * (RT * kTileRows);
   float sum = 0.f;
-  for (int i = 0; i < nsplit; ++i) sum += __ldcg(all + (int64_t)i * kTileRows + tid);
+  for (int i = 0; i < nsplit; ++i) sum += __ldcg(all + (int64_t)i * (RT * kTileRows) + tid);
   if (w.bias) sum += __half2float(reinterpret_cast<const __half*>(w.bias)[m]);
   P.y[wi][m] = __float2half_rn(sum);
 }
@@ -664,9 +743,12 @@ struct TcPlan {
   TcParams P;
   int64_t bytes;
   int total_blocks, total_items;
+  int row_tiles;                    // RT: 128-row tiles per CTA (1 or 2)
   int64_t absmax_off[kMaxGroup];
   int64_t status_off;
 };
+
+static int g_force_rt = 0;   // 0 = choose, 1 / 2 = forced (tuning)
 
 void make_tc_plan(const bsb_weight* ws, int n, TcPlan& pl) {
   TcParams& P = pl.P;
@@ -676,8 +758,17 @@ void make_tc_plan(const bsb_weight* ws, int n, TcPlan& pl) {
   P.n_chunks = (int)ceil_div64(N, kChunkCols);
   // CTAs wanted: about two per multiprocessor (both stay resident and share its tensor pipe)
   const int target = sm_count() * 2;
-  int total_tiles = 0;
-  for (int i = 0; i < n; ++i) total_tiles += (int)ceil_div64(ws[i].out_features, kTileRows);
+  int tiles128 = 0, tiles256 = 0;
+  for (int i = 0; i < n; ++i) {
+    tiles128 += (int)ceil_div64(ws[i].out_features, kTileRows);
+    tiles256 += (int)ceil_div64(ws[i].out_features, 2 * kTileRows);
+  }
+  // two row tiles per CTA halve the Z' traffic; taken when the column splits still give every
+  // multiprocessor its two CTAs
+  int RT = (tiles256 * P.n_chunks >= target) ? 2 : 1;
+  if (g_force_rt) RT = g_force_rt;
+  pl.row_tiles = RT;
+  const int total_tiles = RT == 2 ? tiles256 : tiles128;
   int S = (int)ceil_div64(target, total_tiles > 0 ? total_tiles : 1);
   if (S * total_tiles > target && S > 1) --S;          // round down: never more CTAs than slots
   if (S > P.n_chunks) S = P.n_chunks;
@@ -688,7 +779,7 @@ void make_tc_plan(const bsb_weight* ws, int n, TcPlan& pl) {
   int64_t part_floats = 0;
   for (int i = 0; i < n; ++i) {
     P.w[i] = ws[i];
-    const int n_rt = (int)ceil_div64(ws[i].out_features, kTileRows);
+    const int n_rt = (int)ceil_div64(ws[i].out_features, RT * kTileRows);
     P.splits[i] = S;
     P.chunks_per_item[i] = cpi;
     P.item_base[i] = items;
@@ -698,7 +789,7 @@ void make_tc_plan(const bsb_weight* ws, int n, TcPlan& pl) {
     items += n_rt * S;
     tiles += n_rt;
     blks += ws[i].blocks;
-    part_floats += (int64_t)n_rt * S * kTileRows;
+    part_floats += (int64_t)n_rt * S * RT * kTileRows;
   }
   P.item_base[n] = items;
   P.tile_base[n] = tiles;
@@ -775,7 +866,10 @@ static unsigned long long* g_trace = nullptr;
 static int g_dbg = 0;
 static int g_pdl = 0;   // measured neutral-to-slightly-worse on the decode benchmark; kept selectable
 void gemv_tc5_set_pdl(int on) { g_pdl = on; }
-void gemv_tc5_set_dbg(int m) { g_dbg = m; }
+void gemv_tc5_set_dbg(int m) {
+  if (m >= 200 && m <= 202) g_force_rt = m - 200;   // row tiles per CTA: 200 = choose, 201 / 202 = forced
+  else g_dbg = m;
+}
 void gemv_tc5_set_trace(unsigned long long* p) { g_trace = p; }
 
 bool gemv_tc5_supported(const bsb_weight& w) {
@@ -817,7 +911,8 @@ int launch_gemv_tc5(const bsb_weight* ws, int n_weights, const __half* x, __half
   int dev = 0;
   BSB_CUDA(cudaGetDevice(&dev));
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    BSB_CUDA(cudaFuncSetAttribute(gemv_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SmemLayout) + 1024));
+    BSB_CUDA(cudaFuncSetAttribute(gemv_tc5_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SmemLayout) + 1024));
+    BSB_CUDA(cudaFuncSetAttribute(gemv_tc5_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SmemLayout) + 1024));
     attr_set[dev] = true;
   }
   TcParams& P = pl.P;
@@ -856,7 +951,8 @@ int launch_gemv_tc5(const bsb_weight* ws, int n_weights, const __half* x, __half
     attr[0].val.programmaticStreamSerializationAllowed = g_pdl ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t le = cudaLaunchKernelEx(&cfg, gemv_tc5_kernel, P);
+    cudaError_t le = pl.row_tiles == 2 ? cudaLaunchKernelEx(&cfg, gemv_tc5_kernel<2>, P)
+                                       : cudaLaunchKernelEx(&cfg, gemv_tc5_kernel<1>, P);
     if (le != cudaSuccess) {
       set_error("launch of gemv_tc5_kernel failed: %s", cudaGetErrorString(le));
       return BSB_ECUDA;
