@@ -65,20 +65,18 @@ struct alignas(64) TcParams {
   __half* y[kMaxGroup];
   int n_weights;
   int n_chunks;                    // ceil(in / 512)
-  int item_base[kMaxGroup + 1];
-  int tile_base[kMaxGroup + 1];    // first 128-row tile of each weight
+  int step_base[kMaxGroup + 1];    // first work step of each weight; a step = (row group, block, chunk)
+  int seg_base[kMaxGroup + 1];     // first row group of each weight (index of its counter)
   int blk_base[kMaxGroup + 1];
-  int splits[kMaxGroup];
-  int chunks_per_item[kMaxGroup];
+  int steps_per_cta;               // every CTA takes this many consecutive steps (the last one fewer)
   uint8_t* zops;     // [(weight,block)][chunk][16 KB]
   float* kconst;     // [(weight,block)][chunk][16]
   float* inv_scale;  // [(weight,block)][16]
-  int* counters;     // [row tile]
+  int* counters;     // [row group]: CTAs that have delivered their partial sums
   int* status;       // 0 = fine, else the code of the wait that gave up
   unsigned long long* trace;  // optional [CTA][16] cycle counters (debug), or nullptr
   int dbg;           // 0 = normal; 1 = MMA side only, 2 = producer side only (timing experiments, wrong results)
-  float* partials;
-  int64_t part_base[kMaxGroup];
+  float* partials;   // [CTA][2][RT * 128]: sums of a row group that the CTA shares with other CTAs
 };
 
 // ------------------------------------------------------------------ PTX helpers
@@ -276,7 +274,7 @@ __global__ void __launch_bounds__(256) zprep_tc5_kernel(const __grid_constant__ 
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   if (blockIdx.x == 0 && blockIdx.y == 0) {
-    for (int i = tid; i < P.tile_base[P.n_weights]; i += blockDim.x) P.counters[i] = 0;
+    for (int i = tid; i < P.seg_base[P.n_weights]; i += blockDim.x) P.counters[i] = 0;
     if (tid == 0) *P.status = 0;
   }
   // issue every load first: Vt and x words of this thread, then the pass over x for max |x|
@@ -377,9 +375,14 @@ __global__ void __launch_bounds__(256) zprep_tc5_kernel(const __grid_constant__ 
 #endif
 
 // ------------------------------------------------------------------ main kernel
-// One CTA = RT 128-row tiles x one column split of one weight, ALL active blocks: set-up,
-// pipeline fill and the final reduction are paid once and the fp32 output of a row is
-// accumulated over blocks in a register of its epilogue thread.
+// Work is the sequence of STEPS (weight, row group, block, chunk) in that order, a step being one
+// 512-column chunk of one block for the RT 128-row tiles of a row group.  Every CTA takes the same
+// number of consecutive steps (stream-K): the grid fills both CTA slots of every multiprocessor
+// whatever the shape, at the price that a row group may be shared by several CTAs.  Within its
+// range a CTA meets BLOCK SEGMENTS (consecutive chunks of one block: one accumulate / epilogue
+// cycle) and ROW SEGMENTS (consecutive block segments of one row group: one output flush).  A row
+// group that lies wholly inside one CTA is written directly; otherwise each CTA delivers fp32
+// partial sums and the last CTA to arrive adds them in CTA order (deterministic, no float atomics).
 //
 // A single thread can only issue a tcgen05.mma every ~28 ns (and a commit costs it ~60 ns)
 // while the tensor pipe itself accepts several such streams side by side, so the CTA runs TWO
@@ -388,9 +391,8 @@ __global__ void __launch_bounds__(256) zprep_tc5_kernel(const __grid_constant__ 
 //   RT == 1: pipeline e takes the e-th 32 bytes of every 64-byte sign row (K halves of one row
 //            tile); the epilogue adds the two accumulators.
 //   RT == 2: pipeline e takes row tile e (all 64 bytes of a row); both pipelines read the SAME
-//            Z' slab, which halves the Z' traffic from L2 per sign byte -- with one tile per CTA
-//            that traffic is twice the sign traffic and bounds the kernel.
-// Every D is double buffered across blocks.  Tensor-memory columns:
+//            Z' slab, which halves the Z' traffic from L2 per sign byte.
+// Every D is double buffered across block segments.  Tensor-memory columns:
 //   D(e, b) = e*64 + b*32           (4 x 32)
 //   A(e, s) = 128 + e*64 + s*32     (2 issuers x 2 stages x 4 MMAs)
 constexpr int kSignRingBytes = 6 * kSignTileBytes;
@@ -400,38 +402,61 @@ struct __align__(1024) SmemLayout {
   uint64_t afull[2][2], aempty[2][2], zfull[kNZ], zempty[kNZ], sfull[6], sempty[6], dfull[2][2], dempty[2];
   unsigned long long trace[16];
   uint32_t tmem_base;
+  int n_pending;
+  int pending[2][2];                    // row groups shared with other CTAs (at most the first and the last): weight, row group
   int last;
 };
 
 constexpr int kWarpMma = 8;     // warps 8, 9: MMA issuers 0, 1
-constexpr int kWarpLoad = 10;   // tensor-memory allocation, TMA / bulk loads
+constexpr int kWarpLoad = 10;   // warp 10: tensor-memory allocation, sign tiles (TMA); warp 11: Z' slabs (bulk copies)
 constexpr int kWarpEpi = 12;    // warps 12-15: epilogue (tensor-memory lane quarters 0-3)
+
+// position of a step in (weight, row group, block, chunk) order
+struct Walk {
+  int wi, rg, js, ci, NB, n_rg;
+  __device__ __forceinline__ void init(const TcParams& P, int step, int rows_per_group) {
+    wi = 0;
+    while (wi + 1 < P.n_weights && step >= P.step_base[wi + 1]) ++wi;
+    load(P, rows_per_group);
+    const int local = step - P.step_base[wi];
+    const int per_rg = NB * P.n_chunks;
+    rg = local / per_rg;
+    const int rem = local - rg * per_rg;
+    js = rem / P.n_chunks;
+    ci = rem - js * P.n_chunks;
+  }
+  __device__ __forceinline__ void load(const TcParams& P, int rows_per_group) {
+    NB = P.w[wi].blocks;
+    n_rg = (P.w[wi].out_features + rows_per_group - 1) / rows_per_group;
+  }
+  // advance by n chunks that stay inside the current block
+  __device__ __forceinline__ void advance(const TcParams& P, int rows_per_group, int n = 1) {
+    ci += n;
+    if (ci >= P.n_chunks) {
+      ci = 0;
+      if (++js == NB) {
+        js = 0;
+        if (++rg == n_rg) {
+          rg = 0;
+          if (wi + 1 < P.n_weights) { ++wi; load(P, rows_per_group); }
+        }
+      }
+    }
+  }
+};
 
 template <int RT>
 __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_constant__ TcParams P) {
-  constexpr int kSlotBytes = RT * kSignTileBytes;   // one ring slot = the RT sign tiles of a chunk
+  constexpr int kSlotBytes = RT * kSignTileBytes;   // one ring slot = the RT sign tiles of a step
   constexpr int kNS = 6 / RT;                       // ring slots
-  constexpr int kPP = 2 * RT;                       // operand stages (4 MMAs each) per chunk and pipeline
+  constexpr int kPP = 2 * RT;                       // operand stages (4 MMAs each) per step and pipeline
+  constexpr int kRows = RT * kTileRows;             // rows of a row group
   extern __shared__ uint8_t smem_raw[];
   SmemLayout& S = *reinterpret_cast<SmemLayout*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
 
-  int wi = 0;
-  while (wi + 1 < P.n_weights && (int)blockIdx.x >= P.item_base[wi + 1]) ++wi;
-  const bsb_weight& w = P.w[wi];
-  const int nsplit = P.splits[wi];
-  const int item = blockIdx.x - P.item_base[wi];
-  const int split = item % nsplit;
-  const int rt = item / nsplit;               // group of RT row tiles
-  const int row0 = rt * RT * kTileRows;
-  const int M = w.out_features, NB = w.blocks;
-  const int c_lo = split * P.chunks_per_item[wi];
-  const int c_hi = min(P.n_chunks, c_lo + P.chunks_per_item[wi]);
-  const int nch = c_hi - c_lo;
-  const int total = NB * nch;                 // chunks this CTA streams, block-major
-  const int jb0 = P.blk_base[wi];
-  // every row group walks the blocks in a different rotation, so that co-running CTAs do not
-  // all pull the same Z' slab out of the same L2 lines at the same moment
-  const int j_rot = rt % NB;
+  const int NCH = P.n_chunks;
+  const int step0 = blockIdx.x * P.steps_per_cta;
+  const int total = min(P.steps_per_cta, P.step_base[P.n_weights] - step0);   // steps of this CTA
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // trace slots: 0-3 producer group 0 (total, tile wait, ring wait, expand+store), 4-8 issuer 0 (total,
@@ -449,6 +474,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
   }
   if (tid < 16) S.trace[tid] = 0;
   if (tid == 0) {
+    S.n_pending = 0;
     for (int e = 0; e < 2; ++e)
       for (int i = 0; i < 2; ++i) {
         mbar_init(&S.afull[e][i], kTileRows);
@@ -468,57 +494,57 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
   if (warp == 0) TR_ADD(13, t_cta);
 
   if (warp == kWarpLoad) {
-    // ---- loader: Z' slabs (bulk copy) and sign tiles (tiled TMA), each with its own ring ----
+    // ---- sign loader: tiled TMA into the tile ring (the packed signs do not depend on the Z'
+    //      kernel, so this role never waits for it) -------------------------------------------
     if (lane == 0) {
-      const CUtensorMap* map = &P.sign_map[wi];
-      auto load_signs = [&](int g, int slot) {
-        const int js = g / nch, ci = g - js * nch;
-        const int j = (js + j_rot) % NB;
+      Walk wk;
+      wk.init(P, step0, kRows);
+      for (int g = 0; g < total; ++g) {
+        const int slot = g % kNS, n = g / kNS;
+        TR_BEGIN(t0);
+        if (n >= 1 && !mbar_wait_relaxed(&S.sempty[slot], (n - 1) & 1)) { atomicExch(P.status, 7); break; }
+        TR_ADD(11, t0);
         mbar_expect_tx(&S.sfull[slot], kSlotBytes);
 #pragma unroll
         for (int t = 0; t < RT; ++t)   // rows past the end of the weight read as zeros
-          tma_load_3d(S.sg + slot * kSlotBytes + t * kSignTileBytes, map, (c_lo + ci) * (kChunkCols / 8),
-                      row0 + t * kTileRows, j, &S.sfull[slot]);
-      };
-      // the packed signs do not depend on the Z' kernel: fill the tile ring before waiting for it
-      const int pre = min(total, kNS);
-      for (int g = 0; g < pre; ++g) load_signs(g, g);
+          tma_load_3d(S.sg + slot * kSlotBytes + t * kSignTileBytes, &P.sign_map[wk.wi], wk.ci * (kChunkCols / 8),
+                      wk.rg * kRows + t * kTileRows, wk.js, &S.sfull[slot]);
+        wk.advance(P, kRows);
+      }
+    }
+  } else if (warp == kWarpLoad + 1) {
+    // ---- Z' loader: one 16 KB bulk copy per step ---------------------------------------------
+    if (lane == 0 && P.dbg != 2) {
       asm volatile("griddepcontrol.wait;" ::: "memory");
+      Walk wk;
+      wk.init(P, step0, kRows);
       for (int g = 0; g < total; ++g) {
-        const int js = g / nch, ci = g - js * nch;
-        const int j = (js + j_rot) % NB;
-        if (g >= pre) {
-          const int slot = g % kNS, n = g / kNS;
-          TR_BEGIN(t0);
-          if (n >= 1 && !mbar_wait_relaxed(&S.sempty[slot], (n - 1) & 1)) { atomicExch(P.status, 7); break; }
-          TR_ADD(11, t0);
-          load_signs(g, slot);
-        }
-        if (P.dbg != 2) {
-          const int slot = g % kNZ, n = g / kNZ;
-          if (n >= 1 && !mbar_wait_relaxed(&S.zempty[slot], (n - 1) & 1)) { atomicExch(P.status, 1); break; }
-          const uint8_t* zsrc = P.zops + ((int64_t)(jb0 + j) * P.n_chunks + c_lo + ci) * kChunkBytes;
-          mbar_expect_tx(&S.zfull[slot], kChunkBytes);
-          bulk_g2s(S.zs[slot], zsrc, kChunkBytes, &S.zfull[slot]);
-        }
+        const int slot = g % kNZ, n = g / kNZ;
+        if (n >= 1 && !mbar_wait_relaxed(&S.zempty[slot], (n - 1) & 1)) { atomicExch(P.status, 1); break; }
+        const uint8_t* zsrc = P.zops + ((int64_t)(P.blk_base[wk.wi] + wk.js) * NCH + wk.ci) * kChunkBytes;
+        mbar_expect_tx(&S.zfull[slot], kChunkBytes);
+        bulk_g2s(S.zs[slot], zsrc, kChunkBytes, &S.zfull[slot]);
+        wk.advance(P, kRows);
       }
     }
   } else if (warp == kWarpMma || warp == kWarpMma + 1) {
     // ---- MMA issuer e: RT == 1: words 8e .. 8e+7 of every chunk; RT == 2: all 16 words for row
-    //      tile e; accumulator D(e, block parity) ------------------------------------------
+    //      tile e; accumulator D(e, parity of the block segment) -----------------------------
     if (lane == 0 && P.dbg != 2) {
       const int e = warp - kWarpMma;
       if (e != 0) tr = nullptr;
       const uint32_t idesc = make_idesc_f8(128, 32);
-      int it = 0;
+      Walk wk;
+      wk.init(P, step0, kRows);
+      int it = 0, bs = 0;       // operand stages and block segments so far
+      bool first = true;        // first step of a block segment
       bool ok = true;
       TR_BEGIN(t_mma);
       for (int g = 0; g < total && ok; ++g) {
-        const int js = g / nch, ci = g - js * nch;
-        const int b = js & 1;
-        if (ci == 0 && js >= 2) {
+        const int b = bs & 1;
+        if (first && bs >= 2) {
           TR_BEGIN(t0);
-          if (!mbar_wait(&S.dempty[b], ((js >> 1) - 1) & 1)) { atomicExch(P.status, 6); ok = false; break; }
+          if (!mbar_wait(&S.dempty[b], ((bs >> 1) - 1) & 1)) { atomicExch(P.status, 6); ok = false; break; }
           TR_ADD(7, t0);
           tc_fence_after();
         }
@@ -540,7 +566,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
           const uint32_t acol = tbase + colA + e * 64 + slot * 32;
 #pragma unroll
           for (int ww = 0; ww < 4; ++ww) {
-            mma_ts_f8(dcol, acol + ww * 8, bdesc, idesc, (ci > 0 || pp > 0 || ww > 0) ? 1u : 0u);
+            mma_ts_f8(dcol, acol + ww * 8, bdesc, idesc, (!first || pp > 0 || ww > 0) ? 1u : 0u);
             bdesc += 1024u >> 4;   // next 1 KB operand tile (address field counts 16-byte units)
           }
           mma_commit(&S.aempty[e][slot]);
@@ -548,7 +574,10 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
         }
         if (!ok) break;
         mma_commit(&S.zempty[zslot]);
-        if (ci == nch - 1) mma_commit(&S.dfull[e][b]);
+        const bool seg_end = (wk.ci == NCH - 1) || (g == total - 1);
+        if (seg_end) { mma_commit(&S.dfull[e][b]); ++bs; }
+        first = seg_end;
+        wk.advance(P, kRows);
       }
       TR_ADD(4, t_mma);
     }
@@ -612,8 +641,8 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
       TR_ADD(0, t_prod);
     }
   } else if (warp >= kWarpEpi) {
-    // ---- epilogue warps: y[m] += sum_r U_j[m,r] (T[m,r] / s_r - K_r) per block; T = sum of the
-    //      hi and lo pieces (RT == 1: of both issuers' accumulators) -----------------------
+    // ---- epilogue warps: y[m] += sum_r U_j[m,r] (T[m,r] / s_r - K_r) per block segment; T = sum
+    //      of the hi and lo pieces (RT == 1: of both issuers' accumulators) ------------------
     if (P.dbg == 0) {
     asm volatile("griddepcontrol.wait;" ::: "memory");   // constants below come from the Z' kernel
     const int quarter = warp & 3;                     // tensor-memory lanes this warp may read
@@ -623,12 +652,21 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
 #pragma unroll
     for (int t = 0; t < RT; ++t) yacc[t] = 0.f;
     bool ok = true;
+    Walk wk;
+    wk.init(P, step0, kRows);
+    bool whole = (wk.js == 0 && wk.ci == 0);   // the current row group began inside this CTA
+    bool first_seg = true;                    // partial-sum slot 0 belongs to the CTA's first row segment, slot 1 to any later one
+    int n_pend = 0;
     TR_BEGIN(t_epi);
 #pragma unroll 1
-    for (int js = 0; js < NB; ++js) {
-      const int j = (js + j_rot) % NB;
-      const int b = js & 1;
-      // operands of this block's epilogue, fetched while its MMAs run
+    for (int g = 0, bs = 0; g < total; ++bs) {
+      const int len = min(NCH - wk.ci, total - g);    // chunks of this block segment
+      const bsb_weight& w = P.w[wk.wi];
+      const int M = w.out_features;
+      const int j = wk.js, b = bs & 1;
+      const int row0 = wk.rg * kRows;
+      const int jb = P.blk_base[wk.wi] + j;
+      // operands of this block segment's epilogue, fetched while its MMAs run
       uint4 uq[RT][2];
 #pragma unroll
       for (int t = 0; t < RT; ++t) {
@@ -639,20 +677,20 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
       }
       float inv_mine = 0.f, k_mine = 0.f;
       if (lane < 16) {
-        inv_mine = P.inv_scale[(int64_t)(jb0 + j) * 16 + lane];
-        const float* kc = P.kconst + ((int64_t)(jb0 + j) * P.n_chunks + c_lo) * 16 + lane;
-        for (int c = 0; c < nch; ++c) k_mine += kc[c * 16];
+        inv_mine = P.inv_scale[(int64_t)jb * 16 + lane];
+        const float* kc = P.kconst + ((int64_t)jb * NCH + wk.ci) * 16 + lane;
+        for (int c = 0; c < len; ++c) k_mine += kc[c * 16];
       }
       TR_BEGIN(t0);
       if (RT == 1) {
-        const bool both = mbar_wait_warp_relaxed(&S.dfull[0][b], (js >> 1) & 1) && mbar_wait_warp_relaxed(&S.dfull[1][b], (js >> 1) & 1);
+        const bool both = mbar_wait_warp_relaxed(&S.dfull[0][b], (bs >> 1) & 1) && mbar_wait_warp_relaxed(&S.dfull[1][b], (bs >> 1) & 1);
         if (!both) { if (lane == 0) atomicExch(P.status, 5); ok = false; break; }
       }
       TR_ADD(9, t0);
 #pragma unroll
       for (int t = 0; t < RT; ++t) {
         if (RT == 2) {
-          if (!mbar_wait_warp_relaxed(&S.dfull[t][b], (js >> 1) & 1)) { if (lane == 0) atomicExch(P.status, 5); ok = false; break; }
+          if (!mbar_wait_warp_relaxed(&S.dfull[t][b], (bs >> 1) & 1)) { if (lane == 0) atomicExch(P.status, 5); ok = false; break; }
         }
         tc_fence_after();
         const uint32_t* uw = reinterpret_cast<const uint32_t*>(&uq[t][0]);
@@ -687,24 +725,45 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
       if (!ok) break;
       tc_fence_before();
       mbar_arrive(&S.dempty[b]);
+      g += len;
+      // end of the row segment: the row group ends here, or the CTA does
+      const bool group_end = (wk.js == wk.NB - 1) && (wk.ci + len == NCH);
+      if (group_end || g == total) {
+        const bool direct = whole && group_end;
+        float* part = P.partials + ((int64_t)blockIdx.x * 2 + (first_seg ? 0 : 1)) * kRows;
+#pragma unroll
+        for (int t = 0; t < RT; ++t) {
+          const int m = row0 + t * kTileRows + rtid;
+          if (direct) {
+            if (m < M) {
+              float v = yacc[t];
+              if (w.bias) v += __half2float(reinterpret_cast<const __half*>(w.bias)[m]);
+              P.y[wk.wi][m] = __float2half_rn(v);
+            }
+          } else {
+            part[t * kTileRows + rtid] = yacc[t];
+          }
+          yacc[t] = 0.f;
+        }
+        if (!direct) {
+          __threadfence();
+          if (rtid == 0) {
+            S.pending[n_pend][0] = wk.wi;
+            S.pending[n_pend][1] = wk.rg;
+            S.n_pending = n_pend + 1;
+          }
+          ++n_pend;
+        }
+        whole = true;
+        first_seg = false;
+      }
+      wk.advance(P, kRows, len);
     }
     TR_ADD(10, t_epi);
-#pragma unroll
-    for (int t = 0; t < RT; ++t) {
-      const int m = row0 + t * kTileRows + rtid;
-      const float v0 = ok ? yacc[t] : __int_as_float(0x7FC00000);   // NaN marks a tile that was given up
-      if (nsplit == 1) {
-        if (m < M) {
-          float v = v0;
-          if (w.bias) v += __half2float(reinterpret_cast<const __half*>(w.bias)[m]);
-          P.y[wi][m] = __float2half_rn(v);
-        }
-      } else {
-        float* part = P.partials + P.part_base[wi] + ((int64_t)rt * nsplit + split) * (RT * kTileRows);
-        part[t * kTileRows + rtid] = v0;
-      }
+    if (!ok) {
+      // a wait gave up: mark what this CTA would have written (NaN), nothing is reduced from it
+      S.n_pending = 0;
     }
-    if (nsplit > 1) __threadfence();
     }
   }
 
@@ -720,23 +779,37 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
     __syncwarp();
     tmem_dealloc(tbase, kTmemCols);
   }
-  if (nsplit == 1) return;
+  // ---- shared row groups: the last CTA to deliver adds the partial sums in CTA order ------
+  const int n_pending = S.n_pending;
+  if (n_pending == 0) return;
   asm volatile("griddepcontrol.wait;" ::: "memory");     // the counters were zeroed by the Z' kernel
-  if (tid == 0) {
-    const int old = atomicAdd(&P.counters[P.tile_base[wi] + rt], 1);
-    S.last = (old == nsplit - 1);
+  const int L = P.steps_per_cta;
+  for (int q = 0; q < n_pending; ++q) {
+    const int wi = S.pending[q][0], rg = S.pending[q][1];
+    const bsb_weight& w = P.w[wi];
+    const int per_rg = w.blocks * NCH;
+    const int gs = P.step_base[wi] + rg * per_rg, ge = gs + per_rg;   // steps of the row group
+    const int c_first = gs / L, c_last = (ge - 1) / L;
+    __syncthreads();
+    if (tid == 0) {
+      const int old = atomicAdd(&P.counters[P.seg_base[wi] + rg], 1);
+      S.last = (old == c_last - c_first);
+    }
+    __syncthreads();
+    if (!S.last) continue;
+    __threadfence();
+    const int m = rg * kRows + tid;
+    if (tid < kRows && m < w.out_features) {
+      float sum = 0.f;
+      for (int c = c_first; c <= c_last; ++c) {
+        // the row group is CTA c's first row segment unless it starts after c's first step
+        const int slot = (gs <= c * L) ? 0 : 1;
+        sum += __ldcg(P.partials + ((int64_t)c * 2 + slot) * kRows + tid);
+      }
+      if (w.bias) sum += __half2float(reinterpret_cast<const __half*>(w.bias)[m]);
+      P.y[wi][m] = __float2half_rn(sum);
+    }
   }
-  __syncthreads();
-  if (!S.last || tid >= RT * kTileRows) return;
-  // the last CTA of this row group adds the column-split partial sums in a fixed order
-  __threadfence();
-  const int m = row0 + tid;
-  if (m >= M) return;
-  const float* all = P.partials + P.part_base[wi] + (int64_t)rt * nsplit * (RT * kTileRows);
-  float sum = 0.f;
-  for (int i = 0; i < nsplit; ++i) sum += __ldcg(all + (int64_t)i * (RT * kTileRows) + tid);
-  if (w.bias) sum += __half2float(reinterpret_cast<const __half*>(w.bias)[m]);
-  P.y[wi][m] = __float2half_rn(sum);
 }
 
 struct TcPlan {
@@ -749,6 +822,7 @@ struct TcPlan {
 };
 
 static int g_force_rt = 0;   // 0 = choose, 1 / 2 = forced (tuning)
+constexpr int kMinStepsPair = 4;
 
 void make_tc_plan(const bsb_weight* ws, int n, TcPlan& pl) {
   TcParams& P = pl.P;
@@ -756,44 +830,40 @@ void make_tc_plan(const bsb_weight* ws, int n, TcPlan& pl) {
   P.n_weights = n;
   const int N = ws[0].in_features;
   P.n_chunks = (int)ceil_div64(N, kChunkCols);
-  // CTAs wanted: about two per multiprocessor (both stay resident and share its tensor pipe)
+  // CTAs wanted: two per multiprocessor (both stay resident and share its tensor pipe)
   const int target = sm_count() * 2;
-  int tiles128 = 0, tiles256 = 0;
+  int64_t steps1 = 0, steps2 = 0;
   for (int i = 0; i < n; ++i) {
-    tiles128 += (int)ceil_div64(ws[i].out_features, kTileRows);
-    tiles256 += (int)ceil_div64(ws[i].out_features, 2 * kTileRows);
+    steps1 += ceil_div64(ws[i].out_features, kTileRows) * ws[i].blocks * P.n_chunks;
+    steps2 += ceil_div64(ws[i].out_features, 2 * kTileRows) * ws[i].blocks * P.n_chunks;
   }
-  // two row tiles per CTA halve the Z' traffic; taken when the column splits still give every
-  // multiprocessor its two CTAs
-  int RT = (tiles256 * P.n_chunks >= target) ? 2 : 1;
+  // two row tiles per CTA halve the Z' traffic; taken when every CTA still gets a few steps
+  int RT = (steps2 >= (int64_t)target * kMinStepsPair) ? 2 : 1;
   if (g_force_rt) RT = g_force_rt;
   pl.row_tiles = RT;
-  const int total_tiles = RT == 2 ? tiles256 : tiles128;
-  int S = (int)ceil_div64(target, total_tiles > 0 ? total_tiles : 1);
-  if (S * total_tiles > target && S > 1) --S;          // round down: never more CTAs than slots
-  if (S > P.n_chunks) S = P.n_chunks;
-  if (S < 1) S = 1;
-  const int cpi = (int)ceil_div64(P.n_chunks, S);
-  S = (int)ceil_div64(P.n_chunks, cpi);
-  int items = 0, tiles = 0, blks = 0;
-  int64_t part_floats = 0;
+  const int64_t steps = RT == 2 ? steps2 : steps1;
+  int L = (int)ceil_div64(steps, target);
+  if (L < 1) L = 1;
+  P.steps_per_cta = L;
+  const int grid = (int)ceil_div64(steps, L);
+  int segs = 0, blks = 0;
+  int64_t st = 0;
   for (int i = 0; i < n; ++i) {
     P.w[i] = ws[i];
-    const int n_rt = (int)ceil_div64(ws[i].out_features, RT * kTileRows);
-    P.splits[i] = S;
-    P.chunks_per_item[i] = cpi;
-    P.item_base[i] = items;
-    P.tile_base[i] = tiles;
+    const int n_rg = (int)ceil_div64(ws[i].out_features, RT * kTileRows);
+    P.step_base[i] = (int)st;
+    P.seg_base[i] = segs;
     P.blk_base[i] = blks;
-    P.part_base[i] = part_floats;
-    items += n_rt * S;
-    tiles += n_rt;
+    st += (int64_t)n_rg * ws[i].blocks * P.n_chunks;
+    segs += n_rg;
     blks += ws[i].blocks;
-    part_floats += (int64_t)n_rt * S * RT * kTileRows;
   }
-  P.item_base[n] = items;
-  P.tile_base[n] = tiles;
+  P.step_base[n] = (int)st;
+  P.seg_base[n] = segs;
   P.blk_base[n] = blks;
+  const int tiles = segs;
+  const int items = grid;
+  const int64_t part_floats = (int64_t)grid * 2 * RT * kTileRows;
   pl.total_blocks = blks;
   pl.total_items = items;
   int64_t off = 0;
