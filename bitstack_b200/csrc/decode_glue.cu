@@ -8,37 +8,74 @@ namespace bsb {
 namespace {
 
 // h[row] (+= delta[row]) ; y[row] = h[row] * rsqrt(mean(h^2) + eps) * weight      (fp32 inside)
-__global__ void __launch_bounds__(256) add_rmsnorm_kernel(__half* __restrict__ h, const __half* __restrict__ delta,
-                                                          const __half* __restrict__ weight, float eps,
-                                                          __half* __restrict__ y, int hidden) {
-  extern __shared__ float vals[];   // the row in fp32
-  __shared__ float red[8];
+// one CTA per row; a thread keeps its 8-element vectors (16-byte loads) in registers, so the row is
+// read once, the norm weight is fetched before the reduction and nothing is staged in shared memory
+constexpr int kNormThreads = 512;
+constexpr int kNormVecs = 4;   // vectors per thread: rows up to 512 * 4 * 8 = 16384 elements
+__global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(__half* __restrict__ h, const __half* __restrict__ delta,
+                                                                   const __half* __restrict__ weight, float eps,
+                                                                   __half* __restrict__ y, int hidden) {
+  __shared__ float red[kNormThreads / 32];
   const int64_t row = blockIdx.x;
-  __half* hr = h + row * hidden;
-  const __half* dr = delta ? delta + row * hidden : nullptr;
-  float ss = 0.f;
-  for (int i = threadIdx.x * 2; i < hidden; i += blockDim.x * 2) {
-    float2 v = __half22float2(*reinterpret_cast<const __half2*>(hr + i));
-    if (dr) {
-      const float2 d = __half22float2(*reinterpret_cast<const __half2*>(dr + i));
-      const __half2 s = __floats2half2_rn(v.x + d.x, v.y + d.y);   // the residual stream stays fp16
-      *reinterpret_cast<__half2*>(hr + i) = s;
-      v = __half22float2(s);
+  uint4* hr = reinterpret_cast<uint4*>(h + row * hidden);
+  const uint4* dr = delta ? reinterpret_cast<const uint4*>(delta + row * hidden) : nullptr;
+  const uint4* wr = reinterpret_cast<const uint4*>(weight);
+  const int nvec = hidden / 8;
+  uint4 hv[kNormVecs], dv[kNormVecs], wv[kNormVecs];
+#pragma unroll
+  for (int k = 0; k < kNormVecs; ++k) {
+    const int i = threadIdx.x + k * kNormThreads;
+    if (i < nvec) {
+      hv[k] = hr[i];
+      if (dr) dv[k] = __ldg(dr + i);
+      wv[k] = __ldg(wr + i);
     }
-    vals[i] = v.x;
-    vals[i + 1] = v.y;
-    ss += v.x * v.x + v.y * v.y;
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < kNormVecs; ++k) {
+    const int i = threadIdx.x + k * kNormThreads;
+    if (i < nvec) {
+      __half2* hp = reinterpret_cast<__half2*>(&hv[k]);
+      if (dr) {
+        const __half2* dp = reinterpret_cast<const __half2*>(&dv[k]);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float2 a = __half22float2(hp[q]), d = __half22float2(dp[q]);
+          hp[q] = __floats2half2_rn(a.x + d.x, a.y + d.y);   // the residual stream stays fp16
+        }
+        hr[i] = hv[k];
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 a = __half22float2(hp[q]);
+        ss += a.x * a.x + a.y * a.y;
+      }
+    }
   }
   for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
   __syncthreads();
   float tot = 0.f;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) tot += red[i];
+  for (int i = 0; i < kNormThreads / 32; ++i) tot += red[i];
   const float inv = rsqrtf(tot / (float)hidden + eps);
-  for (int i = threadIdx.x * 2; i < hidden; i += blockDim.x * 2) {
-    const float2 wv = __half22float2(*reinterpret_cast<const __half2*>(weight + i));
-    *reinterpret_cast<__half2*>(y + row * hidden + i) = __floats2half2_rn(vals[i] * inv * wv.x, vals[i + 1] * inv * wv.y);
+  uint4* yr = reinterpret_cast<uint4*>(y + row * hidden);
+#pragma unroll
+  for (int k = 0; k < kNormVecs; ++k) {
+    const int i = threadIdx.x + k * kNormThreads;
+    if (i < nvec) {
+      const __half2* hp = reinterpret_cast<const __half2*>(&hv[k]);
+      const __half2* wp = reinterpret_cast<const __half2*>(&wv[k]);
+      uint4 out;
+      __half2* op = reinterpret_cast<__half2*>(&out);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 a = __half22float2(hp[q]), wq = __half22float2(wp[q]);
+        op[q] = __floats2half2_rn(a.x * inv * wq.x, a.y * inv * wq.y);
+      }
+      yr[i] = out;
+    }
   }
 }
 
@@ -97,16 +134,12 @@ extern "C" {
 int bsb_add_rmsnorm(uint16_t* h, const uint16_t* delta, const uint16_t* weight, float eps, uint16_t* y, int64_t rows,
                     int32_t hidden, void* stream) {
   BSB_CHECK_ARG(h && weight && y, "NULL buffer");
-  BSB_CHECK_ARG(rows >= 0 && hidden > 0 && hidden % 2 == 0 && hidden <= 16384, "hidden must be even and <= 16384");
-  BSB_CHECK_ARG(((uintptr_t)h | (uintptr_t)weight | (uintptr_t)y | (uintptr_t)delta) % 4 == 0, "buffers must be 4-byte aligned");
+  BSB_CHECK_ARG(rows >= 0 && hidden > 0 && hidden % 8 == 0 && hidden <= kNormThreads * kNormVecs * 8,
+                "hidden must be a multiple of 8 and <= 16384");
+  BSB_CHECK_ARG(((uintptr_t)h | (uintptr_t)weight | (uintptr_t)y | (uintptr_t)delta) % 16 == 0, "buffers must be 16-byte aligned");
   if (rows == 0) return BSB_OK;
   BSB_CHECK_ARG(rows <= 65535 * 32, "too many rows");
-  static bool attr_done = false;
-  if (!attr_done) {
-    BSB_CUDA(cudaFuncSetAttribute(add_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 16384 * 4));
-    attr_done = true;
-  }
-  add_rmsnorm_kernel<<<(unsigned)rows, 256, hidden * sizeof(float), (cudaStream_t)stream>>>(
+  add_rmsnorm_kernel<<<(unsigned)rows, kNormThreads, 0, (cudaStream_t)stream>>>(
       (__half*)h, (const __half*)delta, (const __half*)weight, eps, (__half*)y, hidden);
   return check_launch("add_rmsnorm_kernel");
 }

@@ -200,6 +200,25 @@ __device__ __forceinline__ void mma_ts_f8(uint32_t d, uint32_t a, uint64_t bdesc
       "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n}"
       ::"r"(d), "r"(a), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
 }
+// same, always accumulating, without an output-lane mask: the shortest operand list (every
+// operand of the instruction has to be moved to a uniform register first)
+__device__ __forceinline__ void mma_ts_f8_acc(uint32_t d, uint32_t a, uint64_t bdesc, uint32_t idesc) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.eq.b32 p, 0, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], %2, %3, p;\n}"
+      ::"r"(d), "r"(a), "l"(bdesc), "r"(idesc) : "memory");
+}
+__device__ __forceinline__ void mma_ts_f8_first(uint32_t d, uint32_t a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], %2, %3, p;\n}"
+      ::"r"(d), "r"(a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ bool elect_one() {
+  uint32_t ok;
+  asm volatile("{\n.reg .pred p;\nelect.sync _|p, 0xFFFFFFFF;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(ok));
+  return ok != 0;
+}
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -472,9 +491,12 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
     tmem_alloc(&S.tmem_base, kTmemCols);
     tmem_relinquish();
   }
-  if (tid < 16) S.trace[tid] = 0;
+  if (tid < 14) S.trace[tid] = 0;
   if (tid == 0) {
     S.n_pending = 0;
+#ifdef BSB_TRACE
+    S.trace[14] = global_ns();   // wall-clock start / end of the CTA body (slots 14, 15)
+#endif
     for (int e = 0; e < 2; ++e)
       for (int i = 0; i < 2; ++i) {
         mbar_init(&S.afull[e][i], kTileRows);
@@ -530,9 +552,13 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
   } else if (warp == kWarpMma || warp == kWarpMma + 1) {
     // ---- MMA issuer e: RT == 1: words 8e .. 8e+7 of every chunk; RT == 2: all 16 words for row
     //      tile e; accumulator D(e, parity of the block segment) -----------------------------
-    if (lane == 0 && P.dbg != 2) {
+    // The whole warp runs the loop and the waits (a warp-wide poll costs the same issue slots as a
+    // one-lane poll) so that addresses and descriptors stay warp-uniform values; one elected lane
+    // issues the MMAs and commits.
+    if (P.dbg != 2) {
       const int e = warp - kWarpMma;
       if (e != 0) tr = nullptr;
+      const bool leader = elect_one();
       const uint32_t idesc = make_idesc_f8(128, 32);
       Walk wk;
       wk.init(P, step0, kRows);
@@ -544,13 +570,13 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
         const int b = bs & 1;
         if (first && bs >= 2) {
           TR_BEGIN(t0);
-          if (!mbar_wait(&S.dempty[b], ((bs >> 1) - 1) & 1)) { atomicExch(P.status, 6); ok = false; break; }
+          if (!mbar_wait_group(&S.dempty[b], ((bs >> 1) - 1) & 1)) { if (leader) atomicExch(P.status, 6); ok = false; break; }
           TR_ADD(7, t0);
           tc_fence_after();
         }
         const int zslot = g % kNZ;
         TR_BEGIN(t1);
-        if (!mbar_wait(&S.zfull[zslot], (g / kNZ) & 1)) { atomicExch(P.status, 2); ok = false; break; }
+        if (!mbar_wait_group(&S.zfull[zslot], (g / kNZ) & 1)) { if (leader) atomicExch(P.status, 2); ok = false; break; }
         TR_ADD(5, t1);
         const uint32_t zaddr = smem_u32(S.zs[zslot]) + (RT == 1 ? (uint32_t)e * 8u * 1024u : 0u);
         const uint32_t dcol = tbase + e * 64 + b * 32;
@@ -558,24 +584,29 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
         for (int pp = 0; pp < kPP; ++pp, ++it) {
           const int slot = it & 1;
           TR_BEGIN(t2);
-          if (P.dbg != 1 && !mbar_wait(&S.afull[e][slot], (it >> 1) & 1)) { atomicExch(P.status, 3); ok = false; break; }
+          if (P.dbg != 1 && !mbar_wait_group(&S.afull[e][slot], (it >> 1) & 1)) { if (leader) atomicExch(P.status, 3); ok = false; break; }
           TR_ADD(6, t2);
           TR_BEGIN(t3);
           tc_fence_after();
-          uint64_t bdesc = make_smem_desc(zaddr + (uint32_t)(pp * 4) * 1024u, 128, 256);
+          const uint64_t bdesc = make_smem_desc(zaddr + (uint32_t)(pp * 4) * 1024u, 128, 256);
           const uint32_t acol = tbase + colA + e * 64 + slot * 32;
-#pragma unroll
-          for (int ww = 0; ww < 4; ++ww) {
-            mma_ts_f8(dcol, acol + ww * 8, bdesc, idesc, (!first || pp > 0 || ww > 0) ? 1u : 0u);
-            bdesc += 1024u >> 4;   // next 1 KB operand tile (address field counts 16-byte units)
+          if (leader) {
+            // 1 KB operand tiles follow each other: the descriptor's address field counts 16-byte units
+            mma_ts_f8_first(dcol, acol, bdesc, idesc, (!first || pp > 0) ? 1u : 0u);
+            mma_ts_f8_acc(dcol, acol + 8, bdesc + 64, idesc);
+            mma_ts_f8_acc(dcol, acol + 16, bdesc + 128, idesc);
+            mma_ts_f8_acc(dcol, acol + 24, bdesc + 192, idesc);
+            mma_commit(&S.aempty[e][slot]);
           }
-          mma_commit(&S.aempty[e][slot]);
           TR_ADD(8, t3);
         }
         if (!ok) break;
-        mma_commit(&S.zempty[zslot]);
         const bool seg_end = (wk.ci == NCH - 1) || (g == total - 1);
-        if (seg_end) { mma_commit(&S.dfull[e][b]); ++bs; }
+        if (leader) {
+          mma_commit(&S.zempty[zslot]);
+          if (seg_end) mma_commit(&S.dfull[e][b]);
+        }
+        if (seg_end) ++bs;
         first = seg_end;
         wk.advance(P, kRows);
       }
@@ -772,6 +803,9 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
   __syncthreads();
   if (warp == 0) TR_ADD(12, t_cta);
   if (P.trace) {
+#ifdef BSB_TRACE
+    if (tid == 0) S.trace[15] = global_ns();
+#endif
     __syncthreads();
     if (tid < 16) P.trace[(int64_t)blockIdx.x * 16 + tid] = S.trace[tid];
   }

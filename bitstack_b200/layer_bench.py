@@ -49,6 +49,7 @@ def main() -> None:
     ap.add_argument("--calls", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--graph", type=int, default=0, help="also time N back-to-back calls replayed as one CUDA graph")
     a = ap.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("layer_bench needs a CUDA device")
@@ -81,6 +82,25 @@ def main() -> None:
     if k.value:
         line += f"; main kernel median {np.median(main_us):.1f} us ({b / np.median(main_us) / 1e3:.1f} GB/s) over {k.value} launches"
     print(line)
+    if a.graph > 0:
+        # steady-state cost of a call inside a captured decode step: launch gaps included, caches warm
+        st = torch.cuda.Stream()
+        with torch.cuda.stream(st):
+            mod(x)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=st):
+                for _ in range(a.graph):
+                    mod(x)
+            g.replay()
+            st.synchronize()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record(st)
+            for _ in range(5):
+                g.replay()
+            e.record(st)
+            st.synchronize()
+        per = s.elapsed_time(e) * 1e3 / (5 * a.graph)
+        print(f"  graph replay of {a.graph} calls: {per:.1f} us per call ({b / per / 1e3:.1f} GB/s; L2-warm if the weight fits)")
 
 
 if __name__ == "__main__":

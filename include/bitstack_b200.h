@@ -123,7 +123,8 @@ int64_t bsb_linear_grouped_workspace_bytes(const bsb_weight* ws, int32_t n_weigh
 /* ---- decode-time glue (no counterpart in the reference, which leaves these ops to the Hugging
  * Face Llama modules; bitstack/utils/scale_utils.py:3-5 names the classes it wraps) ------------
  * bsb_add_rmsnorm: h[rows][hidden] += delta (if delta != NULL; fp16 residual stream, written
- *   back), then y = h * rsqrt(mean(h^2) + eps) * weight with fp32 arithmetic.
+ *   back), then y = h * rsqrt(mean(h^2) + eps) * weight with fp32 arithmetic.  hidden % 8 == 0,
+ *   hidden <= 16384, 16-byte aligned buffers.
  * bsb_rope_cache: rotary embedding at position *pos (device scalar) on q[batch][q_heads*dim] in
  *   place and on k, which is written with v into caches [batch][kv_heads][max_len][dim];
  *   cos/sin tables are [max_len][dim] in the "rotate half" convention.
