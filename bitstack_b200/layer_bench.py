@@ -50,11 +50,13 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--graph", type=int, default=0, help="also time N back-to-back calls replayed as one CUDA graph")
+    ap.add_argument("--pdl", action="store_true", help="launch the decode kernel as a programmatic dependent of the Z' kernel")
     a = ap.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("layer_bench needs a CUDA device")
     dev = torch.device("cuda:0")
     lib = _lib.load()
+    lib.bsb_debug_set_mode(101 if a.pdl else 100)
     mod = synthetic_projection(a.out, a.inp, a.blocks, a.level, dev)
     x = torch.randn(a.rows, a.inp, device=dev).half()
     flush = None if a.no_flush else torch.empty(512 << 20, dtype=torch.uint8, device=dev)
