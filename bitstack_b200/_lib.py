@@ -51,6 +51,7 @@ SIGNATURES = {
     "bsb_noalloc_scratch_bytes": (_I64, []),
     "bsb_linear_forward_noalloc": (C.c_int, [_WP, _P, _I64, _I64, _P, _I64, _P]),
     "bsb_debug_gemv_status": (C.c_int, [_WP, _I32, _P, C.POINTER(C.c_int32)]),
+    "bsb_debug_gemm_status": (C.c_int, [_WP, _P, C.POINTER(C.c_int32)]),
     "bsb_debug_launch_count": (_I64, []),
     "bsb_debug_set_trace": (C.c_int, [_P]),
     "bsb_debug_set_mode": (C.c_int, [_I32]),

@@ -15,7 +15,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libbitstack_b200.so")
-SOURCES = ["capi.cu", "pack_kernels.cu", "general_kernels.cu", "rebuild_gemm.cu", "gemv_mma.cu", "gemv_tc5.cu", "decode_glue.cu"]
+SOURCES = ["capi.cu", "pack_kernels.cu", "general_kernels.cu", "rebuild_gemm.cu", "gemv_mma.cu", "gemv_tc5.cu", "gemm_tc5.cu", "decode_glue.cu"]
 HEADERS = [os.path.join(CSRC, "common.cuh"), os.path.join(os.path.dirname(HERE), "include", "bitstack_b200.h")]
 FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",
          "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]

@@ -78,7 +78,7 @@ static int64_t workspace_for(const bsb_weight& w, int64_t rows, int algo) {
     case BSB_ALGO_GEMV_TC5:
       return gemv_tc5_workspace_bytes(&w, 1);
     case BSB_ALGO_REBUILD_GEMM:
-      return align_up64((int64_t)w.out_features * w.in_features * 2, 256);
+      return align_up64((int64_t)w.out_features * w.in_features * 2, 256) + 256;   // fp16 W, then the GEMM's status word
     default:
       return 0;
   }
@@ -139,6 +139,15 @@ static int forward_one(const bsb_weight& w, const __half* x, int64_t rows, int64
       BSB_CHECK_ARG((uintptr_t)workspace % 16 == 0, "workspace must be 16-byte aligned");
       __half* wbuf = (__half*)workspace;
       if (int rc = launch_rebuild_weight(w, wbuf, s)) return rc;
+      const int64_t w_bytes = align_up64((int64_t)w.out_features * w.in_features * 2, 256);
+      if (gemm_tc5_supported(rows, w.out_features, w.in_features) && (uintptr_t)y % 16 == 0 && y_stride % 8 == 0 &&
+          (uintptr_t)x % 16 == 0 && x_stride % 8 == 0 && workspace_bytes >= w_bytes + 256) {
+        int* status = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(workspace) + w_bytes);
+        BSB_CUDA(cudaMemsetAsync(status, 0, 4, s));
+        return launch_gemm_tc5(x, rows, x_stride, wbuf, w.out_features, w.in_features,
+                               reinterpret_cast<const __half*>(w.bias), y, y_stride, status, s);
+      }
+      // outputs that are not 16-byte aligned: the warp-level (mma.sync) kernel
       return launch_gemm_xwt(x, rows, x_stride, wbuf, w.out_features, w.in_features,
                              reinterpret_cast<const __half*>(w.bias), y, y_stride, s);
     }
@@ -268,6 +277,13 @@ int bsb_debug_gemv_status(const bsb_weight* ws, int32_t n_weights, const void* w
   BSB_CHECK_ARG(ws && workspace && status_out, "NULL argument");
   const int64_t off = gemv_tc5_status_offset(ws, n_weights);
   BSB_CHECK_ARG(off >= 0, "bad group size");
+  BSB_CUDA(cudaMemcpy(status_out, (const uint8_t*)workspace + off, 4, cudaMemcpyDeviceToHost));
+  return BSB_OK;
+}
+
+int bsb_debug_gemm_status(const bsb_weight* w, const void* workspace, int32_t* status_out) {
+  BSB_CHECK_ARG(w && workspace && status_out, "NULL argument");
+  const int64_t off = align_up64((int64_t)w->out_features * w->in_features * 2, 256);
   BSB_CUDA(cudaMemcpy(status_out, (const uint8_t*)workspace + off, 4, cudaMemcpyDeviceToHost));
   return BSB_OK;
 }

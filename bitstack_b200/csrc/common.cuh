@@ -69,6 +69,12 @@ int launch_gemm_xwt(const __half* x, int64_t rows, int64_t x_stride, const __hal
                     int out_features, int in_features, const __half* bias, __half* y,
                     int64_t y_stride, cudaStream_t s);
 
+// the same product on the tcgen05 tensor cores (TMA-fed, accumulators in tensor memory); `status` is a
+// device word that a wait which gives up raises (may be nullptr)
+bool gemm_tc5_supported(int64_t rows, int out_features, int in_features);
+int launch_gemm_tc5(const __half* x, int64_t rows, int64_t x_stride, const __half* w, int out_features,
+                    int in_features, const __half* bias, __half* y, int64_t y_stride, int* status, cudaStream_t s);
+
 // decode path: packed signs streamed into fp8 tensor-core MMAs
 int launch_vt_absmax(const bsb_weight& w, float* out, cudaStream_t s);
 bool gemv_mma_supported(const bsb_weight& w);

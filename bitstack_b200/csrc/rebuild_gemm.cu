@@ -25,11 +25,20 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* 
                : "r"(addr));
 }
 
+// a ^ (~b & 0x80000000): flips the sign of the fp32 pattern `a` when bit 31 of `b` is clear
+__device__ __forceinline__ uint32_t flip_if_clear(uint32_t a, uint32_t b) {
+  uint32_t out;
+  // minterms of a ^ (~b & c) over (a, b, c) with a = 0xF0, b = 0xCC, c = 0xAA: 0xF0 ^ (0x33 & 0xAA) = 0xD2
+  asm("lop3.b32 %0, %1, %2, %3, 0xD2;" : "=r"(out) : "r"(a), "r"(b), "r"(0x80000000u));
+  return out;
+}
+
 // ---------------------------------------------------------------------------
 // rebuild: CTA = 8 warps = 128 rows x 64 columns of W; warp = 16 rows x 64 cols
 // ---------------------------------------------------------------------------
 constexpr int kRbCols = 64;
 constexpr int kRbRowsPerCta = 128;
+constexpr int kRbRowTiles = 4;             // 128-row tiles per CTA
 constexpr int kRbBlockGroup = 16;          // residual blocks staged in shared memory at once
 constexpr int kRbVtStride = kRbCols + 8;   // halves; +16 B keeps ldmatrix rows on distinct banks
 
@@ -40,10 +49,16 @@ __global__ void __launch_bounds__(256) rebuild_weight_kernel(bsb_weight w, __hal
   const int g = lane >> 2, t = lane & 3;
   const int N = w.in_features, M = w.out_features;
   const int n0 = blockIdx.x * kRbCols;
-  const int m0 = blockIdx.y * kRbRowsPerCta + warp * 16;
-  const bool active = m0 < M;  // out_features is a multiple of 16
   const __half* u_all = reinterpret_cast<const __half*>(w.u);
   const __half* vt_all = reinterpret_cast<const __half*>(w.vt);
+  // a CTA walks kRbRowTiles 128-row tiles of the same 64 columns: with at most kRbBlockGroup
+  // blocks the staged Vt slab is loaded once and reused by all of them
+  const bool one_group = w.blocks <= kRbBlockGroup;
+
+  for (int rt = 0; rt < kRbRowTiles; ++rt) {
+  const int m0 = (blockIdx.y * kRbRowTiles + rt) * kRbRowsPerCta + warp * 16;
+  if ((blockIdx.y * kRbRowTiles + rt) * kRbRowsPerCta >= M) break;   // uniform for the CTA
+  const bool active = m0 < M;  // out_features is a multiple of 16
 
   float acc[8][4];
 #pragma unroll
@@ -53,6 +68,7 @@ __global__ void __launch_bounds__(256) rebuild_weight_kernel(bsb_weight w, __hal
 
   for (int j0 = 0; j0 < w.blocks; j0 += kRbBlockGroup) {
     const int nj = min(kRbBlockGroup, w.blocks - j0);
+    if (rt == 0 || !one_group) {
     __syncthreads();  // previous group fully consumed
     // stage Vt[j0..j0+nj)[0..16)[n0..n0+64): 16 B per thread per step
     for (int i = threadIdx.x; i < nj * 16 * (kRbCols / 8); i += blockDim.x) {
@@ -64,21 +80,28 @@ __global__ void __launch_bounds__(256) rebuild_weight_kernel(bsb_weight w, __hal
       *reinterpret_cast<uint4*>(&vt_s[jj][r][c8 * 8]) = v;
     }
     __syncthreads();
+    }
     if (!active) continue;
 
-    for (int jj = 0; jj < nj; ++jj) {
-      const int j = j0 + jj;
-      // A fragment: U_j rows m0+g / m0+g+8, ranks 2t,2t+1 / 2t+8,2t+9
+    // operands of a block that come straight from global memory (A fragment of U_j: rows m0+g /
+    // m0+g+8, ranks 2t,2t+1 / 2t+8,2t+9; 64 sign bits of the two rows) are fetched one block ahead
+    auto fetch = [&](int j, uint32_t (&af)[4], uint2& lo, uint2& hi) {
       const __half* u = u_all + (int64_t)j * w.u_block_stride;
-      uint32_t a[4];
-      a[0] = __ldg(reinterpret_cast<const uint32_t*>(u + (int64_t)(m0 + g) * 16 + 2 * t));
-      a[1] = __ldg(reinterpret_cast<const uint32_t*>(u + (int64_t)(m0 + g + 8) * 16 + 2 * t));
-      a[2] = __ldg(reinterpret_cast<const uint32_t*>(u + (int64_t)(m0 + g) * 16 + 2 * t + 8));
-      a[3] = __ldg(reinterpret_cast<const uint32_t*>(u + (int64_t)(m0 + g + 8) * 16 + 2 * t + 8));
-      // 64 sign bits of rows m0+g and m0+g+8
+      af[0] = __ldg(reinterpret_cast<const uint32_t*>(u + (int64_t)(m0 + g) * 16 + 2 * t));
+      af[1] = __ldg(reinterpret_cast<const uint32_t*>(u + (int64_t)(m0 + g + 8) * 16 + 2 * t));
+      af[2] = __ldg(reinterpret_cast<const uint32_t*>(u + (int64_t)(m0 + g) * 16 + 2 * t + 8));
+      af[3] = __ldg(reinterpret_cast<const uint32_t*>(u + (int64_t)(m0 + g + 8) * 16 + 2 * t + 8));
       const uint8_t* q = w.qweight + (int64_t)j * w.q_block_stride;
-      const uint2 s_lo = __ldg(reinterpret_cast<const uint2*>(q + ((int64_t)(m0 + g) * N + n0) / 8));
-      const uint2 s_hi = __ldg(reinterpret_cast<const uint2*>(q + ((int64_t)(m0 + g + 8) * N + n0) / 8));
+      lo = __ldg(reinterpret_cast<const uint2*>(q + ((int64_t)(m0 + g) * N + n0) / 8));
+      hi = __ldg(reinterpret_cast<const uint2*>(q + ((int64_t)(m0 + g + 8) * N + n0) / 8));
+    };
+    uint32_t a_next[4];
+    uint2 lo_next, hi_next;
+    fetch(j0, a_next, lo_next, hi_next);
+    for (int jj = 0; jj < nj; ++jj) {
+      uint32_t a[4] = {a_next[0], a_next[1], a_next[2], a_next[3]};
+      const uint2 s_lo = lo_next, s_hi = hi_next;
+      if (jj + 1 < nj) fetch(j0 + jj + 1, a_next, lo_next, hi_next);
 #pragma unroll
       for (int pair = 0; pair < 4; ++pair) {  // two 8-column tiles per ldmatrix.x4
         uint32_t b[4];
@@ -96,24 +119,22 @@ __global__ void __launch_bounds__(256) rebuild_weight_kernel(bsb_weight w, __hal
           const uint32_t wlo = (i < 4) ? s_lo.x : s_lo.y;
           const uint32_t whi = (i < 4) ? s_hi.x : s_hi.y;
           const int sh = 24 - 8 * (i & 3) + 2 * t;
-          const uint32_t f0 = ~(wlo << sh) & 0x80000000u;
-          const uint32_t f1 = ~(wlo << (sh + 1)) & 0x80000000u;
-          const uint32_t f2 = ~(whi << sh) & 0x80000000u;
-          const uint32_t f3 = ~(whi << (sh + 1)) & 0x80000000u;
-          acc[i][0] += __uint_as_float(__float_as_uint(d[0]) ^ f0);
-          acc[i][1] += __uint_as_float(__float_as_uint(d[1]) ^ f1);
-          acc[i][2] += __uint_as_float(__float_as_uint(d[2]) ^ f2);
-          acc[i][3] += __uint_as_float(__float_as_uint(d[3]) ^ f3);
+          // sign application d ^ (~f & 0x80000000) is one LOP3 per element
+          acc[i][0] += __uint_as_float(flip_if_clear(__float_as_uint(d[0]), wlo << sh));
+          acc[i][1] += __uint_as_float(flip_if_clear(__float_as_uint(d[1]), wlo << (sh + 1)));
+          acc[i][2] += __uint_as_float(flip_if_clear(__float_as_uint(d[2]), whi << sh));
+          acc[i][3] += __uint_as_float(flip_if_clear(__float_as_uint(d[3]), whi << (sh + 1)));
         }
       }
     }
   }
-  if (!active) return;
+  if (!active) continue;
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const int n = n0 + 8 * i + 2 * t;
     *reinterpret_cast<__half2*>(out + (int64_t)(m0 + g) * N + n) = __floats2half2_rn(acc[i][0], acc[i][1]);
     *reinterpret_cast<__half2*>(out + (int64_t)(m0 + g + 8) * N + n) = __floats2half2_rn(acc[i][2], acc[i][3]);
+  }
   }
 }
 
@@ -243,7 +264,7 @@ int launch_rebuild_weight(const bsb_weight& w, __half* w_out, cudaStream_t s) {
   BSB_CHECK_ARG(rebuild_supported(w), "rebuild: unsupported shape/alignment (out=%d in=%d k=%d)",
                 w.out_features, w.in_features, w.k);
   BSB_CHECK_ARG((uintptr_t)w_out % 4 == 0, "rebuild: output must be 4-byte aligned");
-  dim3 grid(w.in_features / kRbCols, (unsigned)ceil_div64(w.out_features, kRbRowsPerCta));
+  dim3 grid(w.in_features / kRbCols, (unsigned)ceil_div64(w.out_features, kRbRowsPerCta * kRbRowTiles));
   rebuild_weight_kernel<<<grid, 256, 0, s>>>(w, w_out);
   return check_launch("rebuild_weight_kernel");
 }

@@ -83,6 +83,9 @@ def main() -> None:
     line = f"{a.out}x{a.inp} blocks={a.blocks} rows={a.rows} level={a.level}: whole call median {np.median(whole):.1f} us ({b / np.median(whole) / 1e3:.1f} GB/s)"
     if k.value:
         line += f"; main kernel median {np.median(main_us):.1f} us ({b / np.median(main_us) / 1e3:.1f} GB/s) over {k.value} launches"
+        if a.rows > 4 and a.level in (0, 9):
+            fl = 2.0 * a.rows * a.out * a.inp
+            line += f" = {fl / np.median(main_us) / 1e6:.1f} TFLOP/s for the GEMM alone"
     print(line)
     if a.graph > 0:
         # steady-state cost of a call inside a captured decode step: launch gaps included, caches warm

@@ -164,6 +164,8 @@ int bsb_linear_forward_noalloc(const bsb_weight* w, const uint16_t* x, int64_t r
  * *status_out (host): 0 = every hand-off completed, otherwise the code of the
  * time-bounded wait that gave up.  Synchronises the device. */
 int bsb_debug_gemv_status(const bsb_weight* ws, int32_t n_weights, const void* workspace, int32_t* status_out);
+/* The same for the tcgen05 GEMM of a batch call (rows > 4) that used `workspace`. */
+int bsb_debug_gemm_status(const bsb_weight* w, const void* workspace, int32_t* status_out);
 
 /* Measurement aids (no reference counterpart).  bsb_debug_launch_count: kernels this
  * library has launched so far in the process.  bsb_debug_profile_start/stop: while

@@ -297,6 +297,27 @@ def test_bias_3d_input_and_empty_batch(dev):
     assert np.allclose(y0, np.broadcast_to(bias.astype(np.float32), (6, 128)))
 
 
+@pytest.mark.parametrize("rows,m,n,nb", [(37, 1040, 576, 3), (5, 128, 64, 1), (300, 272, 4096, 2), (129, 4096, 192, 4)])
+def test_batch_gemm_ragged_shapes(dev, rows, m, n, nb):
+    """Batch path (rebuild + tcgen05 GEMM): row counts, feature counts and K extents that are not
+    multiples of the 128 x BN tile, with a bias; the GEMM's status word must stay 0."""
+    import ctypes as C
+    from bitstack_b200 import _lib, linear
+    q, u, vt = orc.synthetic_layer(m, n, nb, seed=rows + m)
+    bias = (np.random.default_rng(rows).standard_normal(m) * 0.1).astype(np.float16)
+    mod = make_module(q, u, vt, bias, dev, level=9)
+    x_np = orc.synthetic_input(rows, n, seed=rows + n)
+    y = mod(torch.from_numpy(x_np).to(dev))
+    torch.cuda.synchronize()
+    e_max, e_l2 = errs(y.float().cpu().numpy(), orc.forward_f64(x_np, q, u, vt, nb, bias))
+    assert e_max <= EXACT_TOL and e_l2 <= EXACT_TOL, (e_max, e_l2)
+    lib = _lib.load()
+    ws = linear.get_workspace(dev, 1)
+    st = C.c_int32(-1)
+    assert lib.bsb_debug_gemm_status(C.byref(mod.weight_desc(dev)), ws.data_ptr(), C.byref(st)) == 0
+    assert st.value == 0
+
+
 def test_linearity_and_block_additivity(dev):
     """Size-independent properties: y(a x1 + x2) = a y(x1) + y(x2); the output with b
     blocks equals the sum of single-block outputs."""
