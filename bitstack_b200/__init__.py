@@ -4,8 +4,10 @@ Public surface (mirrors the reference's operator API):
     BitStackLinear            module with the reference's constructor / buffers / methods
     pack_sign, unpack_sign    sign bit packing on the device
     forward_grouped           several projections of one input in one launch sequence
+    loader                    budget selection (compression_config.json) and partial safetensors loading
 """
 from .linear import BitStackLinear, forward_grouped, get_workspace
 from .pack import pack_sign, unpack_sign
+from . import loader
 
-__all__ = ["BitStackLinear", "forward_grouped", "get_workspace", "pack_sign", "unpack_sign"]
+__all__ = ["BitStackLinear", "forward_grouped", "get_workspace", "pack_sign", "unpack_sign", "loader"]
