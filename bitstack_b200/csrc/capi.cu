@@ -21,6 +21,7 @@ static unsigned long long g_launches = 0;
 void count_launch() { __atomic_fetch_add(&g_launches, 1ull, __ATOMIC_RELAXED); }
 
 // profiling hook: a bounded list of event pairs recorded around the tcgen05 decode kernel
+int g_pdl_enabled = 1;   // programmatic dependent launch between the library's kernels (1-1.5 us less per launch in graph replay)
 static const int kMaxProfile = 4096;
 static cudaEvent_t g_prof_ev[2 * kMaxProfile];
 static int g_prof_cap = 0, g_prof_n = 0;

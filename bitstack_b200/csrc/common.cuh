@@ -45,6 +45,30 @@ inline int check_launch(const char* what) {
   return BSB_OK;
 }
 
+// Programmatic dependent launch.  Every kernel of the decode step starts with pdl_wait() (returns when
+// the kernels before it in the stream have completed and their writes are visible; a no-op for a normal
+// launch) followed by pdl_trigger() (the NEXT kernel's launch may be processed now: it will sit in its
+// own pdl_wait()).  Only the launch latency overlaps; no kernel touches memory before its wait.
+extern int g_pdl_enabled;
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = g_pdl_enabled ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
+
 static inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
 static inline int64_t align_up64(int64_t a, int64_t b) { return ceil_div64(a, b) * b; }
 

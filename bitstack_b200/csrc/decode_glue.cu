@@ -16,6 +16,8 @@ __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(__half* __res
                                                                    const __half* __restrict__ weight, float eps,
                                                                    __half* __restrict__ y, int hidden) {
   __shared__ float red[kNormThreads / 32];
+  pdl_wait();
+  pdl_trigger();
   const int64_t row = blockIdx.x;
   uint4* hr = reinterpret_cast<uint4*>(h + row * hidden);
   const uint4* dr = delta ? reinterpret_cast<const uint4*>(delta + row * hidden) : nullptr;
@@ -86,6 +88,8 @@ __global__ void __launch_bounds__(128) rope_cache_kernel(__half* __restrict__ q,
                                                          const __half* __restrict__ sin_t, const int64_t* __restrict__ pos_p,
                                                          __half* __restrict__ k_cache, __half* __restrict__ v_cache,
                                                          int Hq, int Hkv, int D, int max_len) {
+  pdl_wait();
+  pdl_trigger();
   const int b = blockIdx.y, head = blockIdx.x;
   const int64_t pos = *pos_p;
   if (pos < 0 || pos >= max_len) return;   // out of the cache: nothing is written
@@ -114,8 +118,182 @@ __global__ void __launch_bounds__(128) rope_cache_kernel(__half* __restrict__ q,
   }
 }
 
+// ---- single-token attention with the rotary embedding and the KV-cache write folded in --------
+// kAttSplits CTAs per (query head, batch row), each over a contiguous share of the cache positions
+// (one CTA alone pays every memory latency of its phases in sequence; the cache of a layer is cold);
+// 256 threads; caches [batch][kv_heads][max_len][D] fp16.
+//   A. q and the new k are rotated in fp32 and rounded to fp16 (what a separate rotary kernel would
+//      have stored); the new k and v go into the caches (every CTA of a KV group writes the same
+//      bytes), q stays in shared memory as fp32.
+//   B. scores: one THREAD per cache position -- its whole K row is D/8 independent 16-byte loads, so
+//      a CTA keeps tens of KB in flight instead of paying one memory latency per position.
+//   C. softmax statistics over the scores in shared memory (fp32).
+//   D. P.V: thread (r, c) adds rows r, r+16, ... of V for the c-th 8-element vector, eight rows in
+//      flight; the 16 partial sums per element are merged in shared memory.
+//   E. every CTA leaves (max, sum, unnormalised output) in `partial`; the last one to arrive on the
+//      head's counter merges the kAttSplits results, writes `out` and resets the counter to 0.
+constexpr int kAttSplits = 4;
+template <int D>
+__global__ void __launch_bounds__(256) decode_attention_kernel(const __half* __restrict__ q, const __half* __restrict__ k,
+                                                               const __half* __restrict__ v, const __half* __restrict__ cos_t,
+                                                               const __half* __restrict__ sin_t, const int64_t* __restrict__ pos_p,
+                                                               __half* __restrict__ k_cache, __half* __restrict__ v_cache,
+                                                               __half* __restrict__ out, int Hq, int Hkv, int max_len, float scale,
+                                                               float* __restrict__ partial, int* __restrict__ counters) {
+  constexpr int kVec = D / 8;            // 16-byte vectors per row
+  constexpr int kRowsPerPass = 256 / kVec;
+  extern __shared__ float s_score[];     // [pos + 1]
+  __shared__ float s_q[D];
+  __shared__ float s_red[8];
+  __shared__ float s_part[kRowsPerPass][D];
+  __shared__ int s_last;
+  pdl_wait();
+  pdl_trigger();
+  const int h = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int64_t pos = *pos_p;
+  if (pos < 0 || pos >= max_len) return;   // out of the cache: nothing is written
+  const int hk = h / (Hq / Hkv);
+  __half* kc = k_cache + ((int64_t)b * Hkv + hk) * (int64_t)max_len * D;
+  __half* vc = v_cache + ((int64_t)b * Hkv + hk) * (int64_t)max_len * D;
+
+  // ---- A ----
+  if (tid < D / 2) {
+    const int i = tid;
+    const float c0 = __half2float(cos_t[pos * D + i]), c1 = __half2float(cos_t[pos * D + i + D / 2]);
+    const float s0 = __half2float(sin_t[pos * D + i]), s1 = __half2float(sin_t[pos * D + i + D / 2]);
+    // x*cos + rotate_half(x)*sin with rotate_half(x) = [-x1, x0]
+    const __half* qs = q + ((int64_t)b * Hq + h) * D;
+    float x0 = __half2float(qs[i]), x1 = __half2float(qs[i + D / 2]);
+    s_q[i] = __half2float(__float2half_rn(x0 * c0 - x1 * s0));
+    s_q[i + D / 2] = __half2float(__float2half_rn(x1 * c1 + x0 * s1));
+    const __half* ks = k + ((int64_t)b * Hkv + hk) * D;
+    x0 = __half2float(ks[i]);
+    x1 = __half2float(ks[i + D / 2]);
+    kc[pos * D + i] = __float2half_rn(x0 * c0 - x1 * s0);
+    kc[pos * D + i + D / 2] = __float2half_rn(x1 * c1 + x0 * s1);
+  } else if (tid < D / 2 + D / 8) {
+    const int c = tid - D / 2;
+    reinterpret_cast<uint4*>(vc + pos * D)[c] = reinterpret_cast<const uint4*>(v + ((int64_t)b * Hkv + hk) * D)[c];
+  }
+  __syncthreads();
+
+  // ---- B ----  (positions [p_lo, p_lo + n) of the pos + 1 in the cache; scores are indexed from p_lo)
+  const int n_all = (int)pos + 1;
+  const int share = (n_all + kAttSplits - 1) / kAttSplits;
+  const int p_lo = min(split * share, n_all);
+  const int n = min(share, n_all - p_lo);
+  kc += (int64_t)p_lo * D;
+  vc += (int64_t)p_lo * D;
+  float m_loc = -INFINITY;
+  for (int p = tid; p < n; p += 256) {
+    const uint4* row = reinterpret_cast<const uint4*>(kc + (int64_t)p * D);
+    uint4 raw[kVec];
+#pragma unroll
+    for (int c = 0; c < kVec; ++c) raw[c] = row[c];
+    float dot = 0.f;
+#pragma unroll
+    for (int c = 0; c < kVec; ++c) {
+      const __half2* h2 = reinterpret_cast<const __half2*>(&raw[c]);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __half22float2(h2[e]);
+        dot = fmaf(f.x, s_q[c * 8 + 2 * e], dot);
+        dot = fmaf(f.y, s_q[c * 8 + 2 * e + 1], dot);
+      }
+    }
+    const float sc = dot * scale;
+    s_score[p] = sc;
+    m_loc = fmaxf(m_loc, sc);
+  }
+  // ---- C ----
+  for (int o = 16; o > 0; o >>= 1) m_loc = fmaxf(m_loc, __shfl_xor_sync(0xFFFFFFFFu, m_loc, o));
+  if (lane == 0) s_red[warp] = m_loc;
+  __syncthreads();
+  float m = s_red[0];
+#pragma unroll
+  for (int w = 1; w < 8; ++w) m = fmaxf(m, s_red[w]);
+  __syncthreads();
+  float l_loc = 0.f;
+  for (int p = tid; p < n; p += 256) {
+    const float e = __expf(s_score[p] - m);
+    s_score[p] = e;
+    l_loc += e;
+  }
+  for (int o = 16; o > 0; o >>= 1) l_loc += __shfl_xor_sync(0xFFFFFFFFu, l_loc, o);
+  if (lane == 0) s_red[warp] = l_loc;
+  __syncthreads();
+  float l = 0.f;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) l += s_red[w];
+
+  // ---- D ----
+  const int r = tid / kVec, c = tid % kVec;
+  float acc[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+  for (int p = r; p < n; p += 8 * kRowsPerPass) {
+    uint4 raw[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {          // rows past the end: no load, weight 0
+      const int pu = p + u * kRowsPerPass;
+      raw[u] = pu < n ? reinterpret_cast<const uint4*>(vc + (int64_t)pu * D)[c] : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int pu = p + u * kRowsPerPass;
+      const float w = pu < n ? s_score[pu] : 0.f;
+      const __half2* h2 = reinterpret_cast<const __half2*>(&raw[u]);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __half22float2(h2[e]);
+        acc[2 * e] = fmaf(w, f.x, acc[2 * e]);
+        acc[2 * e + 1] = fmaf(w, f.y, acc[2 * e + 1]);
+      }
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < 8; ++e) s_part[r][c * 8 + e] = acc[e];
+  __syncthreads();
+  // ---- E ----
+  float* mine = partial + (((int64_t)b * Hq + h) * kAttSplits + split) * (D + 2);
+  if (tid < D) {
+    float o = 0.f;
+#pragma unroll
+    for (int rr = 0; rr < kRowsPerPass; ++rr) o += s_part[rr][tid];
+    mine[2 + tid] = o;
+  }
+  if (tid == 0) { mine[0] = m; mine[1] = l; }
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const int old = atomicAdd(&counters[b * Hq + h], 1);
+    s_last = (old == kAttSplits - 1);
+    if (s_last) counters[b * Hq + h] = 0;   // ready for the next call
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  if (tid < D) {
+    const float* all = partial + ((int64_t)b * Hq + h) * kAttSplits * (D + 2);
+    float mm = -INFINITY;
+#pragma unroll
+    for (int sidx = 0; sidx < kAttSplits; ++sidx) mm = fmaxf(mm, __ldcg(all + sidx * (D + 2)));
+    float ll = 0.f, o = 0.f;
+#pragma unroll
+    for (int sidx = 0; sidx < kAttSplits; ++sidx) {
+      const float f = __expf(__ldcg(all + sidx * (D + 2)) - mm);   // an empty share has max -inf, sum 0: weight 0
+      ll += __ldcg(all + sidx * (D + 2) + 1) * f;
+      o += __ldcg(all + sidx * (D + 2) + 2 + tid) * f;
+    }
+    out[((int64_t)b * Hq + h) * D + tid] = __float2half_rn(o / ll);
+  }
+}
+
 __global__ void __launch_bounds__(256) silu_mul_kernel(const __half2* __restrict__ g, const __half2* __restrict__ u,
                                                        __half2* __restrict__ out, int64_t n2) {
+  pdl_wait();
+  pdl_trigger();
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n2; i += (int64_t)gridDim.x * blockDim.x) {
     const float2 a = __half22float2(g[i]), b = __half22float2(u[i]);
     const __half2 s = __floats2half2_rn(a.x / (1.f + __expf(-a.x)), a.y / (1.f + __expf(-a.y)));   // fp16 SiLU, as torch rounds it
@@ -139,8 +317,8 @@ int bsb_add_rmsnorm(uint16_t* h, const uint16_t* delta, const uint16_t* weight, 
   BSB_CHECK_ARG(((uintptr_t)h | (uintptr_t)weight | (uintptr_t)y | (uintptr_t)delta) % 16 == 0, "buffers must be 16-byte aligned");
   if (rows == 0) return BSB_OK;
   BSB_CHECK_ARG(rows <= 65535 * 32, "too many rows");
-  add_rmsnorm_kernel<<<(unsigned)rows, kNormThreads, 0, (cudaStream_t)stream>>>(
-      (__half*)h, (const __half*)delta, (const __half*)weight, eps, (__half*)y, hidden);
+  BSB_CUDA(launch_pdl(add_rmsnorm_kernel, dim3((unsigned)rows), dim3(kNormThreads), 0, (cudaStream_t)stream,
+                      (__half*)h, (const __half*)delta, (const __half*)weight, eps, (__half*)y, hidden));
   return check_launch("add_rmsnorm_kernel");
 }
 
@@ -151,11 +329,44 @@ int bsb_rope_cache(uint16_t* q, const uint16_t* k, const uint16_t* v, const uint
   BSB_CHECK_ARG(batch >= 1 && q_heads >= 1 && kv_heads >= 1 && head_dim >= 2 && head_dim % 2 == 0 && max_len >= 1,
                 "bad attention shape");
   dim3 grid(q_heads + 2 * kv_heads, batch);
-  rope_cache_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>((__half*)q, (const __half*)k, (const __half*)v,
-                                                            (const __half*)cos_table, (const __half*)sin_table, pos,
-                                                            (__half*)k_cache, (__half*)v_cache, q_heads, kv_heads,
-                                                            head_dim, max_len);
+  BSB_CUDA(launch_pdl(rope_cache_kernel, grid, dim3(128), 0, (cudaStream_t)stream, (__half*)q, (const __half*)k, (const __half*)v,
+                      (const __half*)cos_table, (const __half*)sin_table, pos, (__half*)k_cache, (__half*)v_cache, q_heads,
+                      kv_heads, head_dim, max_len));
   return check_launch("rope_cache_kernel");
+}
+
+int64_t bsb_decode_attention_scratch_bytes(int32_t batch, int32_t q_heads, int32_t head_dim) {
+  if (batch < 1 || q_heads < 1 || head_dim < 1) return -1;
+  return align_up64((int64_t)batch * q_heads * 4, 256) + (int64_t)batch * q_heads * kAttSplits * (head_dim + 2) * 4;
+}
+
+int bsb_decode_attention(const uint16_t* q, const uint16_t* k, const uint16_t* v, const uint16_t* cos_table,
+                         const uint16_t* sin_table, const int64_t* pos, uint16_t* k_cache, uint16_t* v_cache, uint16_t* out,
+                         int32_t batch, int32_t q_heads, int32_t kv_heads, int32_t head_dim, int32_t max_len, void* scratch,
+                         int64_t scratch_bytes, void* stream) {
+  BSB_CHECK_ARG(q && k && v && cos_table && sin_table && pos && k_cache && v_cache && out && scratch, "NULL buffer");
+  BSB_CHECK_ARG(batch >= 1 && q_heads >= 1 && head_dim >= 1 && scratch_bytes >= bsb_decode_attention_scratch_bytes(batch, q_heads, head_dim) &&
+                (uintptr_t)scratch % 16 == 0, "scratch too small or not 16-byte aligned");
+  BSB_CHECK_ARG(batch >= 1 && batch <= 65535 && q_heads >= 1 && kv_heads >= 1 && q_heads % kv_heads == 0 && max_len >= 1,
+                "bad attention shape");
+  BSB_CHECK_ARG(head_dim == 128 || head_dim == 64, "decode attention is built for head_dim 64 and 128 (got %d)", head_dim);
+  BSB_CHECK_ARG(((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) % 16 == 0,
+                "buffers must be 16-byte aligned");
+  BSB_CHECK_ARG(max_len <= 8192, "decode attention keeps one fp32 score per cache position in shared memory: max_len <= 8192 (got %d)", max_len);
+  const float scale = 1.0f / sqrtf((float)head_dim);
+  dim3 grid(q_heads, batch, kAttSplits);
+  const size_t smem = (size_t)((max_len + kAttSplits - 1) / kAttSplits + 1) * sizeof(float);
+  int* counters = reinterpret_cast<int*>(scratch);
+  float* partial = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(scratch) + align_up64((int64_t)batch * q_heads * 4, 256));
+  if (head_dim == 128)
+    BSB_CUDA(launch_pdl(decode_attention_kernel<128>, grid, dim3(256), smem, (cudaStream_t)stream,
+                        (const __half*)q, (const __half*)k, (const __half*)v, (const __half*)cos_table, (const __half*)sin_table, pos,
+                        (__half*)k_cache, (__half*)v_cache, (__half*)out, q_heads, kv_heads, max_len, scale, partial, counters));
+  else
+    BSB_CUDA(launch_pdl(decode_attention_kernel<64>, grid, dim3(256), smem, (cudaStream_t)stream,
+                        (const __half*)q, (const __half*)k, (const __half*)v, (const __half*)cos_table, (const __half*)sin_table, pos,
+                        (__half*)k_cache, (__half*)v_cache, (__half*)out, q_heads, kv_heads, max_len, scale, partial, counters));
+  return check_launch("decode_attention_kernel");
 }
 
 int bsb_silu_mul(const uint16_t* gate, const uint16_t* up, uint16_t* out, int64_t n, void* stream) {
@@ -165,7 +376,8 @@ int bsb_silu_mul(const uint16_t* gate, const uint16_t* up, uint16_t* out, int64_
   if (n == 0) return BSB_OK;
   int64_t blocks = ceil_div64(n / 2, 256);
   if (blocks > 1184) blocks = 1184;
-  silu_mul_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((const __half2*)gate, (const __half2*)up, (__half2*)out, n / 2);
+  BSB_CUDA(launch_pdl(silu_mul_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (const __half2*)gate,
+                      (const __half2*)up, (__half2*)out, n / 2));
   return check_launch("silu_mul_kernel");
 }
 

@@ -288,9 +288,11 @@ __global__ void __launch_bounds__(256) zprep_tc5_kernel(const __grid_constant__ 
   const int word = tid >> 4, r = tid & 15;
   const int col0 = chunk * kChunkCols + word * 32;
 
-  // the decode kernel of this call may be scheduled now (if launched as a programmatic
-  // dependent): it waits (griddepcontrol.wait) before touching anything written here
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // x and the scratch of the previous call are safe to touch once the kernels before this one are
+  // done; then the decode kernel of this call may be scheduled (it waits before touching anything
+  // written here)
+  pdl_wait();
+  pdl_trigger();
 
   if (blockIdx.x == 0 && blockIdx.y == 0) {
     for (int i = tid; i < P.seg_base[P.n_weights]; i += blockDim.x) P.counters[i] = 0;
@@ -473,6 +475,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
   extern __shared__ uint8_t smem_raw[];
   SmemLayout& S = *reinterpret_cast<SmemLayout*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
 
+  pdl_trigger();   // the kernel after this one may be launched; it waits for this grid before it reads y
   const int NCH = P.n_chunks;
   const int step0 = blockIdx.x * P.steps_per_cta;
   const int total = min(P.steps_per_cta, P.step_base[P.n_weights] - step0);   // steps of this CTA
@@ -968,8 +971,7 @@ static int make_sign_map(const bsb_weight& w, CUtensorMap* map) {
 
 static unsigned long long* g_trace = nullptr;
 static int g_dbg = 0;
-static int g_pdl = 1;   // programmatic dependent launch of the decode kernel: 1-1.5 us less per call in graph replay
-void gemv_tc5_set_pdl(int on) { g_pdl = on; }
+void gemv_tc5_set_pdl(int on) { g_pdl_enabled = on; }
 void gemv_tc5_set_dbg(int m) {
   if (m >= 200 && m <= 202) g_force_rt = m - 200;   // row tiles per CTA: 200 = choose, 201 / 202 = forced
   else g_dbg = m;
@@ -1040,7 +1042,13 @@ int launch_gemv_tc5(const bsb_weight* ws, int n_weights, const __half* x, __half
       P.vt_absmax[i] = am;
     }
   }
-  zprep_tc5_kernel<<<dim3(P.n_chunks, pl.total_blocks), 256, 0, s>>>(P, x);
+  {
+    cudaError_t le = launch_pdl(zprep_tc5_kernel, dim3(P.n_chunks, pl.total_blocks), dim3(256), 0, s, P, x);
+    if (le != cudaSuccess) {
+      set_error("launch of zprep_tc5_kernel failed: %s", cudaGetErrorString(le));
+      return BSB_ECUDA;
+    }
+  }
   if (int rc = check_launch("zprep_tc5_kernel")) return rc;
   profile_mark(s, false);
   {
@@ -1052,7 +1060,7 @@ int launch_gemv_tc5(const bsb_weight* ws, int n_weights, const __half* x, __half
     cfg.stream = s;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = g_pdl ? 1 : 0;
+    attr[0].val.programmaticStreamSerializationAllowed = g_pdl_enabled ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     cudaError_t le = pl.row_tiles == 2 ? cudaLaunchKernelEx(&cfg, gemv_tc5_kernel<2>, P)

@@ -194,7 +194,7 @@ class BitStackLlamaDecoder:
 
     def _decode_fused(self):
         """One decode step (one new token per sequence) with the fused glue kernels: per layer
-        13 launches instead of ~30.  Same math as `_forward` on a single position."""
+        12 launches instead of ~30.  Same math as `_forward` on a single position."""
         s = self.shape
         B = self.batch
         hd = s.head_dim
@@ -203,11 +203,15 @@ class BitStackLlamaDecoder:
         x = glue.add_rmsnorm(h, None, self.layers[0]["in_norm"], s.rms_eps)
         for i, lay in enumerate(self.layers):
             q, k, v = forward_grouped([lay["self_attn.q_proj"], lay["self_attn.k_proj"], lay["self_attn.v_proj"]], x)
-            glue.rope_cache(q, k, v, self.cos, self.sin, self.pos, self.k_cache[i], self.v_cache[i],
-                            self.q_local, self.kv_local, hd)
-            att = F.scaled_dot_product_attention(q.view(B, self.q_local, 1, hd), self.k_cache[i], self.v_cache[i],
-                                                 attn_mask=mask, enable_gqa=True)
-            o = self._allreduce(lay["self_attn.o_proj"](att.reshape(B, self.q_local * hd)))
+            if hd in (64, 128) and self.max_len <= 8192:
+                att = glue.decode_attention(q, k, v, self.cos, self.sin, self.pos, self.k_cache[i], self.v_cache[i],
+                                            self.q_local, self.kv_local, hd)
+            else:
+                glue.rope_cache(q, k, v, self.cos, self.sin, self.pos, self.k_cache[i], self.v_cache[i],
+                                self.q_local, self.kv_local, hd)
+                att = F.scaled_dot_product_attention(q.view(B, self.q_local, 1, hd), self.k_cache[i], self.v_cache[i],
+                                                     attn_mask=mask, enable_gqa=True).reshape(B, self.q_local * hd)
+            o = self._allreduce(lay["self_attn.o_proj"](att))
             x = glue.add_rmsnorm(h, o, lay["post_norm"], s.rms_eps)
             g, u = forward_grouped([lay["mlp.gate_proj"], lay["mlp.up_proj"]], x)
             d = self._allreduce(lay["mlp.down_proj"](glue.silu_mul(g, u)))

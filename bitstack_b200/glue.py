@@ -8,6 +8,9 @@ import torch
 from . import _lib
 
 
+_att_scratch = {}   # (device, batch, heads, head_dim) -> zero-initialised scratch of decode_attention
+
+
 def _s(t):
     return torch.cuda.current_stream(t.device).cuda_stream
 
@@ -39,6 +42,29 @@ def rope_cache(q, k, v, cos, sin, pos, k_cache, v_cache, q_heads, kv_heads, head
                                         head_dim, k_cache.shape[2], _s(q))
     _lib.check(rc, "bsb_rope_cache")
     return q
+
+
+def decode_attention(q, k, v, cos, sin, pos, k_cache, v_cache, q_heads, kv_heads, head_dim):
+    """One new token per batch row: rotary embedding of q and k at position pos[0] (device int64), k and v
+    appended to k_cache / v_cache [batch, kv_heads, max_len, head_dim], then grouped-query attention of the
+    rotated q over cache positions 0..pos.  q is left untouched; returns [batch, q_heads * head_dim] fp16."""
+    for t in (q, k, v, cos, sin, k_cache, v_cache):
+        assert t.is_cuda and t.dtype == torch.float16 and t.is_contiguous()
+    assert pos.dtype == torch.int64 and pos.is_cuda
+    batch = q.shape[0]
+    out = torch.empty(batch, q_heads * head_dim, dtype=torch.float16, device=q.device)
+    lib = _lib.load()
+    key = (q.device.index, batch, q_heads, head_dim)
+    scratch = _att_scratch.get(key)
+    if scratch is None:   # zeroed once; the kernel leaves its counters at zero for the next call
+        scratch = torch.zeros(lib.bsb_decode_attention_scratch_bytes(batch, q_heads, head_dim), dtype=torch.uint8, device=q.device)
+        _att_scratch[key] = scratch
+    with torch.cuda.device(q.device):
+        rc = lib.bsb_decode_attention(q.data_ptr(), k.data_ptr(), v.data_ptr(), cos.data_ptr(), sin.data_ptr(),
+                                      pos.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), batch,
+                                      q_heads, kv_heads, head_dim, k_cache.shape[2], scratch.data_ptr(), scratch.numel(), _s(q))
+    _lib.check(rc, "bsb_decode_attention")
+    return out
 
 
 def silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:

@@ -128,12 +128,22 @@ int64_t bsb_linear_grouped_workspace_bytes(const bsb_weight* ws, int32_t n_weigh
  * bsb_rope_cache: rotary embedding at position *pos (device scalar) on q[batch][q_heads*dim] in
  *   place and on k, which is written with v into caches [batch][kv_heads][max_len][dim];
  *   cos/sin tables are [max_len][dim] in the "rotate half" convention.
+ * bsb_decode_attention: the same rotary embedding and cache write as bsb_rope_cache (q is NOT
+ *   modified) followed by softmax(q.K^T / sqrt(dim)).V over cache positions 0..*pos for one new
+ *   token per batch row, grouped-query heads, fp32 softmax; out[batch][q_heads*dim].  head_dim 64 or 128,
+ *   max_len <= 8192.  `scratch` (bsb_decode_attention_scratch_bytes, 16-byte aligned) must be ZERO before its
+ *   first use and is left ready for the next call; calls sharing a scratch must be stream-ordered.
  * bsb_silu_mul: out = silu(gate) * up over n fp16 elements. */
 int bsb_add_rmsnorm(uint16_t* h, const uint16_t* delta, const uint16_t* weight, float eps, uint16_t* y, int64_t rows,
                     int32_t hidden, void* stream);
 int bsb_rope_cache(uint16_t* q, const uint16_t* k, const uint16_t* v, const uint16_t* cos_table, const uint16_t* sin_table,
                    const int64_t* pos, uint16_t* k_cache, uint16_t* v_cache, int32_t batch, int32_t q_heads,
                    int32_t kv_heads, int32_t head_dim, int32_t max_len, void* stream);
+int bsb_decode_attention(const uint16_t* q, const uint16_t* k, const uint16_t* v, const uint16_t* cos_table,
+                         const uint16_t* sin_table, const int64_t* pos, uint16_t* k_cache, uint16_t* v_cache, uint16_t* out,
+                         int32_t batch, int32_t q_heads, int32_t kv_heads, int32_t head_dim, int32_t max_len, void* scratch,
+                         int64_t scratch_bytes, void* stream);
+int64_t bsb_decode_attention_scratch_bytes(int32_t batch, int32_t q_heads, int32_t head_dim);
 int bsb_silu_mul(const uint16_t* gate, const uint16_t* up, uint16_t* out, int64_t n, void* stream);
 
 /* Forward for callers that may not allocate device memory.  It has no counterpart in the

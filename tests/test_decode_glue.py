@@ -69,6 +69,34 @@ def test_rope_cache(dev):
     assert kc[:, :, :37].abs().max() == 0 and kc[:, :, 38:].abs().max() == 0
 
 
+@pytest.mark.parametrize("B,Hq,Hkv,D,L,at", [(2, 8, 2, 128, 64, 37), (1, 32, 8, 128, 700, 640), (3, 4, 4, 64, 40, 0), (1, 8, 1, 128, 33, 32)])
+def test_decode_attention_matches_rope_then_sdpa(dev, B, Hq, Hkv, D, L, at):
+    """Fused rotary + cache write + single-token attention against the separate rotary kernel followed by
+    torch's scaled_dot_product_attention on the same caches."""
+    from bitstack_b200 import glue
+    g = torch.Generator(device=dev).manual_seed(B * 1000 + at)
+    q = torch.randn(B, Hq * D, device=dev, generator=g).half()
+    k = torch.randn(B, Hkv * D, device=dev, generator=g).half()
+    v = torch.randn(B, Hkv * D, device=dev, generator=g).half()
+    inv = 1.0 / (500000.0 ** (torch.arange(0, D, 2, device=dev).float() / D))
+    fr = torch.outer(torch.arange(L, device=dev).float(), inv)
+    cos, sin = torch.cat([fr, fr], -1).cos().half(), torch.cat([fr, fr], -1).sin().half()
+    kc = torch.randn(B, Hkv, L, D, device=dev, generator=g).half()
+    vc = torch.randn(B, Hkv, L, D, device=dev, generator=g).half()
+    kc[:, :, at:] = 0
+    vc[:, :, at:] = 0
+    pos = torch.tensor([at], device=dev)
+    kc2, vc2, q2 = kc.clone(), vc.clone(), q.clone()
+    out = glue.decode_attention(q, k, v, cos, sin, pos, kc, vc, Hq, Hkv, D)
+    assert torch.equal(q, q2)                                  # q is not modified
+    glue.rope_cache(q2, k, v, cos, sin, pos, kc2, vc2, Hq, Hkv, D)
+    assert torch.equal(kc, kc2) and torch.equal(vc, vc2)        # same cache contents, bit for bit
+    mask = (torch.arange(L, device=dev) <= at).view(1, 1, 1, L)
+    ref = F.scaled_dot_product_attention(q2.view(B, Hq, 1, D).float(), kc2.float(), vc2.float(), attn_mask=mask,
+                                         enable_gqa=True).reshape(B, Hq * D)
+    assert (out.float() - ref).abs().max() <= 3e-3 * ref.abs().max()
+
+
 def test_fused_decode_step_matches_unfused(dev):
     from bitstack_b200 import decode
     shape = decode.LlamaShape("tiny", 2, 512, 4, 2, 1024, vocab=1000)
