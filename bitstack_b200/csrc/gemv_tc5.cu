@@ -859,6 +859,7 @@ struct TcPlan {
 };
 
 static int g_force_rt = 0;   // 0 = choose, 1 / 2 = forced (tuning)
+static int g_target_ctas = 0;   // 0 = two per multiprocessor, else this many (tuning)
 constexpr int kMinStepsPair = 4;
 
 void make_tc_plan(const bsb_weight* ws, int n, TcPlan& pl) {
@@ -868,7 +869,7 @@ void make_tc_plan(const bsb_weight* ws, int n, TcPlan& pl) {
   const int N = ws[0].in_features;
   P.n_chunks = (int)ceil_div64(N, kChunkCols);
   // CTAs wanted: two per multiprocessor (both stay resident and share its tensor pipe)
-  const int target = sm_count() * 2;
+  const int target = g_target_ctas > 0 ? g_target_ctas : sm_count() * 2;
   int64_t steps1 = 0, steps2 = 0;
   for (int i = 0; i < n; ++i) {
     steps1 += ceil_div64(ws[i].out_features, kTileRows) * ws[i].blocks * P.n_chunks;
@@ -974,6 +975,7 @@ static int g_dbg = 0;
 void gemv_tc5_set_pdl(int on) { g_pdl_enabled = on; }
 void gemv_tc5_set_dbg(int m) {
   if (m >= 200 && m <= 202) g_force_rt = m - 200;   // row tiles per CTA: 200 = choose, 201 / 202 = forced
+  else if (m >= 1000 && m < 2000) g_target_ctas = m - 1000;   // grid size wanted (1000 = default)
   else g_dbg = m;
 }
 void gemv_tc5_set_trace(unsigned long long* p) { g_trace = p; }
