@@ -18,6 +18,14 @@ __device__ __forceinline__ void mma_f16_16816(float (&d)[4], const uint32_t (&a)
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// same with a zero C operand: D = A.B (no register tuple to clear before every MMA)
+__device__ __forceinline__ void mma_f16_16816_zero(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
+}
+
 __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_ptr) {
   const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem_ptr);
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
@@ -100,7 +108,8 @@ __global__ void __launch_bounds__(256) rebuild_weight_kernel(bsb_weight w, __hal
     fetch(j0, a_next, lo_next, hi_next);
     for (int jj = 0; jj < nj; ++jj) {
       uint32_t a[4] = {a_next[0], a_next[1], a_next[2], a_next[3]};
-      const uint2 s_lo = lo_next, s_hi = hi_next;
+      const uint2 lo_t = make_uint2(lo_next.x << (2 * t), lo_next.y << (2 * t));
+      const uint2 hi_t = make_uint2(hi_next.x << (2 * t), hi_next.y << (2 * t));
       if (jj + 1 < nj) fetch(j0 + jj + 1, a_next, lo_next, hi_next);
 #pragma unroll
       for (int pair = 0; pair < 4; ++pair) {  // two 8-column tiles per ldmatrix.x4
@@ -113,13 +122,15 @@ __global__ void __launch_bounds__(256) rebuild_weight_kernel(bsb_weight w, __hal
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           const int i = 2 * pair + h;
-          float d[4] = {0.f, 0.f, 0.f, 0.f};
-          mma_f16_16816(d, a, b[2 * h], b[2 * h + 1]);
-          // column 8i+2t is bit 7-2t of byte i; bring it to bit 31 and flip d when clear
-          const uint32_t wlo = (i < 4) ? s_lo.x : s_lo.y;
-          const uint32_t whi = (i < 4) ? s_hi.x : s_hi.y;
-          const int sh = 24 - 8 * (i & 3) + 2 * t;
-          // sign application d ^ (~f & 0x80000000) is one LOP3 per element
+          float d[4];
+          mma_f16_16816_zero(d, a, b[2 * h], b[2 * h + 1]);
+          // column 8i+2t is bit 7-2t of byte i: the words were shifted left by 2t once per block, so the
+          // shift that brings an element's bit to bit 31 is a compile-time constant (the compiler is free to
+          // place it on the multiply pipe); d is flipped when the bit is clear, one LOP3 per element
+          const uint32_t wlo = (i < 4) ? lo_t.x : lo_t.y;
+          const uint32_t whi = (i < 4) ? hi_t.x : hi_t.y;
+          constexpr int kBase = 24;
+          const int sh = kBase - 8 * (i & 3);
           acc[i][0] += __uint_as_float(flip_if_clear(__float_as_uint(d[0]), wlo << sh));
           acc[i][1] += __uint_as_float(flip_if_clear(__float_as_uint(d[1]), wlo << (sh + 1)));
           acc[i][2] += __uint_as_float(flip_if_clear(__float_as_uint(d[2]), whi << sh));
