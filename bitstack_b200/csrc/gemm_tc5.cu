@@ -11,7 +11,9 @@
 // layout.  Roles: warp 0 = TMA producer (one lane), warp 1 = tensor-memory allocation + MMA issue
 // (tcgen05.mma.kind::f16, one elected lane, tcgen05.commit releases stages), warps 2-5 =
 // epilogue (tcgen05.ld -> bias -> fp16 -> 16-byte stores; y is row-major with the token row on
-// the tensor-memory lane, so every thread writes contiguous bytes of its own row).
+// the tensor-memory lane, so every thread writes contiguous bytes of its own row).  CTAs are
+// persistent (one per multiprocessor) with two accumulator buffers in tensor memory, so the
+// epilogue of a tile overlaps the main loop of the next one.
 // All waits are time-bounded; a wait that gives up sets the status word and the CTA leaves.
 #include <cuda.h>
 
@@ -30,6 +32,9 @@ constexpr uint64_t kWaitLimitNs = 200ull * 1000 * 1000;
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
@@ -127,27 +132,33 @@ template <int BN>
 __global__ void __launch_bounds__(kThreads, 1) gemm_tc5_kernel(const __grid_constant__ GemmParams P) {
   constexpr int kStages = GemmSmem<BN>::kStages;
   constexpr int kABytes = kBM * kBK * 2, kBBytes = BN * kBK * 2;
+  constexpr int kAcc = (2 * BN <= 512) ? 2 : 1;      // accumulator buffers in tensor memory
+  constexpr int kTmemCols = (kAcc * BN < 32) ? 32 : kAcc * BN;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sa = base;                               // [stage][128 rows][128 B]
   uint8_t* sb = base + kStages * kABytes;            // [stage][BN rows][128 B]
   uint64_t* full = reinterpret_cast<uint64_t*>(sb + kStages * kBBytes);
   uint64_t* empty = full + kStages;
-  uint64_t* dfull = empty + kStages;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dfull + 1);
+  uint64_t* dfull = empty + kStages;                 // [kAcc] accumulator complete
+  uint64_t* dempty = dfull + 2;                      // [kAcc] accumulator read out by the epilogue
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dempty + 2);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int m0 = blockIdx.y * kBM;                   // first input row of the tile
-  const int n0 = blockIdx.x * BN;                    // first output feature of the tile
   const int k_steps = (P.in_features + kBK - 1) / kBK;
+  // Persistent CTAs walk the tiles output-column-major: consecutive tiles (and the CTAs of one wave)
+  // share a W tile and differ in the row tile, so W comes from DRAM once and x stays in L2.
+  const int row_tiles = (P.rows + kBM - 1) / kBM;
+  const int col_tiles = (P.out_features + BN - 1) / BN;
+  const int n_tiles = row_tiles * col_tiles;
 
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BN) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   if (tid == 0) {
     for (int i = 0; i < kStages; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
-    mbar_init(dfull, 1);
+    for (int i = 0; i < kAcc; ++i) { mbar_init(&dfull[i], 1); mbar_init(&dempty[i], 128); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   tc_fence_before();
@@ -158,13 +169,18 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc5_kernel(const __grid_cons
   if (warp == 0) {
     // ---- TMA producer ------------------------------------------------------------------
     if (lane == 0) {
-      for (int k = 0; k < k_steps; ++k) {
-        const int s = k % kStages, n = k / kStages;
-        if (n >= 1 && !mbar_wait(&empty[s], (n - 1) & 1)) { if (P.status) atomicExch(P.status, 21); break; }
-        mbar_expect_tx(&full[s], kABytes + kBBytes);
-        // rows and K past the end of a tensor read as zeros
-        tma_load_2d(sa + s * kABytes, &P.map_x, k * kBK, m0, &full[s]);
-        tma_load_2d(sb + s * kBBytes, &P.map_w, k * kBK, n0, &full[s]);
+      int it = 0;                                    // stages filled so far, over all tiles
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % row_tiles) * kBM, n0 = (tile / row_tiles) * BN;
+        for (int k = 0; k < k_steps; ++k, ++it) {
+          const int s = it % kStages, n = it / kStages;
+          if (n >= 1 && !mbar_wait(&empty[s], (n - 1) & 1)) { if (P.status) atomicExch(P.status, 21); ok = false; break; }
+          mbar_expect_tx(&full[s], kABytes + kBBytes);
+          // rows and K past the end of a tensor read as zeros
+          tma_load_2d(sa + s * kABytes, &P.map_x, k * kBK, m0, &full[s]);
+          tma_load_2d(sb + s * kBBytes, &P.map_w, k * kBK, n0, &full[s]);
+        }
       }
     }
   } else if (warp == 1) {
@@ -172,36 +188,49 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc5_kernel(const __grid_cons
     const bool leader = elect_one();
     const uint32_t idesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);   // f16 x f16 -> f32, K-major
     bool ok = true;
-    for (int k = 0; k < k_steps; ++k) {
-      const int s = k % kStages;
-      if (!mbar_wait(&full[s], (k / kStages) & 1)) { if (leader && P.status) atomicExch(P.status, 22); ok = false; break; }
+    int it = 0, t_idx = 0;
+    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++t_idx) {
+      const int ab = t_idx % kAcc, use = t_idx / kAcc;
+      // the epilogue must have emptied this accumulator (its use before this one)
+      if (use >= 1 && !mbar_wait(&dempty[ab], (use - 1) & 1)) { if (leader && P.status) atomicExch(P.status, 24); ok = false; break; }
       tc_fence_after();
-      if (leader) {
-        const uint64_t adesc = make_desc_sw128(smem_u32(sa + s * kABytes));
-        const uint64_t bdesc = make_desc_sw128(smem_u32(sb + s * kBBytes));
+      const uint32_t dcol = tbase + ab * BN;
+      for (int k = 0; k < k_steps; ++k, ++it) {
+        const int s = it % kStages;
+        if (!mbar_wait(&full[s], (it / kStages) & 1)) { if (leader && P.status) atomicExch(P.status, 22); ok = false; break; }
+        tc_fence_after();
+        if (leader) {
+          const uint64_t adesc = make_desc_sw128(smem_u32(sa + s * kABytes));
+          const uint64_t bdesc = make_desc_sw128(smem_u32(sb + s * kBBytes));
 #pragma unroll
-        for (int kk = 0; kk < kBK / 16; ++kk)   // 16 elements = 32 bytes further along the swizzled row
-          mma_ss_f16(tbase, adesc + 2 * kk, bdesc + 2 * kk, idesc, (k > 0 || kk > 0) ? 1u : 0u);
-        mma_commit(&empty[s]);
+          for (int kk = 0; kk < kBK / 16; ++kk)   // 16 elements = 32 bytes further along the swizzled row
+            mma_ss_f16(dcol, adesc + 2 * kk, bdesc + 2 * kk, idesc, (k > 0 || kk > 0) ? 1u : 0u);
+          mma_commit(&empty[s]);
+        }
       }
+      if (leader && ok) mma_commit(&dfull[ab]);
     }
-    if (leader && ok) mma_commit(dfull);
   } else {
     // ---- epilogue: warp w reads tensor-memory lanes 32 (w % 4) .. +31 = input rows -----------
     const int quarter = warp & 3;
-    const int row = m0 + quarter * 32 + lane;
-    bool ok = mbar_wait(dfull, 0);
-    ok = __all_sync(0xFFFFFFFFu, ok ? 1 : 0) != 0;
-    if (!ok) {
-      if (lane == 0 && P.status) atomicExch(P.status, 23);
-    } else {
+    const uint32_t lane_base = tbase + ((uint32_t)(quarter * 32) << 16);
+    int t_idx = 0;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++t_idx) {
+      const int m0 = (tile % row_tiles) * kBM, n0 = (tile / row_tiles) * BN;
+      const int ab = t_idx % kAcc, use = t_idx / kAcc;
+      const int row = m0 + quarter * 32 + lane;
+      bool ok = mbar_wait(&dfull[ab], use & 1);
+      ok = __all_sync(0xFFFFFFFFu, ok ? 1 : 0) != 0;
+      if (!ok) {
+        if (lane == 0 && P.status) atomicExch(P.status, 23);
+        break;
+      }
       tc_fence_after();
-      const uint32_t lane_base = tbase + ((uint32_t)(quarter * 32) << 16);
       __half* yrow = P.y + (int64_t)row * P.y_stride;
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         uint32_t d[32];
-        tmem_ld32(lane_base + c, d);
+        tmem_ld32(lane_base + ab * BN + c, d);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         if (row < P.rows) {
 #pragma unroll
@@ -224,13 +253,16 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc5_kernel(const __grid_cons
           }
         }
       }
+      // the accumulator may be overwritten by the tile after next
+      tc_fence_before();
+      mbar_arrive(&dempty[ab]);
     }
   }
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     __syncwarp();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tbase), "r"(BN) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tbase), "r"(kTmemCols) : "memory");
   }
 }
 
@@ -273,7 +305,7 @@ int make_map(CUtensorMap* map, const __half* ptr, int64_t n_rows, int n_cols, in
 template <int BN>
 int launch_bn(GemmParams& P, const __half* x, int64_t x_stride, const __half* w, cudaStream_t s) {
   constexpr int kStages = GemmSmem<BN>::kStages;
-  constexpr int smem = kStages * GemmSmem<BN>::kStageBytes + (2 * kStages + 1) * 8 + 16 + 1024;
+  constexpr int smem = kStages * GemmSmem<BN>::kStageBytes + (2 * kStages + 4) * 8 + 16 + 1024;
   static bool attr_set[64] = {false};
   int dev = 0;
   BSB_CUDA(cudaGetDevice(&dev));
@@ -283,7 +315,8 @@ int launch_bn(GemmParams& P, const __half* x, int64_t x_stride, const __half* w,
   }
   if (int rc = make_map(&P.map_x, x, P.rows, P.in_features, x_stride, kBM)) return rc;
   if (int rc = make_map(&P.map_w, w, P.out_features, P.in_features, P.in_features, BN)) return rc;
-  dim3 grid((unsigned)ceil_div64(P.out_features, BN), (unsigned)ceil_div64(P.rows, kBM));
+  const int64_t n_tiles = ceil_div64(P.out_features, BN) * ceil_div64(P.rows, kBM);
+  dim3 grid((unsigned)(n_tiles < sm_count() ? n_tiles : sm_count()));   // persistent: one CTA per multiprocessor
   profile_mark(s, false);
   gemm_tc5_kernel<BN><<<grid, kThreads, smem, s>>>(P);
   profile_mark(s, true);
