@@ -343,7 +343,7 @@ def run_ours(args):
                     "algorithmic_bytes_per_launch": float(np.mean(launch_bytes))}
         else:
             roof = {"bound": "hbm", "kernel": "gemv_tc5_kernel", "achieved": None, "peak": peak, "unit": "GB/s", "frac": None,
-                    "traffic": None, "note": f"{n.value} decode-kernel launches profiled in one step (batch {batch}: rows > 4 use the rebuild+GEMM path)"}
+                    "traffic": None, "note": f"{n.value} decode-kernel launches profiled in one step (batch {batch}: rows > 6 use the rebuild+GEMM path)"}
 
     # ---- CPU restatement on a bounded sample ---------------------------------------------
     cpu = None

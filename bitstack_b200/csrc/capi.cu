@@ -64,9 +64,13 @@ static int check_weight(const bsb_weight* w) {
   return BSB_OK;
 }
 
+// largest batch that goes through the decode kernel (pairs of rows); above it the weight is rebuilt once and
+// multiplied by the GEMM
+static const int kDecodeRowsMax = 6;
+
 static int pick_algo(const bsb_weight& w, int64_t rows, int algo) {
   if (algo != BSB_ALGO_AUTO) return algo;
-  if (rows <= 4 && gemv_tc5_supported(w)) return BSB_ALGO_GEMV_TC5;
+  if (rows <= kDecodeRowsMax && gemv_tc5_supported(w)) return BSB_ALGO_GEMV_TC5;   // two rows per pass: cheaper than rebuilding W up to here
   if (rows <= 4 && gemv_mma_supported(w)) return BSB_ALGO_GEMV_MMA;
   if (rebuild_supported(w) && gemm_supported(rows, w.out_features, w.in_features)) return BSB_ALGO_REBUILD_GEMM;
   return BSB_ALGO_GENERAL;
@@ -77,7 +81,7 @@ static int64_t workspace_for(const bsb_weight& w, int64_t rows, int algo) {
     case BSB_ALGO_GEMV_MMA:
       return gemv_mma_workspace_bytes(&w, 1);
     case BSB_ALGO_GEMV_TC5:
-      return gemv_tc5_workspace_bytes(&w, 1);
+      return gemv_tc5_workspace_bytes(&w, 1, rows >= 2 ? 2 : 1);
     case BSB_ALGO_REBUILD_GEMM:
       return align_up64((int64_t)w.out_features * w.in_features * 2, 256) + 256;   // fp16 W, then the GEMM's status word
     default:
@@ -127,9 +131,12 @@ static int forward_one(const bsb_weight& w, const __half* x, int64_t rows, int64
     case BSB_ALGO_GEMV_TC5: {
       BSB_CHECK_ARG(gemv_tc5_supported(w), "GEMV_TC5: unsupported shape/alignment (out=%d in=%d k=%d)",
                     w.out_features, w.in_features, w.k);
-      for (int64_t r = 0; r < rows; ++r) {
+      // rows go through the kernel two at a time (one MMA serves both), a last odd row alone
+      for (int64_t r = 0; r < rows;) {
+        const int nr = (rows - r >= 2 && x_stride % 8 == 0) ? 2 : 1;
         __half* yr = y + r * y_stride;
-        if (int rc = launch_gemv_tc5(&w, 1, x + r * x_stride, &yr, workspace, workspace_bytes, s)) return rc;
+        if (int rc = launch_gemv_tc5(&w, 1, x + r * x_stride, x_stride, nr, &yr, &y_stride, workspace, workspace_bytes, s)) return rc;
+        r += nr;
       }
       return BSB_OK;
     }
@@ -231,23 +238,25 @@ int bsb_linear_forward_grouped(const bsb_weight* ws, int32_t n_weights, const ui
   cudaStream_t s = (cudaStream_t)stream;
   // one fused launch sequence when every member qualifies for the decode kernel
   const bool use_tc5 = (algo == BSB_ALGO_AUTO || algo == BSB_ALGO_GEMV_TC5);
-  bool fused = (use_tc5 || algo == BSB_ALGO_GEMV_MMA) && rows >= 1 && rows <= 4 && n_weights <= 4;
+  bool fused = (use_tc5 || algo == BSB_ALGO_GEMV_MMA) && rows >= 1 && rows <= (use_tc5 ? kDecodeRowsMax : 4) && n_weights <= 4;
   for (int i = 0; i < n_weights && fused; ++i)
     fused = ws[i].blocks > 0 && ws[i].out_features > 0 &&
             (use_tc5 ? gemv_tc5_supported(ws[i]) : gemv_mma_supported(ws[i]));
   if (fused) {
-    const int64_t need = use_tc5 ? gemv_tc5_workspace_bytes(ws, n_weights) : gemv_mma_workspace_bytes(ws, n_weights);
+    const int64_t need = use_tc5 ? gemv_tc5_workspace_bytes(ws, n_weights, rows >= 2 ? 2 : 1) : gemv_mma_workspace_bytes(ws, n_weights);
     if (workspace == nullptr || workspace_bytes < need) {
       set_error("workspace of %lld bytes needed, %lld given", (long long)need, (long long)workspace_bytes);
       return BSB_EWORKSPACE;
     }
-    for (int64_t r = 0; r < rows; ++r) {
+    for (int64_t r = 0; r < rows;) {
+      const int nr = (use_tc5 && rows - r >= 2 && x_stride % 8 == 0) ? 2 : 1;   // two rows per pass of the tcgen05 kernel
       __half* yr[4];
       for (int i = 0; i < n_weights; ++i) yr[i] = (__half*)ys[i] + r * y_strides[i];
       const int rc = use_tc5
-          ? launch_gemv_tc5(ws, n_weights, (const __half*)x + r * x_stride, yr, workspace, workspace_bytes, s)
+          ? launch_gemv_tc5(ws, n_weights, (const __half*)x + r * x_stride, x_stride, nr, yr, y_strides, workspace, workspace_bytes, s)
           : launch_gemv_mma(ws, n_weights, (const __half*)x + r * x_stride, yr, workspace, workspace_bytes, s);
       if (rc) return rc;
+      r += nr;
     }
     return BSB_OK;
   }
@@ -263,14 +272,14 @@ int64_t bsb_linear_grouped_workspace_bytes(const bsb_weight* ws, int32_t n_weigh
   if (!ws || n_weights < 1 || rows < 0) return -1;
   int64_t need = 0;
   const bool use_tc5 = (algo == BSB_ALGO_AUTO || algo == BSB_ALGO_GEMV_TC5);
-  bool fused = (use_tc5 || algo == BSB_ALGO_GEMV_MMA) && rows >= 1 && rows <= 4 && n_weights <= 4;
+  bool fused = (use_tc5 || algo == BSB_ALGO_GEMV_MMA) && rows >= 1 && rows <= (use_tc5 ? kDecodeRowsMax : 4) && n_weights <= 4;
   for (int i = 0; i < n_weights; ++i) {
     if (check_weight(&ws[i]) != BSB_OK) return -1;
     fused = fused && ws[i].blocks > 0 && ws[i].out_features > 0 &&
             (use_tc5 ? gemv_tc5_supported(ws[i]) : gemv_mma_supported(ws[i]));
     if (ws[i].blocks > 0 && rows > 0) need = max(need, workspace_for(ws[i], rows, algo));
   }
-  if (fused) need = max(need, use_tc5 ? gemv_tc5_workspace_bytes(ws, n_weights) : gemv_mma_workspace_bytes(ws, n_weights));
+  if (fused) need = max(need, use_tc5 ? gemv_tc5_workspace_bytes(ws, n_weights, rows >= 2 ? 2 : 1) : gemv_mma_workspace_bytes(ws, n_weights));
   return need;
 }
 

@@ -108,12 +108,12 @@ int launch_gemv_mma(const bsb_weight* ws, int n_weights, const __half* x, __half
 
 // decode path, tcgen05 generation (A operand in tensor memory)
 bool gemv_tc5_supported(const bsb_weight& w);
-int64_t gemv_tc5_workspace_bytes(const bsb_weight* ws, int n_weights);
+int64_t gemv_tc5_workspace_bytes(const bsb_weight* ws, int n_weights, int rows_per_pass);   // rows_per_pass: 1 or 2
 void gemv_tc5_set_trace(unsigned long long* device_buffer);
 void gemv_tc5_set_dbg(int mode);
 void gemv_tc5_set_pdl(int on);
 int64_t gemv_tc5_status_offset(const bsb_weight* ws, int n_weights);
-int launch_gemv_tc5(const bsb_weight* ws, int n_weights, const __half* x, __half* const* ys,
-                    void* workspace, int64_t workspace_bytes, cudaStream_t s);
+int launch_gemv_tc5(const bsb_weight* ws, int n_weights, const __half* x, int64_t x_stride, int rows, __half* const* ys,
+                    const int64_t* y_strides, void* workspace, int64_t workspace_bytes, cudaStream_t s);
 
 }  // namespace bsb

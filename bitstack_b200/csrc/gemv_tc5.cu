@@ -39,11 +39,7 @@ constexpr int kThreads = 512;                    // 8 producer warps, 2 MMA issu
 #ifndef BSB_NZ
 #define BSB_NZ 3
 #endif
-#ifndef BSB_NP
-#define BSB_NP 6
-#endif
 constexpr int kNZ = BSB_NZ;                          // Z' slabs resident in shared memory
-constexpr int kNP = BSB_NP;                          // sign tiles (128 rows x 64 B, TMA) resident in shared memory
 constexpr int kSignTileBytes = kTileRows * 64;
 constexpr int kTmemCols = 256;                  // 4 x 32 (D: 2 issuers x 2 buffers) + 4 x 32 (A: 2 issuers x 2 stages)
 constexpr int kMaxGroup = 4;
@@ -64,19 +60,22 @@ struct alignas(64) TcParams {
   const float* vt_absmax[kMaxGroup];
   __half* y[kMaxGroup];
   int n_weights;
+  int rows;                        // input rows of this pass (1 or 2): the B operand holds 32 columns per row
+  int64_t x_stride;                // elements between input rows
+  int64_t y_stride[kMaxGroup];     // elements between output rows
   int n_chunks;                    // ceil(in / 512)
   int step_base[kMaxGroup + 1];    // first work step of each weight; a step = (row group, block, chunk)
   int seg_base[kMaxGroup + 1];     // first row group of each weight (index of its counter)
   int blk_base[kMaxGroup + 1];
   int steps_per_cta;               // every CTA takes this many consecutive steps (the last one fewer)
-  uint8_t* zops;     // [(weight,block)][chunk][16 KB]
-  float* kconst;     // [(weight,block)][chunk][16]
-  float* inv_scale;  // [(weight,block)][16]
+  uint8_t* zops;     // [(weight,block)][chunk][16 words][rows][1 KB]
+  float* kconst;     // [(weight,block)][chunk][rows][16]
+  float* inv_scale;  // [(weight,block)][rows][16]
   int* counters;     // [row group]: CTAs that have delivered their partial sums
   int* status;       // 0 = fine, else the code of the wait that gave up
   unsigned long long* trace;  // optional [CTA][16] cycle counters (debug), or nullptr
   int dbg;           // 0 = normal; 1 = MMA side only, 2 = producer side only (timing experiments, wrong results)
-  float* partials;   // [CTA][2][RT * 128]: sums of a row group that the CTA shares with other CTAs
+  float* partials;   // [CTA][2][rows][RT * 128]: sums of a row group that the CTA shares with other CTAs
 };
 
 // ------------------------------------------------------------------ PTX helpers
@@ -170,38 +169,14 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
         "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr) : "memory");
-}
 __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
                : "r"(taddr) : "memory");
 }
-// D[tmem] (+)= A[tmem] . B[smem]^T, e4m3 x e4m3 -> f32
-__device__ __forceinline__ void mma_ts_f8(uint32_t d, uint32_t a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n}"
-      ::"r"(d), "r"(a), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
-}
-// same, always accumulating, without an output-lane mask: the shortest operand list (every
-// operand of the instruction has to be moved to a uniform register first)
+// D[tmem] += A[tmem] . B[smem]^T, e4m3 x e4m3 -> f32, always accumulating, without an output-lane
+// mask: the shortest operand list (every operand of the instruction has to be moved to a uniform
+// register first)
 __device__ __forceinline__ void mma_ts_f8_acc(uint32_t d, uint32_t a, uint64_t bdesc, uint32_t idesc) {
   asm volatile(
       "{\n.reg .pred p;\nsetp.eq.b32 p, 0, 0;\n"
@@ -235,9 +210,6 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo,
 __host__ __device__ constexpr uint32_t make_idesc_f8(int M, int N) {
   return (1u << 4) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
-__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_u32(smem)), "l"(gmem) : "memory");
-}
 __device__ __forceinline__ void bulk_g2s(void* smem, const void* gmem, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(smem_u32(smem)), "l"(gmem), "r"(bytes), "r"(smem_u32(bar)) : "memory");
@@ -247,14 +219,6 @@ __device__ __forceinline__ void tma_load_3d(void* smem, const CUtensorMap* map, 
   asm volatile(
       "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
       ::"r"(smem_u32(smem)), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ float e4m3_to_float(uint8_t v) {
-  const __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)v, __NV_E4M3);
-  return __half2float(__half(h));
-}
-template <int I>
-__device__ __forceinline__ uint32_t expand(uint32_t word) {
-  return (word & (0x01010101u << I)) | (class_byte(I) * 0x01010101u);
 }
 // (word & mask_I) | c  in one LOP3: the mask is an immediate, the OR-constant a register
 template <int I>
@@ -269,7 +233,7 @@ __device__ __forceinline__ void expand_word_c(uint32_t word, const uint32_t (&c)
 }
 
 // ------------------------------------------------------------------ Z' preparation
-// grid = (n_chunks, total blocks), 256 threads.  Operand tile of word w (32 columns):
+// grid = (n_chunks, total blocks, input rows), 256 threads.  Operand tile of word w (32 columns):
 // byte offset (n%8)*16 + (n/8)*256 + (k%16) + (k/16)*128 with n = 16*piece + rank and
 // k = 4*i + c for the column 8c+7-i of the word.
 __global__ void __launch_bounds__(256) zprep_tc5_kernel(const __grid_constant__ TcParams P, const __half* __restrict__ x) {
@@ -294,7 +258,9 @@ __global__ void __launch_bounds__(256) zprep_tc5_kernel(const __grid_constant__ 
   pdl_wait();
   pdl_trigger();
 
-  if (blockIdx.x == 0 && blockIdx.y == 0) {
+  const int R = P.rows, row = blockIdx.z;
+  x += (int64_t)row * P.x_stride;
+  if (blockIdx.x == 0 && blockIdx.y == 0 && row == 0) {
     for (int i = tid; i < P.seg_base[P.n_weights]; i += blockDim.x) P.counters[i] = 0;
     if (tid == 0) *P.status = 0;
   }
@@ -328,7 +294,7 @@ __global__ void __launch_bounds__(256) zprep_tc5_kernel(const __grid_constant__ 
   const float bound = vmax * xm;
   const float scale = (bound > 0.f) ? (kTargetMax * kMinD) / (2.f * bound) : 1.f;
   const float inv_scale = 1.f / scale;
-  if (chunk == 0 && tid < 16) P.inv_scale[(int64_t)blockIdx.y * 16 + r] = inv_scale;
+  if (chunk == 0 && tid < 16) P.inv_scale[((int64_t)blockIdx.y * R + row) * 16 + r] = inv_scale;
 
   // z[lc] = vt * x for the 32 columns of the word
   float z[32];
@@ -342,7 +308,8 @@ __global__ void __launch_bounds__(256) zprep_tc5_kernel(const __grid_constant__ 
       z[2 * i + 1] = a.y * b.y;
     }
   }
-  uint8_t* tile = P.zops + ((int64_t)blockIdx.y * P.n_chunks + chunk) * kChunkBytes + word * 1024;
+  // the operand tile of a word holds the rows one after the other (row i = B columns 32i .. 32i+31)
+  uint8_t* tile = P.zops + (((int64_t)blockIdx.y * P.n_chunks + chunk) * 16 + word) * (1024 * R) + row * 1024;
   float c_sum = 0.f, z_sum = 0.f;
 #pragma unroll
   for (int kh = 0; kh < 2; ++kh) {
@@ -382,7 +349,7 @@ __global__ void __launch_bounds__(256) zprep_tc5_kernel(const __grid_constant__ 
     float v = 0.f;
 #pragma unroll
     for (int i = 0; i < 16; ++i) v += kred[i][tid];
-    P.kconst[((int64_t)blockIdx.y * P.n_chunks + chunk) * 16 + tid] = v;
+    P.kconst[(((int64_t)blockIdx.y * P.n_chunks + chunk) * R + row) * 16 + tid] = v;
   }
 }
 
@@ -416,11 +383,16 @@ __global__ void __launch_bounds__(256) zprep_tc5_kernel(const __grid_constant__ 
 // Every D is double buffered across block segments.  Tensor-memory columns:
 //   D(e, b) = e*64 + b*32           (4 x 32)
 //   A(e, s) = 128 + e*64 + s*32     (2 issuers x 2 stages x 4 MMAs)
-constexpr int kSignRingBytes = 6 * kSignTileBytes;
+// R = input rows per pass (1 or 2).  With two rows the B operand is 64 columns wide (one MMA serves both
+// rows: the sign expansion, the tensor-memory stores and the MMA issue are paid once), the Z' slab of a
+// step is 32 KB, and the accumulators (64 columns each) are single-buffered to stay inside 256 columns.
+template <int R>
 struct __align__(1024) SmemLayout {
-  uint8_t zs[kNZ][kChunkBytes];         // Z' operand slabs (bulk-copied)
-  uint8_t sg[kSignRingBytes];           // sign tiles: row r at r*64, 16-byte piece p at ((p ^ ((r>>1)&3)) * 16)
-  uint64_t afull[2][2], aempty[2][2], zfull[kNZ], zempty[kNZ], sfull[6], sempty[6], dfull[2][2], dempty[2];
+  static constexpr int kSlabs = (R == 1) ? kNZ : 2;          // Z' slabs resident
+  static constexpr int kSignTiles = (R == 1) ? 6 : 4;        // sign tiles resident
+  uint8_t zs[kSlabs][kChunkBytes * R];  // Z' operand slabs (bulk-copied)
+  uint8_t sg[kSignTiles * kSignTileBytes];   // sign tiles: row r at r*64, 16-byte piece p at ((p ^ ((r>>1)&3)) * 16)
+  uint64_t afull[2][2], aempty[2][2], zfull[kSlabs], zempty[kSlabs], sfull[6], sempty[6], dfull[2][2], dempty[2];
   unsigned long long trace[16];
   uint32_t tmem_base;
   int n_pending;
@@ -466,14 +438,19 @@ struct Walk {
   }
 };
 
-template <int RT>
+template <int RT, int R>
 __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_constant__ TcParams P) {
+  using Smem = SmemLayout<R>;
   constexpr int kSlotBytes = RT * kSignTileBytes;   // one ring slot = the RT sign tiles of a step
-  constexpr int kNS = 6 / RT;                       // ring slots
+  constexpr int kNS = Smem::kSignTiles / RT;        // ring slots
+  constexpr int kNZr = Smem::kSlabs;                // Z' ring slots
+  constexpr int kSlabBytes = kChunkBytes * R;       // Z' slab of one step
+  constexpr int kND = (R == 1) ? 2 : 1;             // accumulator buffers per pipeline
+  constexpr int kDCols = 32 * R;                    // columns of one accumulator
   constexpr int kPP = 2 * RT;                       // operand stages (4 MMAs each) per step and pipeline
   constexpr int kRows = RT * kTileRows;             // rows of a row group
   extern __shared__ uint8_t smem_raw[];
-  SmemLayout& S = *reinterpret_cast<SmemLayout*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  Smem& S = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
 
   pdl_trigger();   // the kernel after this one may be launched; it waits for this grid before it reads y
   const int NCH = P.n_chunks;
@@ -506,7 +483,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
         mbar_init(&S.aempty[e][i], 1);
         mbar_init(&S.dfull[e][i], 1);
       }
-    for (int i = 0; i < kNZ; ++i) { mbar_init(&S.zfull[i], 1); mbar_init(&S.zempty[i], 2); }
+    for (int i = 0; i < kNZr; ++i) { mbar_init(&S.zfull[i], 1); mbar_init(&S.zempty[i], 2); }
     for (int i = 0; i < kNS; ++i) { mbar_init(&S.sfull[i], 1); mbar_init(&S.sempty[i], 2 * kTileRows); }
     for (int i = 0; i < 2; ++i) mbar_init(&S.dempty[i], kTileRows);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -515,7 +492,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tbase = S.tmem_base;
-  const uint32_t colA = 128;
+  const uint32_t colA = 2 * kND * kDCols;   // = 128: accumulators D(e, b) at (e*kND + b)*kDCols, operand stages behind them
   if (warp == 0) TR_ADD(13, t_cta);
 
   if (warp == kWarpLoad) {
@@ -544,11 +521,11 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
       Walk wk;
       wk.init(P, step0, kRows);
       for (int g = 0; g < total; ++g) {
-        const int slot = g % kNZ, n = g / kNZ;
+        const int slot = g % kNZr, n = g / kNZr;
         if (n >= 1 && !mbar_wait_relaxed(&S.zempty[slot], (n - 1) & 1)) { atomicExch(P.status, 1); break; }
-        const uint8_t* zsrc = P.zops + ((int64_t)(P.blk_base[wk.wi] + wk.js) * NCH + wk.ci) * kChunkBytes;
-        mbar_expect_tx(&S.zfull[slot], kChunkBytes);
-        bulk_g2s(S.zs[slot], zsrc, kChunkBytes, &S.zfull[slot]);
+        const uint8_t* zsrc = P.zops + ((int64_t)(P.blk_base[wk.wi] + wk.js) * NCH + wk.ci) * kSlabBytes;
+        mbar_expect_tx(&S.zfull[slot], kSlabBytes);
+        bulk_g2s(S.zs[slot], zsrc, kSlabBytes, &S.zfull[slot]);
         wk.advance(P, kRows);
       }
     }
@@ -562,7 +539,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
       const int e = warp - kWarpMma;
       if (e != 0) tr = nullptr;
       const bool leader = elect_one();
-      const uint32_t idesc = make_idesc_f8(128, 32);
+      const uint32_t idesc = make_idesc_f8(128, kDCols);
       Walk wk;
       wk.init(P, step0, kRows);
       int it = 0, bs = 0;       // operand stages and block segments so far
@@ -570,19 +547,19 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
       bool ok = true;
       TR_BEGIN(t_mma);
       for (int g = 0; g < total && ok; ++g) {
-        const int b = bs & 1;
-        if (first && bs >= 2) {
+        const int b = bs % kND;
+        if (first && bs >= kND) {
           TR_BEGIN(t0);
-          if (!mbar_wait(&S.dempty[b], ((bs >> 1) - 1) & 1)) { if (leader) atomicExch(P.status, 6); ok = false; break; }
+          if (!mbar_wait(&S.dempty[b], ((bs / kND) - 1) & 1)) { if (leader) atomicExch(P.status, 6); ok = false; break; }
           TR_ADD(7, t0);
           tc_fence_after();
         }
-        const int zslot = g % kNZ;
+        const int zslot = g % kNZr;
         TR_BEGIN(t1);
-        if (!mbar_wait(&S.zfull[zslot], (g / kNZ) & 1)) { if (leader) atomicExch(P.status, 2); ok = false; break; }
+        if (!mbar_wait(&S.zfull[zslot], (g / kNZr) & 1)) { if (leader) atomicExch(P.status, 2); ok = false; break; }
         TR_ADD(5, t1);
-        const uint32_t zaddr = smem_u32(S.zs[zslot]) + (RT == 1 ? (uint32_t)e * 8u * 1024u : 0u);
-        const uint32_t dcol = tbase + e * 64 + b * 32;
+        const uint32_t zaddr = smem_u32(S.zs[zslot]) + (RT == 1 ? (uint32_t)e * 8u * 1024u * R : 0u);
+        const uint32_t dcol = tbase + (e * kND + b) * kDCols;
 #pragma unroll 1
         for (int pp = 0; pp < kPP; ++pp, ++it) {
           const int slot = it & 1;
@@ -591,14 +568,14 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
           TR_ADD(6, t2);
           TR_BEGIN(t3);
           tc_fence_after();
-          const uint64_t bdesc = make_smem_desc(zaddr + (uint32_t)(pp * 4) * 1024u, 128, 256);
+          const uint64_t bdesc = make_smem_desc(zaddr + (uint32_t)(pp * 4) * 1024u * R, 128, 256);
           const uint32_t acol = tbase + colA + e * 64 + slot * 32;
           if (leader) {
-            // 1 KB operand tiles follow each other: the descriptor's address field counts 16-byte units
+            // R KB operand tiles follow each other: the descriptor's address field counts 16-byte units
             mma_ts_f8_first(dcol, acol, bdesc, idesc, (!first || pp > 0) ? 1u : 0u);
-            mma_ts_f8_acc(dcol, acol + 8, bdesc + 64, idesc);
-            mma_ts_f8_acc(dcol, acol + 16, bdesc + 128, idesc);
-            mma_ts_f8_acc(dcol, acol + 24, bdesc + 192, idesc);
+            mma_ts_f8_acc(dcol, acol + 8, bdesc + 64 * R, idesc);
+            mma_ts_f8_acc(dcol, acol + 16, bdesc + 128 * R, idesc);
+            mma_ts_f8_acc(dcol, acol + 24, bdesc + 192 * R, idesc);
             mma_commit(&S.aempty[e][slot]);
           }
           TR_ADD(8, t3);
@@ -682,9 +659,11 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
     const int quarter = warp & 3;                     // tensor-memory lanes this warp may read
     const int rtid = quarter * 32 + lane;
     const uint32_t lane_base = tbase + ((uint32_t)(quarter * 32) << 16);
-    float yacc[RT];
+    float yacc[RT][R];
 #pragma unroll
-    for (int t = 0; t < RT; ++t) yacc[t] = 0.f;
+    for (int t = 0; t < RT; ++t)
+#pragma unroll
+      for (int r = 0; r < R; ++r) yacc[t][r] = 0.f;
     bool ok = true;
     Walk wk;
     wk.init(P, step0, kRows);
@@ -697,7 +676,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
       const int len = min(NCH - wk.ci, total - g);    // chunks of this block segment
       const bsb_weight& w = P.w[wk.wi];
       const int M = w.out_features;
-      const int j = wk.js, b = bs & 1;
+      const int j = wk.js, b = bs % kND;
       const int row0 = wk.rg * kRows;
       const int jb = P.blk_base[wk.wi] + j;
       // operands of this block segment's epilogue, fetched while its MMAs run
@@ -709,38 +688,45 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
         uq[t][0] = __ldg(reinterpret_cast<const uint4*>(u));
         uq[t][1] = __ldg(reinterpret_cast<const uint4*>(u) + 1);
       }
-      float inv_mine = 0.f, k_mine = 0.f;
-      if (lane < 16) {
-        inv_mine = P.inv_scale[(int64_t)jb * 16 + lane];
-        const float* kc = P.kconst + ((int64_t)jb * NCH + wk.ci) * 16 + lane;
-        for (int c = 0; c < len; ++c) k_mine += kc[c * 16];
+      float inv_mine[R], k_mine[R];
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        inv_mine[r] = 0.f;
+        k_mine[r] = 0.f;
+        if (lane < 16) {
+          inv_mine[r] = P.inv_scale[((int64_t)jb * R + r) * 16 + lane];
+          const float* kc = P.kconst + (((int64_t)jb * NCH + wk.ci) * R + r) * 16 + lane;
+          for (int c = 0; c < len; ++c) k_mine[r] += kc[c * R * 16];
+        }
       }
       TR_BEGIN(t0);
       if (RT == 1) {
-        const bool both = mbar_wait_warp_relaxed(&S.dfull[0][b], (bs >> 1) & 1) && mbar_wait_warp_relaxed(&S.dfull[1][b], (bs >> 1) & 1);
+        const bool both = mbar_wait_warp_relaxed(&S.dfull[0][b], (bs / kND) & 1) && mbar_wait_warp_relaxed(&S.dfull[1][b], (bs / kND) & 1);
         if (!both) { if (lane == 0) atomicExch(P.status, 5); ok = false; break; }
       }
       TR_ADD(9, t0);
 #pragma unroll
       for (int t = 0; t < RT; ++t) {
         if (RT == 2) {
-          if (!mbar_wait_warp_relaxed(&S.dfull[t][b], (bs >> 1) & 1)) { if (lane == 0) atomicExch(P.status, 5); ok = false; break; }
+          if (!mbar_wait_warp_relaxed(&S.dfull[t][b], (bs / kND) & 1)) { if (lane == 0) atomicExch(P.status, 5); ok = false; break; }
         }
         tc_fence_after();
         const uint32_t* uw = reinterpret_cast<const uint32_t*>(&uq[t][0]);
 #pragma unroll
+        for (int r = 0; r < R; ++r) {     // input row r = accumulator columns 32r .. 32r+31
+#pragma unroll
         for (int h = 0; h < 2; ++h) {   // ranks 8h .. 8h+7
           float T[8];
           uint32_t d0[8], d1[8];
-          const uint32_t c0 = lane_base + (RT == 1 ? 0 : t * 64) + b * 32 + h * 8;
+          const uint32_t c0 = lane_base + ((RT == 1 ? 0 : t * kND) + b) * kDCols + r * 32 + h * 8;
           tmem_ld8(c0, d0);        // hi piece
           tmem_ld8(c0 + 16, d1);   // lo piece
           tmem_wait_ld();
 #pragma unroll
           for (int i = 0; i < 8; ++i) T[i] = __uint_as_float(d0[i]) + __uint_as_float(d1[i]);
           if (RT == 1) {           // second issuer's accumulator (other K half)
-            tmem_ld8(c0 + 64, d0);
-            tmem_ld8(c0 + 64 + 16, d1);
+            tmem_ld8(c0 + kND * kDCols, d0);
+            tmem_ld8(c0 + kND * kDCols + 16, d1);
             tmem_wait_ld();
 #pragma unroll
             for (int i = 0; i < 8; ++i) T[i] += __uint_as_float(d0[i]) + __uint_as_float(d1[i]);
@@ -749,11 +735,12 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
           for (int rr = 0; rr < 4; ++rr) {
             const int r0 = 8 * h + 2 * rr;
             const __half2 h2 = *reinterpret_cast<const __half2*>(&uw[4 * h + rr]);
-            const float i0 = __shfl_sync(0xFFFFFFFFu, inv_mine, r0), i1 = __shfl_sync(0xFFFFFFFFu, inv_mine, r0 + 1);
-            const float k0 = __shfl_sync(0xFFFFFFFFu, k_mine, r0), k1 = __shfl_sync(0xFFFFFFFFu, k_mine, r0 + 1);
-            yacc[t] = fmaf(__low2float(h2), T[2 * rr] * i0 - k0, yacc[t]);
-            yacc[t] = fmaf(__high2float(h2), T[2 * rr + 1] * i1 - k1, yacc[t]);
+            const float i0 = __shfl_sync(0xFFFFFFFFu, inv_mine[r], r0), i1 = __shfl_sync(0xFFFFFFFFu, inv_mine[r], r0 + 1);
+            const float k0 = __shfl_sync(0xFFFFFFFFu, k_mine[r], r0), k1 = __shfl_sync(0xFFFFFFFFu, k_mine[r], r0 + 1);
+            yacc[t][r] = fmaf(__low2float(h2), T[2 * rr] * i0 - k0, yacc[t][r]);
+            yacc[t][r] = fmaf(__high2float(h2), T[2 * rr + 1] * i1 - k1, yacc[t][r]);
           }
+        }
         }
       }
       if (!ok) break;
@@ -764,20 +751,23 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
       const bool group_end = (wk.js == wk.NB - 1) && (wk.ci + len == NCH);
       if (group_end || g == total) {
         const bool direct = whole && group_end;
-        float* part = P.partials + ((int64_t)blockIdx.x * 2 + (first_seg ? 0 : 1)) * kRows;
+        float* part = P.partials + ((int64_t)blockIdx.x * 2 + (first_seg ? 0 : 1)) * (R * kRows);
 #pragma unroll
         for (int t = 0; t < RT; ++t) {
           const int m = row0 + t * kTileRows + rtid;
-          if (direct) {
-            if (m < M) {
-              float v = yacc[t];
-              if (w.bias) v += __half2float(reinterpret_cast<const __half*>(w.bias)[m]);
-              P.y[wk.wi][m] = __float2half_rn(v);
+#pragma unroll
+          for (int r = 0; r < R; ++r) {
+            if (direct) {
+              if (m < M) {
+                float v = yacc[t][r];
+                if (w.bias) v += __half2float(reinterpret_cast<const __half*>(w.bias)[m]);
+                P.y[wk.wi][(int64_t)r * P.y_stride[wk.wi] + m] = __float2half_rn(v);
+              }
+            } else {
+              part[r * kRows + t * kTileRows + rtid] = yacc[t][r];
             }
-          } else {
-            part[t * kTileRows + rtid] = yacc[t];
+            yacc[t][r] = 0.f;
           }
-          yacc[t] = 0.f;
         }
         if (!direct) {
           __threadfence();
@@ -837,14 +827,17 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
     __threadfence();
     const int m = rg * kRows + tid;
     if (tid < kRows && m < w.out_features) {
-      float sum = 0.f;
-      for (int c = c_first; c <= c_last; ++c) {
-        // the row group is CTA c's first row segment unless it starts after c's first step
-        const int slot = (gs <= c * L) ? 0 : 1;
-        sum += __ldcg(P.partials + ((int64_t)c * 2 + slot) * kRows + tid);
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        float sum = 0.f;
+        for (int c = c_first; c <= c_last; ++c) {
+          // the row group is CTA c's first row segment unless it starts after c's first step
+          const int slot = (gs <= c * L) ? 0 : 1;
+          sum += __ldcg(P.partials + (((int64_t)c * 2 + slot) * R + r) * kRows + tid);
+        }
+        if (w.bias) sum += __half2float(reinterpret_cast<const __half*>(w.bias)[m]);
+        P.y[wi][(int64_t)r * P.y_stride[wi] + m] = __float2half_rn(sum);
       }
-      if (w.bias) sum += __half2float(reinterpret_cast<const __half*>(w.bias)[m]);
-      P.y[wi][m] = __float2half_rn(sum);
     }
   }
 }
@@ -862,10 +855,12 @@ static int g_force_rt = 0;   // 0 = choose, 1 / 2 = forced (tuning)
 static int g_target_ctas = 0;   // 0 = two per multiprocessor, else this many (tuning)
 constexpr int kMinStepsPair = 4;
 
-void make_tc_plan(const bsb_weight* ws, int n, TcPlan& pl) {
+// R = input rows per pass (1 or 2).  The status word sits at offset 0 of the workspace whatever the plan.
+void make_tc_plan(const bsb_weight* ws, int n, int R, TcPlan& pl) {
   TcParams& P = pl.P;
   memset(&P, 0, sizeof(P));
   P.n_weights = n;
+  P.rows = R;
   const int N = ws[0].in_features;
   P.n_chunks = (int)ceil_div64(N, kChunkCols);
   // CTAs wanted: two per multiprocessor (both stay resident and share its tensor pipe)
@@ -901,20 +896,19 @@ void make_tc_plan(const bsb_weight* ws, int n, TcPlan& pl) {
   P.blk_base[n] = blks;
   const int tiles = segs;
   const int items = grid;
-  const int64_t part_floats = (int64_t)grid * 2 * RT * kTileRows;
+  const int64_t part_floats = (int64_t)grid * 2 * R * RT * kTileRows;
   pl.total_blocks = blks;
   pl.total_items = items;
-  int64_t off = 0;
+  pl.status_off = 0;
+  int64_t off = 256;
   const int64_t z_off = off;
-  off = align_up64(off + (int64_t)blks * P.n_chunks * kChunkBytes, 256);
+  off = align_up64(off + (int64_t)blks * P.n_chunks * kChunkBytes * R, 256);
   const int64_t k_off = off;
-  off = align_up64(off + (int64_t)blks * P.n_chunks * 16 * 4, 256);
+  off = align_up64(off + (int64_t)blks * P.n_chunks * R * 16 * 4, 256);
   const int64_t s_off = off;
-  off = align_up64(off + (int64_t)blks * 16 * 4, 256);
+  off = align_up64(off + (int64_t)blks * R * 16 * 4, 256);
   const int64_t c_off = off;
   off = align_up64(off + (int64_t)tiles * 4, 256);
-  pl.status_off = off;
-  off += 256;
   const int64_t p_off = off;
   off = align_up64(off + part_floats * 4, 256);
   for (int i = 0; i < n; ++i) {
@@ -987,29 +981,30 @@ bool gemv_tc5_supported(const bsb_weight& w) {
          ((uintptr_t)w.u % 16 == 0) && (w.u_block_stride % 8 == 0);
 }
 
-int64_t gemv_tc5_workspace_bytes(const bsb_weight* ws, int n_weights) {
-  if (n_weights < 1 || n_weights > kMaxGroup) return -1;
+int64_t gemv_tc5_workspace_bytes(const bsb_weight* ws, int n_weights, int rows_per_pass) {
+  if (n_weights < 1 || n_weights > kMaxGroup || rows_per_pass < 1 || rows_per_pass > 2) return -1;
   TcPlan pl;
-  make_tc_plan(ws, n_weights, pl);
+  make_tc_plan(ws, n_weights, rows_per_pass, pl);
   return pl.bytes;
 }
 
 int64_t gemv_tc5_status_offset(const bsb_weight* ws, int n_weights) {
-  if (n_weights < 1 || n_weights > kMaxGroup) return -1;
-  TcPlan pl;
-  make_tc_plan(ws, n_weights, pl);
-  return pl.status_off;
+  (void)ws;
+  return (n_weights < 1 || n_weights > kMaxGroup) ? -1 : 0;
 }
 
-int launch_gemv_tc5(const bsb_weight* ws, int n_weights, const __half* x, __half* const* ys, void* workspace,
-                    int64_t workspace_bytes, cudaStream_t s) {
+// rows = 1 or 2 input rows in one pass: x rows x_stride apart, row r of weight i goes to ys[i] + r * y_strides[i]
+// (y_strides may be nullptr when rows == 1)
+int launch_gemv_tc5(const bsb_weight* ws, int n_weights, const __half* x, int64_t x_stride, int rows, __half* const* ys,
+                    const int64_t* y_strides, void* workspace, int64_t workspace_bytes, cudaStream_t s) {
   BSB_CHECK_ARG(n_weights >= 1 && n_weights <= kMaxGroup, "gemv: 1..%d weights per group", kMaxGroup);
+  BSB_CHECK_ARG(rows == 1 || (rows == 2 && y_strides != nullptr && x_stride % 8 == 0), "gemv: 1 or 2 rows per pass (16-byte aligned rows)");
   for (int i = 0; i < n_weights; ++i) {
     BSB_CHECK_ARG(gemv_tc5_supported(ws[i]), "gemv: weight %d has an unsupported shape/alignment", i);
     BSB_CHECK_ARG(ws[i].in_features == ws[0].in_features, "gemv: grouped weights must share in_features");
   }
   TcPlan pl;
-  make_tc_plan(ws, n_weights, pl);
+  make_tc_plan(ws, n_weights, rows, pl);
   if (workspace == nullptr || workspace_bytes < pl.bytes) {
     set_error("gemv: workspace of %lld bytes needed, %lld given", (long long)pl.bytes, (long long)workspace_bytes);
     return BSB_EWORKSPACE;
@@ -1019,8 +1014,10 @@ int launch_gemv_tc5(const bsb_weight* ws, int n_weights, const __half* x, __half
   int dev = 0;
   BSB_CUDA(cudaGetDevice(&dev));
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    BSB_CUDA(cudaFuncSetAttribute(gemv_tc5_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SmemLayout) + 1024));
-    BSB_CUDA(cudaFuncSetAttribute(gemv_tc5_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SmemLayout) + 1024));
+    BSB_CUDA(cudaFuncSetAttribute(gemv_tc5_kernel<1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SmemLayout<1>) + 1024));
+    BSB_CUDA(cudaFuncSetAttribute(gemv_tc5_kernel<2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SmemLayout<1>) + 1024));
+    BSB_CUDA(cudaFuncSetAttribute(gemv_tc5_kernel<1, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SmemLayout<2>) + 1024));
+    BSB_CUDA(cudaFuncSetAttribute(gemv_tc5_kernel<2, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SmemLayout<2>) + 1024));
     attr_set[dev] = true;
   }
   TcParams& P = pl.P;
@@ -1033,8 +1030,10 @@ int launch_gemv_tc5(const bsb_weight* ws, int n_weights, const __half* x, __half
   P.status = (int*)(base + pl.status_off);
   P.trace = g_trace;
   P.dbg = g_dbg;
+  P.x_stride = x_stride;
   for (int i = 0; i < n_weights; ++i) {
     P.y[i] = ys[i];
+    P.y_stride[i] = y_strides ? y_strides[i] : 0;
     if (int rc = make_sign_map(ws[i], &P.sign_map[i])) return rc;
     if (ws[i].vt_absmax) {
       P.vt_absmax[i] = ws[i].vt_absmax;
@@ -1045,7 +1044,7 @@ int launch_gemv_tc5(const bsb_weight* ws, int n_weights, const __half* x, __half
     }
   }
   {
-    cudaError_t le = launch_pdl(zprep_tc5_kernel, dim3(P.n_chunks, pl.total_blocks), dim3(256), 0, s, P, x);
+    cudaError_t le = launch_pdl(zprep_tc5_kernel, dim3(P.n_chunks, pl.total_blocks, rows), dim3(256), 0, s, P, x);
     if (le != cudaSuccess) {
       set_error("launch of zprep_tc5_kernel failed: %s", cudaGetErrorString(le));
       return BSB_ECUDA;
@@ -1058,15 +1057,17 @@ int launch_gemv_tc5(const bsb_weight* ws, int n_weights, const __half* x, __half
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(pl.total_items);
     cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = sizeof(SmemLayout) + 1024;
+    cfg.dynamicSmemBytes = (rows == 2 ? sizeof(SmemLayout<2>) : sizeof(SmemLayout<1>)) + 1024;
     cfg.stream = s;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = g_pdl_enabled ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t le = pl.row_tiles == 2 ? cudaLaunchKernelEx(&cfg, gemv_tc5_kernel<2>, P)
-                                       : cudaLaunchKernelEx(&cfg, gemv_tc5_kernel<1>, P);
+    cudaError_t le = rows == 2 ? (pl.row_tiles == 2 ? cudaLaunchKernelEx(&cfg, gemv_tc5_kernel<2, 2>, P)
+                                                    : cudaLaunchKernelEx(&cfg, gemv_tc5_kernel<1, 2>, P))
+                               : (pl.row_tiles == 2 ? cudaLaunchKernelEx(&cfg, gemv_tc5_kernel<2, 1>, P)
+                                                    : cudaLaunchKernelEx(&cfg, gemv_tc5_kernel<1, 1>, P));
     if (le != cudaSuccess) {
       set_error("launch of gemv_tc5_kernel failed: %s", cudaGetErrorString(le));
       return BSB_ECUDA;
@@ -1094,7 +1095,7 @@ extern "C" int bsb_linear_forward_noalloc(const bsb_weight* w, const uint16_t* x
   BSB_CHECK_ARG(w->blocks >= 1 && gemv_tc5_supported(*w),
                 "noalloc forward: needs k == 16, in_features %% 128 == 0, 16-byte aligned tensors, >= 1 active block");
   BSB_CHECK_ARG(x_stride >= w->in_features && y_stride >= w->out_features, "row stride smaller than the row");
-  const int64_t need = gemv_tc5_workspace_bytes(w, 1);
+  const int64_t need = gemv_tc5_workspace_bytes(w, 1, 1);
   if (need > kNoAllocScratchBytes) {
     set_error("noalloc forward: this weight needs %lld bytes of scratch, the built-in area holds %lld "
               "(use bsb_linear_forward with a caller-provided workspace)", (long long)need, (long long)kNoAllocScratchBytes);
@@ -1112,8 +1113,8 @@ extern "C" int bsb_linear_forward_noalloc(const bsb_weight* w, const uint16_t* x
   }
   for (int64_t r = 0; r < rows; ++r) {
     __half* yr = reinterpret_cast<__half*>(y) + r * y_stride;
-    if (int rc = launch_gemv_tc5(w, 1, reinterpret_cast<const __half*>(x) + r * x_stride, &yr, scratch_ptr[dev],
-                                 kNoAllocScratchBytes, (cudaStream_t)stream))
+    if (int rc = launch_gemv_tc5(w, 1, reinterpret_cast<const __half*>(x) + r * x_stride, x_stride, 1, &yr, nullptr,
+                                 scratch_ptr[dev], kNoAllocScratchBytes, (cudaStream_t)stream))
       return rc;
   }
   return BSB_OK;

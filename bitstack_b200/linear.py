@@ -7,7 +7,7 @@ constructor, buffer names / shapes / dtypes (these are the checkpoint keys),
 (0-5) runs the same fused CUDA path here -- the levels only differed in how the
 reference staged its Triton kernels -- and extra levels pin one kernel:
 
-    0-5, 6  automatic choice (decode kernel for <= 4 rows, rebuild+GEMM above)
+    0-5, 6  automatic choice (decode kernel, two rows per pass, for <= 6 rows; rebuild + tcgen05 GEMM above)
     7       shape-agnostic CUDA-core kernel
     8       decode kernel, warp-level MMA generation, any row count
     9       rebuild fp16 weight + dense MMA

@@ -318,6 +318,34 @@ def test_batch_gemm_ragged_shapes(dev, rows, m, n, nb):
     assert st.value == 0
 
 
+@pytest.mark.parametrize("rows", [2, 3, 5, 6])
+def test_decode_kernel_row_pairs(dev, rows):
+    """Small batches run through the decode kernel two rows per pass (a last odd row alone): every row
+    must equal the single-row result bit for bit is NOT required (different operand widths), but each must
+    meet the same tolerance, alone and in a group of projections with different block counts."""
+    from bitstack_b200 import forward_grouped
+    mods, refs = [], []
+    x_np = orc.synthetic_input(rows, 1024, seed=rows)
+    x = torch.from_numpy(x_np).to(dev)
+    for i, (m, nb) in enumerate(((512, 3), (256, 1), (1280, 5))):
+        q, u, vt = orc.synthetic_layer(m, 1024, nb, seed=40 + i)
+        mods.append(make_module(q, u, vt, None, dev, level=10))
+        refs.append(orc.forward_f64(x_np, q, u, vt, nb, None))
+    for mod, ref in zip(mods, refs):
+        y = mod(x).float().cpu().numpy()
+        e_max, e_l2 = errs(y, ref)
+        assert e_max <= EXACT_TOL and e_l2 <= EXACT_TOL, (e_max, e_l2)
+    ys = forward_grouped(mods, x)
+    for y, ref in zip(ys, refs):
+        e_max, e_l2 = errs(y.float().cpu().numpy(), ref)
+        assert e_max <= EXACT_TOL and e_l2 <= EXACT_TOL, (e_max, e_l2)
+    # a strided (non-contiguous rows) input takes the same path
+    xs = torch.zeros(rows, 2048, dtype=torch.float16, device=dev)
+    xs[:, :1024] = x
+    y = mods[0](xs[:, :1024]).float().cpu().numpy()
+    assert errs(y, refs[0])[0] <= EXACT_TOL
+
+
 def test_linearity_and_block_additivity(dev):
     """Size-independent properties: y(a x1 + x2) = a y(x1) + y(x2); the output with b
     blocks equals the sum of single-block outputs."""
