@@ -49,6 +49,7 @@ SIGNATURES = {
     "bsb_rope_cache": (C.c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _I32, _I32, _I32, _I32, _I32, _P]),
     "bsb_decode_attention": (C.c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I32, _I32, _I32, _I32, _I32, _P, _I64, _P]),
     "bsb_decode_attention_scratch_bytes": (C.c_int64, [_I32, _I32, _I32]),
+    "bsb_greedy_step": (C.c_int, [_P, _I64, _I64, _I64, _P, _P, _P]),
     "bsb_silu_mul": (C.c_int, [_P, _P, _P, _I64, _P]),
     "bsb_noalloc_scratch_bytes": (_I64, []),
     "bsb_linear_forward_noalloc": (C.c_int, [_WP, _P, _I64, _I64, _P, _I64, _P]),

@@ -2,6 +2,8 @@
 // (a handful of rows): residual add + RMSNorm, rotary embedding + KV-cache write, SiLU*up.
 // The reference delegates these to the Hugging Face Llama modules (one PyTorch launch per
 // elementary op); at batch 1 the launches cost more than the math, hence the fusion.
+#include <cstdint>
+
 #include "common.cuh"
 
 namespace bsb {
@@ -290,6 +292,56 @@ __global__ void __launch_bounds__(256) decode_attention_kernel(const __half* __r
   }
 }
 
+// greedy sampling step: tokens[b] = index of the first maximum of logits[b][0..V), then *pos += 1.
+// One CTA per batch row, 16-byte loads; ties go to the lowest index (torch.argmax's rule).
+__global__ void __launch_bounds__(1024) greedy_step_kernel(const __half* __restrict__ logits, int64_t V, int64_t stride,
+                                                           int64_t* __restrict__ tokens, int64_t* __restrict__ pos) {
+  __shared__ float s_val[32];
+  __shared__ int64_t s_idx[32];
+  pdl_wait();
+  pdl_trigger();
+  const __half* row = logits + (int64_t)blockIdx.x * stride;
+  float best = -INFINITY;
+  int64_t best_i = INT64_MAX;
+  const bool vec_ok = (reinterpret_cast<uintptr_t>(row) % 16 == 0);
+  const int64_t n8 = vec_ok ? V / 8 : 0;
+  for (int64_t i = threadIdx.x; i < n8; i += blockDim.x) {
+    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(row) + i);
+    const __half* h = reinterpret_cast<const __half*>(&raw);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float f = __half2float(h[e]);
+      if (f > best) { best = f; best_i = i * 8 + e; }   // ascending index within a thread: the first maximum stays
+    }
+  }
+  for (int64_t i = n8 * 8 + threadIdx.x; i < V; i += blockDim.x) {
+    const float f = __half2float(row[i]);
+    if (f > best || (f == best && i < best_i)) { best = f; best_i = i; }
+  }
+  auto better = [](float a, int64_t ai, float b, int64_t bi) { return a > b || (a == b && ai < bi); };
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xFFFFFFFFu, best, o);
+    const int64_t oi = __shfl_xor_sync(0xFFFFFFFFu, best_i, o);
+    if (better(ov, oi, best, best_i)) { best = ov; best_i = oi; }
+  }
+  if ((threadIdx.x & 31) == 0) { s_val[threadIdx.x >> 5] = best; s_idx[threadIdx.x >> 5] = best_i; }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    const int nw = (blockDim.x + 31) / 32;
+    best = threadIdx.x < nw ? s_val[threadIdx.x] : -INFINITY;
+    best_i = threadIdx.x < nw ? s_idx[threadIdx.x] : INT64_MAX;
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xFFFFFFFFu, best, o);
+      const int64_t oi = __shfl_xor_sync(0xFFFFFFFFu, best_i, o);
+      if (better(ov, oi, best, best_i)) { best = ov; best_i = oi; }
+    }
+    if (threadIdx.x == 0) {
+      tokens[blockIdx.x] = best_i == INT64_MAX ? 0 : best_i;   // a row of NaNs: token 0
+      if (blockIdx.x == 0 && pos != nullptr) *pos += 1;
+    }
+  }
+}
+
 __global__ void __launch_bounds__(256) silu_mul_kernel(const __half2* __restrict__ g, const __half2* __restrict__ u,
                                                        __half2* __restrict__ out, int64_t n2) {
   pdl_wait();
@@ -367,6 +419,15 @@ int bsb_decode_attention(const uint16_t* q, const uint16_t* k, const uint16_t* v
                         (const __half*)q, (const __half*)k, (const __half*)v, (const __half*)cos_table, (const __half*)sin_table, pos,
                         (__half*)k_cache, (__half*)v_cache, (__half*)out, q_heads, kv_heads, max_len, scale, partial, counters));
   return check_launch("decode_attention_kernel");
+}
+
+int bsb_greedy_step(const uint16_t* logits, int64_t batch, int64_t vocab, int64_t row_stride, int64_t* tokens, int64_t* pos,
+                    void* stream) {
+  BSB_CHECK_ARG(logits && tokens, "NULL buffer");
+  BSB_CHECK_ARG(batch >= 1 && batch <= 65535 && vocab >= 1 && row_stride >= vocab, "bad shape");
+  BSB_CUDA(launch_pdl(greedy_step_kernel, dim3((unsigned)batch), dim3(1024), 0, (cudaStream_t)stream, (const __half*)logits,
+                      vocab, row_stride, tokens, pos));
+  return check_launch("greedy_step_kernel");
 }
 
 int bsb_silu_mul(const uint16_t* gate, const uint16_t* up, uint16_t* out, int64_t n, void* stream) {

@@ -199,11 +199,12 @@ class BitStackLlamaDecoder:
         B = self.batch
         hd = s.head_dim
         h = self.embed.index_select(0, self.tokens).contiguous()            # [B, hidden], residual stream
-        mask = (self.arange <= self.pos).view(1, 1, 1, self.max_len)
+        fused_att = hd in (64, 128) and self.max_len <= 8192
+        mask = None if fused_att else (self.arange <= self.pos).view(1, 1, 1, self.max_len)
         x = glue.add_rmsnorm(h, None, self.layers[0]["in_norm"], s.rms_eps)
         for i, lay in enumerate(self.layers):
             q, k, v = forward_grouped([lay["self_attn.q_proj"], lay["self_attn.k_proj"], lay["self_attn.v_proj"]], x)
-            if hd in (64, 128) and self.max_len <= 8192:
+            if fused_att:
                 att = glue.decode_attention(q, k, v, self.cos, self.sin, self.pos, self.k_cache[i], self.v_cache[i],
                                             self.q_local, self.kv_local, hd)
             else:
@@ -233,7 +234,12 @@ class BitStackLlamaDecoder:
     @torch.no_grad()
     def decode_step(self):
         """One greedy token for every sequence; position and token feedback stay on the device."""
-        logits = self._decode_fused() if self.fused_glue else self._forward(self.tokens.view(-1, 1), self.pos)
+        if self.fused_glue:
+            logits = self._decode_fused()
+            if logits.dtype == torch.float16 and logits.dim() == 2 and logits.stride(1) == 1:
+                return glue.greedy_step(logits, self.tokens, self.pos)
+        else:
+            logits = self._forward(self.tokens.view(-1, 1), self.pos)
         self.tokens.copy_(logits.argmax(-1))
         self.pos.add_(1)
         return self.tokens

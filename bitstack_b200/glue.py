@@ -67,6 +67,19 @@ def decode_attention(q, k, v, cos, sin, pos, k_cache, v_cache, q_heads, kv_heads
     return out
 
 
+def greedy_step(logits: torch.Tensor, tokens: torch.Tensor, pos) -> torch.Tensor:
+    """tokens[b] = argmax(logits[b]) (first maximum), then pos[0] += 1 (skipped when pos is None), in one launch.
+    logits: [batch, vocab] fp16 with unit inner stride; tokens: [batch] int64; pos: [1] int64 or None."""
+    assert logits.is_cuda and logits.dtype == torch.float16 and logits.dim() == 2 and logits.stride(1) == 1
+    assert tokens.dtype == torch.int64 and tokens.is_contiguous() and tokens.numel() == logits.shape[0]
+    assert pos is None or (pos.dtype == torch.int64 and pos.is_cuda)
+    with torch.cuda.device(logits.device):
+        rc = _lib.load().bsb_greedy_step(logits.data_ptr(), logits.shape[0], logits.shape[1], logits.stride(0), tokens.data_ptr(),
+                                         None if pos is None else pos.data_ptr(), _s(logits))
+    _lib.check(rc, "bsb_greedy_step")
+    return tokens
+
+
 def silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     assert gate.is_cuda and gate.dtype == torch.float16 and gate.is_contiguous() and up.is_contiguous()
     out = torch.empty_like(gate)

@@ -133,6 +133,8 @@ int64_t bsb_linear_grouped_workspace_bytes(const bsb_weight* ws, int32_t n_weigh
  *   token per batch row, grouped-query heads, fp32 softmax; out[batch][q_heads*dim].  head_dim 64 or 128,
  *   max_len <= 8192.  `scratch` (bsb_decode_attention_scratch_bytes, 16-byte aligned) must be ZERO before its
  *   first use and is left ready for the next call; calls sharing a scratch must be stream-ordered.
+ * bsb_greedy_step: tokens[b] = first index of the maximum of logits[b][0..vocab) (fp16 rows row_stride apart), then
+ *   *pos += 1 (pos may be NULL): the sampling and bookkeeping of a greedy decode step in one launch.
  * bsb_silu_mul: out = silu(gate) * up over n fp16 elements. */
 int bsb_add_rmsnorm(uint16_t* h, const uint16_t* delta, const uint16_t* weight, float eps, uint16_t* y, int64_t rows,
                     int32_t hidden, void* stream);
@@ -144,6 +146,8 @@ int bsb_decode_attention(const uint16_t* q, const uint16_t* k, const uint16_t* v
                          int32_t batch, int32_t q_heads, int32_t kv_heads, int32_t head_dim, int32_t max_len, void* scratch,
                          int64_t scratch_bytes, void* stream);
 int64_t bsb_decode_attention_scratch_bytes(int32_t batch, int32_t q_heads, int32_t head_dim);
+int bsb_greedy_step(const uint16_t* logits, int64_t batch, int64_t vocab, int64_t row_stride, int64_t* tokens, int64_t* pos,
+                    void* stream);
 int bsb_silu_mul(const uint16_t* gate, const uint16_t* up, uint16_t* out, int64_t n, void* stream);
 
 /* Forward for callers that may not allocate device memory.  It has no counterpart in the

@@ -97,6 +97,27 @@ def test_decode_attention_matches_rope_then_sdpa(dev, B, Hq, Hkv, D, L, at):
     assert (out.float() - ref).abs().max() <= 3e-3 * ref.abs().max()
 
 
+def test_greedy_step_is_argmax_with_first_index_ties(dev):
+    from bitstack_b200 import glue
+    g = torch.Generator(device=dev).manual_seed(9)
+    for B, V in ((1, 128256), (3, 1000), (2, 7), (4, 32000)):
+        logits = torch.randn(B, V, device=dev, generator=g).half()
+        logits[0, V // 2] = 9.0
+        logits[0, V - 1] = 9.0          # tie: the lower index wins
+        if B > 1:
+            logits[1, 0] = 11.0
+        tokens = torch.zeros(B, dtype=torch.long, device=dev)
+        pos = torch.tensor([41], device=dev)
+        glue.greedy_step(logits, tokens, pos)
+        assert torch.equal(tokens, logits.float().argmax(-1)) and tokens[0].item() == V // 2
+        assert pos.item() == 42
+        # a view with a row stride larger than the vocabulary, no position update
+        wide = torch.zeros(B, V + 8, device=dev, dtype=torch.float16)
+        wide[:, :V] = logits
+        glue.greedy_step(wide[:, :V], tokens.zero_(), None)
+        assert torch.equal(tokens, logits.float().argmax(-1))
+
+
 def test_fused_decode_step_matches_unfused(dev):
     from bitstack_b200 import decode
     shape = decode.LlamaShape("tiny", 2, 512, 4, 2, 1024, vocab=1000)
