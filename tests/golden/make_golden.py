@@ -53,7 +53,9 @@ def _import_reference(ref_root):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <path to a checkout of the reference repository>")
+    ref_root = sys.argv[1]
     BitStackLinear, pack_utils, model_utils = _import_reference(ref_root)
     sys.path.insert(0, ROOT)
     from oracle import bitstack_oracle as orc
