@@ -162,6 +162,24 @@ def test_forward_matches_reference_synthetic(dev, golden_dir, level):
         assert e_max <= EXACT_TOL and e_l2 <= EXACT_TOL, ("f64", level, key, rows, a, e_max, e_l2)
 
 
+# shards of the 8B projections at tensor-parallel degree 8 (output rows / input columns divided by 8): the shapes the
+# decode kernel sees on each rank, among them an input width (1792) that ends inside a 512-column chunk
+TP8_SHARDS = {"q": (512, 4096), "k": (128, 4096), "o": (4096, 512), "gate": (1792, 4096), "down": (4096, 1792)}
+
+
+@pytest.mark.parametrize("name", list(TP8_SHARDS))
+@pytest.mark.parametrize("rows", [1, 2, 16])
+def test_tensor_parallel_shard_shapes(dev, name, rows):
+    m, n = TP8_SHARDS[name]
+    nb = 5
+    q, u, vt = orc.synthetic_layer(m, n, nb, seed=300 + m % 97 + n % 89)
+    x_np = orc.synthetic_input(rows, n, seed=3 + rows)
+    mod = make_module(q, u, vt, None, dev, level=6)
+    y = mod(torch.from_numpy(x_np).to(dev)).float().cpu().numpy()
+    e_max, e_l2 = errs(y, orc.forward_f64(x_np, q, u, vt, nb, None))
+    assert e_max <= EXACT_TOL and e_l2 <= EXACT_TOL, (name, rows, e_max, e_l2)
+
+
 # --------------------------------------------------------------------------- benchmark shapes
 LLAMA8B = {"q": (4096, 4096), "k": (1024, 4096), "gate": (14336, 4096), "down": (4096, 14336)}
 
