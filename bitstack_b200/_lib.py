@@ -24,6 +24,18 @@ class BsbWeight(C.Structure):
     ]
 
 
+class BsbInputTransform(C.Structure):
+    """Mirror of `struct bsb_input_transform`."""
+    _fields_ = [
+        ("mode", C.c_int32), ("eps", C.c_float),
+        ("x2", C.c_void_p), ("norm_weight", C.c_void_p), ("h_out", C.c_void_p),
+        ("x2_stride", C.c_int64), ("h_out_stride", C.c_int64),
+    ]
+
+
+INPUT_PLAIN, INPUT_ADD_RMSNORM, INPUT_SILU_MUL = 0, 1, 2
+
+
 class BitStackLibraryError(RuntimeError):
     pass
 
@@ -44,6 +56,7 @@ SIGNATURES = {
     "bsb_linear_workspace_bytes": (_I64, [_WP, _I64, C.c_int]),
     "bsb_linear_forward": (C.c_int, [_WP, _P, _I64, _I64, _P, _I64, _P, _I64, C.c_int, _P]),
     "bsb_linear_forward_grouped": (C.c_int, [_WP, _I32, _P, _I64, _I64, C.POINTER(_P), C.POINTER(_I64), _P, _I64, C.c_int, _P]),
+    "bsb_linear_forward_grouped_tf": (C.c_int, [_WP, _I32, _P, _I64, _I64, C.POINTER(BsbInputTransform), C.POINTER(_P), C.POINTER(_I64), _P, _I64, _P]),
     "bsb_linear_grouped_workspace_bytes": (_I64, [_WP, _I32, _I64, C.c_int]),
     "bsb_add_rmsnorm": (C.c_int, [_P, _P, _P, C.c_float, _P, _I64, _I32, _P]),
     "bsb_rope_cache": (C.c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _I32, _I32, _I32, _I32, _I32, _P]),

@@ -113,7 +113,9 @@ void gemv_tc5_set_trace(unsigned long long* device_buffer);
 void gemv_tc5_set_dbg(int mode);
 void gemv_tc5_set_pdl(int on);
 int64_t gemv_tc5_status_offset(const bsb_weight* ws, int n_weights);
+// `tf` (may be nullptr): input transform applied while the Z' operand is built, see bsb_input_transform
 int launch_gemv_tc5(const bsb_weight* ws, int n_weights, const __half* x, int64_t x_stride, int rows, __half* const* ys,
-                    const int64_t* y_strides, void* workspace, int64_t workspace_bytes, cudaStream_t s);
+                    const int64_t* y_strides, void* workspace, int64_t workspace_bytes, cudaStream_t s,
+                    const bsb_input_transform* tf = nullptr);
 
 }  // namespace bsb

@@ -63,6 +63,15 @@ struct alignas(64) TcParams {
   int rows;                        // input rows of this pass (1 or 2): the B operand holds 32 columns per row
   int64_t x_stride;                // elements between input rows
   int64_t y_stride[kMaxGroup];     // elements between output rows
+  // input transform applied while Z' is built (bsb_input_mode): 0 = x as given; 1 = x = rmsnorm(x + x2) * norm_w with
+  // the sum x + x2 (fp16) also written to h_out; 2 = x = silu(x) * x2
+  int x_mode;
+  const __half* x2;                // second operand of the transform (may be nullptr in mode 1), rows x2_stride apart
+  int64_t x2_stride;
+  const __half* norm_w;
+  float eps;
+  __half* h_out;                   // mode 1: the updated residual stream, rows h_out_stride apart
+  int64_t h_out_stride;
   int n_chunks;                    // ceil(in / 512)
   int step_base[kMaxGroup + 1];    // first work step of each weight; a step = (row group, block, chunk)
   int seg_base[kMaxGroup + 1];     // first row group of each weight (index of its counter)
@@ -237,7 +246,7 @@ __device__ __forceinline__ void expand_word_c(uint32_t word, const uint32_t (&c)
 // byte offset (n%8)*16 + (n/8)*256 + (k%16) + (k/16)*128 with n = 16*piece + rank and
 // k = 4*i + c for the column 8c+7-i of the word.
 __global__ void __launch_bounds__(256) zprep_tc5_kernel(const __grid_constant__ TcParams P, const __half* __restrict__ x) {
-  __shared__ float red[8];
+  __shared__ float red[8], red2[8];
   __shared__ float kred[16][16];
 
   const int chunk = blockIdx.x;
@@ -264,6 +273,28 @@ __global__ void __launch_bounds__(256) zprep_tc5_kernel(const __grid_constant__ 
     for (int i = tid; i < P.seg_base[P.n_weights]; i += blockDim.x) P.counters[i] = 0;
     if (tid == 0) *P.status = 0;
   }
+  // 8 consecutive values of the transform's pre-normalisation input: x (mode 0), silu(x) * x2 rounded as the
+  // stand-alone kernel rounds it (mode 2), or the fp16 sum x + x2 (mode 1)
+  const int mode = P.x_mode;
+  const __half* x2 = P.x2 ? P.x2 + (int64_t)row * P.x2_stride : nullptr;
+  auto load8 = [&](int i8) -> uint4 {
+    uint4 a = __ldg(reinterpret_cast<const uint4*>(x) + i8);
+    if (mode == 0 || x2 == nullptr) return a;
+    const uint4 b = __ldg(reinterpret_cast<const uint4*>(x2) + i8);
+    __half2* ah = reinterpret_cast<__half2*>(&a);
+    const __half2* bh = reinterpret_cast<const __half2*>(&b);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 fa = __half22float2(ah[i]), fb = __half22float2(bh[i]);
+      if (mode == 1) {
+        ah[i] = __floats2half2_rn(fa.x + fb.x, fa.y + fb.y);
+      } else {
+        const float2 sf = __half22float2(__floats2half2_rn(fa.x / (1.f + __expf(-fa.x)), fa.y / (1.f + __expf(-fa.y))));
+        ah[i] = __floats2half2_rn(sf.x * fb.x, sf.y * fb.y);
+      }
+    }
+    return a;
+  };
   // issue every load first: Vt and x words of this thread, then the pass over x for max |x|
   uint4 vq[4], xq[4];
   const __half* vt = reinterpret_cast<const __half*>(w.vt) + (int64_t)j * w.vt_block_stride + (int64_t)r * N;
@@ -271,24 +302,60 @@ __global__ void __launch_bounds__(256) zprep_tc5_kernel(const __grid_constant__ 
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     vq[i] = in_range ? __ldg(reinterpret_cast<const uint4*>(vt + col0) + i) : make_uint4(0, 0, 0, 0);
-    xq[i] = in_range ? __ldg(reinterpret_cast<const uint4*>(x + col0) + i) : make_uint4(0, 0, 0, 0);
+    xq[i] = in_range ? load8(col0 / 8 + i) : make_uint4(0, 0, 0, 0);
   }
-  float xm = 0.f;
+  float xm = 0.f, ss = 0.f;
+  const bool writer = (mode == 1 && P.h_out != nullptr && blockIdx.x == 0 && blockIdx.y == 0);
   for (int n8 = tid; n8 < N / 8; n8 += blockDim.x) {
-    const uint4 q = __ldg(reinterpret_cast<const uint4*>(x) + n8);
+    const uint4 q = load8(n8);
     const __half2* h = reinterpret_cast<const __half2*>(&q);
+    if (mode == 1) {
+      if (writer) reinterpret_cast<uint4*>(P.h_out + (int64_t)row * P.h_out_stride)[n8] = q;
+      const uint4 wv = __ldg(reinterpret_cast<const uint4*>(P.norm_w) + n8);
+      const __half2* wh = reinterpret_cast<const __half2*>(&wv);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float2 f = __half22float2(__habs2(h[i]));
-      xm = fmaxf(xm, fmaxf(f.x, f.y));
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(h[i]), g = __half22float2(wh[i]);
+        ss += f.x * f.x + f.y * f.y;
+        xm = fmaxf(xm, fmaxf(fabsf(f.x * g.x), fabsf(f.y * g.y)));
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(__habs2(h[i]));
+        xm = fmaxf(xm, fmaxf(f.x, f.y));
+      }
     }
   }
-  for (int o = 16; o > 0; o >>= 1) xm = fmaxf(xm, __shfl_xor_sync(0xFFFFFFFFu, xm, o));
-  if (lane == 0) red[warp] = xm;
+  for (int o = 16; o > 0; o >>= 1) {
+    xm = fmaxf(xm, __shfl_xor_sync(0xFFFFFFFFu, xm, o));
+    ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+  }
+  if (lane == 0) { red[warp] = xm; red2[warp] = ss; }
   __syncthreads();
   xm = red[0];
+  ss = red2[0];
 #pragma unroll
-  for (int i = 1; i < 8; ++i) xm = fmaxf(xm, red[i]);
+  for (int i = 1; i < 8; ++i) { xm = fmaxf(xm, red[i]); ss += red2[i]; }
+  if (mode == 1) {
+    // x = (x + x2) * rsqrt(mean square + eps) * norm_w, rounded to fp16 like the stand-alone kernel; the bound on
+    // |x| is taken a hair larger to cover that rounding
+    const float inv = rsqrtf(ss / (float)N + P.eps);
+    xm = xm * inv * 1.001f;
+    if (in_range) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint4 wv = __ldg(reinterpret_cast<const uint4*>(P.norm_w + col0) + i);
+        const __half2* wh = reinterpret_cast<const __half2*>(&wv);
+        __half2* xh = reinterpret_cast<__half2*>(&xq[i]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __half22float2(xh[e]), g = __half22float2(wh[e]);
+          xh[e] = __floats2half2_rn(f.x * inv * g.x, f.y * inv * g.y);
+        }
+      }
+    }
+  }
 
   const float vmax = P.vt_absmax[wi][j * 16 + r];
   const float bound = vmax * xm;
@@ -996,8 +1063,16 @@ int64_t gemv_tc5_status_offset(const bsb_weight* ws, int n_weights) {
 // rows = 1 or 2 input rows in one pass: x rows x_stride apart, row r of weight i goes to ys[i] + r * y_strides[i]
 // (y_strides may be nullptr when rows == 1)
 int launch_gemv_tc5(const bsb_weight* ws, int n_weights, const __half* x, int64_t x_stride, int rows, __half* const* ys,
-                    const int64_t* y_strides, void* workspace, int64_t workspace_bytes, cudaStream_t s) {
+                    const int64_t* y_strides, void* workspace, int64_t workspace_bytes, cudaStream_t s,
+                    const bsb_input_transform* tf) {
   BSB_CHECK_ARG(n_weights >= 1 && n_weights <= kMaxGroup, "gemv: 1..%d weights per group", kMaxGroup);
+  if (tf != nullptr && tf->mode != BSB_INPUT_PLAIN) {
+    BSB_CHECK_ARG(tf->mode == BSB_INPUT_ADD_RMSNORM || tf->mode == BSB_INPUT_SILU_MUL, "gemv: unknown input transform %d", tf->mode);
+    BSB_CHECK_ARG(tf->mode != BSB_INPUT_SILU_MUL || tf->x2 != nullptr, "gemv: silu*mul needs the second operand");
+    BSB_CHECK_ARG(tf->mode != BSB_INPUT_ADD_RMSNORM || tf->norm_weight != nullptr, "gemv: rmsnorm needs its weight");
+    BSB_CHECK_ARG(((uintptr_t)tf->x2 | (uintptr_t)tf->norm_weight | (uintptr_t)tf->h_out) % 16 == 0 && tf->x2_stride % 8 == 0 &&
+                  tf->h_out_stride % 8 == 0, "gemv: transform operands must be 16-byte aligned");
+  }
   BSB_CHECK_ARG(rows == 1 || (rows == 2 && y_strides != nullptr && x_stride % 8 == 0), "gemv: 1 or 2 rows per pass (16-byte aligned rows)");
   for (int i = 0; i < n_weights; ++i) {
     BSB_CHECK_ARG(gemv_tc5_supported(ws[i]), "gemv: weight %d has an unsupported shape/alignment", i);
@@ -1031,6 +1106,15 @@ int launch_gemv_tc5(const bsb_weight* ws, int n_weights, const __half* x, int64_
   P.trace = g_trace;
   P.dbg = g_dbg;
   P.x_stride = x_stride;
+  if (tf != nullptr) {
+    P.x_mode = tf->mode;
+    P.x2 = reinterpret_cast<const __half*>(tf->x2);
+    P.x2_stride = tf->x2_stride;
+    P.norm_w = reinterpret_cast<const __half*>(tf->norm_weight);
+    P.eps = tf->eps;
+    P.h_out = reinterpret_cast<__half*>(tf->h_out);
+    P.h_out_stride = tf->h_out_stride;
+  }
   for (int i = 0; i < n_weights; ++i) {
     P.y[i] = ys[i];
     P.y_stride[i] = y_strides ? y_strides[i] : 0;

@@ -284,3 +284,56 @@ def forward_grouped(modules, x, algo=_lib.ALGO_AUTO):
                                             torch.cuda.current_stream(x.device).cuda_stream)
     _lib.check(rc, "bsb_linear_forward_grouped")
     return [y.reshape(*x.shape[:-1], m.out_features) for y, m in zip(ys, modules)]
+
+
+def transform_supported(modules, rows: int) -> bool:
+    """Whether `forward_grouped_transformed` can take these modules and this many rows (decode path only)."""
+    return 1 <= rows <= 6 and 1 <= len(modules) <= 4 and all(
+        m.k == 16 and m.in_features % 128 == 0 and m.w_bit > 0 and m.in_features == modules[0].in_features for m in modules)
+
+
+def forward_grouped_transformed(modules, x, *, add=None, norm_weight=None, eps=1e-5, h_out=None, silu_mul=None):
+    """`forward_grouped` on a transformed input, without a separate launch for the transform:
+
+        norm_weight given:  the projections see rmsnorm(x + add) * norm_weight (add may be None); the fp16 sum
+                            x + add is written to `h_out` (same shape as x; must not alias x or add) if given
+        silu_mul given:     the projections see silu(x) * silu_mul
+
+    x: [rows, in_features] fp16 CUDA, rows <= 6 (see `transform_supported`).  Returns the list of outputs."""
+    assert (norm_weight is None) != (silu_mul is None), "exactly one of norm_weight / silu_mul"
+    x2 = x.reshape(-1, x.shape[-1])
+    assert x2.is_cuda and x2.dtype == torch.float16 and x2.stride(-1) == 1
+    rows, n = x2.shape[0], len(modules)
+    tf = _lib.BsbInputTransform()
+    other = add if norm_weight is not None else silu_mul
+    if other is not None:
+        other = other.reshape(rows, -1)
+        assert other.dtype == torch.float16 and other.shape == x2.shape and other.stride(-1) == 1
+        tf.x2, tf.x2_stride = other.data_ptr(), other.stride(0)
+    if norm_weight is not None:
+        assert norm_weight.dtype == torch.float16 and norm_weight.is_contiguous() and norm_weight.numel() == x2.shape[1]
+        tf.mode, tf.norm_weight, tf.eps = _lib.INPUT_ADD_RMSNORM, norm_weight.data_ptr(), float(eps)
+        if h_out is not None:
+            ho = h_out.reshape(rows, -1)
+            assert ho.dtype == torch.float16 and ho.shape == x2.shape and ho.stride(-1) == 1
+            assert ho.data_ptr() != x2.data_ptr() and (other is None or ho.data_ptr() != other.data_ptr())
+            tf.h_out, tf.h_out_stride = ho.data_ptr(), ho.stride(0)
+    else:
+        tf.mode = _lib.INPUT_SILU_MUL
+    descs = (_lib.BsbWeight * n)()
+    for i, m in enumerate(modules):
+        C.memmove(C.byref(descs[i]), C.byref(m.weight_desc(x.device)), C.sizeof(_lib.BsbWeight))
+    ys = [torch.empty(rows, m.out_features, dtype=torch.float16, device=x.device) for m in modules]
+    yptrs = (C.c_void_p * n)(*[y.data_ptr() for y in ys])
+    ystr = (C.c_int64 * n)(*[m.out_features for m in modules])
+    lib = _lib.load()
+    with torch.cuda.device(x.device):
+        need = lib.bsb_linear_grouped_workspace_bytes(descs, n, rows, _lib.ALGO_AUTO)
+        if need < 0:
+            raise ValueError("grouped workspace query rejected the arguments: " + lib.bsb_last_error().decode())
+        ws = get_workspace(x.device, need)
+        rc = lib.bsb_linear_forward_grouped_tf(descs, n, x2.data_ptr(), rows, x2.stride(0) if rows > 1 else x2.shape[-1],
+                                               C.byref(tf), yptrs, ystr, ws.data_ptr(), ws.numel(),
+                                               torch.cuda.current_stream(x.device).cuda_stream)
+    _lib.check(rc, "bsb_linear_forward_grouped_tf")
+    return [y.reshape(*x.shape[:-1], m.out_features) for y, m in zip(ys, modules)]

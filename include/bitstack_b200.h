@@ -117,6 +117,31 @@ int bsb_linear_forward_grouped(const bsb_weight* ws, int32_t n_weights, const ui
                                const int64_t* y_strides, void* workspace, int64_t workspace_bytes,
                                int algo, void* stream);
 
+/* Input transform of bsb_linear_forward_grouped_tf: what the projections multiply is not x itself but
+ *   BSB_INPUT_ADD_RMSNORM: rmsnorm(x + x2) * norm_weight (x2 may be NULL); the fp16 sum x + x2, the updated
+ *                          residual stream, is also written to h_out (may be NULL; must not alias x or x2);
+ *   BSB_INPUT_SILU_MUL:    silu(x) * x2.
+ * Both are computed while the decode kernel's operand is prepared, with the roundings of the stand-alone
+ * bsb_add_rmsnorm / bsb_silu_mul, so a decode step needs no separate launch for them.  No counterpart in the
+ * reference (it leaves these ops to the Hugging Face modules around the projections). */
+enum { BSB_INPUT_PLAIN = 0, BSB_INPUT_ADD_RMSNORM = 1, BSB_INPUT_SILU_MUL = 2 };
+typedef struct bsb_input_transform {
+  int32_t mode;
+  float eps;                   /* rmsnorm epsilon */
+  const uint16_t* x2;          /* fp16 [rows][in_features], rows x2_stride apart */
+  const uint16_t* norm_weight; /* fp16 [in_features] */
+  uint16_t* h_out;             /* fp16 [rows][in_features], rows h_out_stride apart */
+  int64_t x2_stride;
+  int64_t h_out_stride;
+} bsb_input_transform;
+
+/* bsb_linear_forward_grouped with an input transform.  Decode path only: rows <= 6, every weight with k == 16,
+ * in_features % 128 == 0 and 16-byte aligned tensors; anything else returns BSB_EINVAL (apply the transform with
+ * the stand-alone kernels and call bsb_linear_forward_grouped).  Scratch: bsb_linear_grouped_workspace_bytes. */
+int bsb_linear_forward_grouped_tf(const bsb_weight* ws, int32_t n_weights, const uint16_t* x, int64_t rows,
+                                  int64_t x_stride, const bsb_input_transform* tf, uint16_t* const* ys,
+                                  const int64_t* y_strides, void* workspace, int64_t workspace_bytes, void* stream);
+
 /* Scratch bytes bsb_linear_forward_grouped needs. */
 int64_t bsb_linear_grouped_workspace_bytes(const bsb_weight* ws, int32_t n_weights, int64_t rows, int algo);
 
