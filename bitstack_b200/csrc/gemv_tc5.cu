@@ -245,6 +245,8 @@ __device__ __forceinline__ void expand_word_c(uint32_t word, const uint32_t (&c)
 // grid = (n_chunks, total blocks, input rows), 256 threads.  Operand tile of word w (32 columns):
 // byte offset (n%8)*16 + (n/8)*256 + (k%16) + (k/16)*128 with n = 16*piece + rank and
 // k = 4*i + c for the column 8c+7-i of the word.
+// MODE = the input transform (bsb_input_transform.mode), a template parameter so that the plain path carries none of it
+template <int MODE>
 __global__ void __launch_bounds__(256) zprep_tc5_kernel(const __grid_constant__ TcParams P, const __half* __restrict__ x) {
   __shared__ float red[8], red2[8];
   __shared__ float kred[16][16];
@@ -275,7 +277,7 @@ __global__ void __launch_bounds__(256) zprep_tc5_kernel(const __grid_constant__ 
   }
   // 8 consecutive values of the transform's pre-normalisation input: x (mode 0), silu(x) * x2 rounded as the
   // stand-alone kernel rounds it (mode 2), or the fp16 sum x + x2 (mode 1)
-  const int mode = P.x_mode;
+  constexpr int mode = MODE;
   const __half* x2 = P.x2 ? P.x2 + (int64_t)row * P.x2_stride : nullptr;
   auto load8 = [&](int i8) -> uint4 {
     uint4 a = __ldg(reinterpret_cast<const uint4*>(x) + i8);
@@ -1128,7 +1130,10 @@ int launch_gemv_tc5(const bsb_weight* ws, int n_weights, const __half* x, int64_
     }
   }
   {
-    cudaError_t le = launch_pdl(zprep_tc5_kernel, dim3(P.n_chunks, pl.total_blocks, rows), dim3(256), 0, s, P, x);
+    const dim3 zgrid(P.n_chunks, pl.total_blocks, rows);
+    cudaError_t le = P.x_mode == BSB_INPUT_ADD_RMSNORM ? launch_pdl(zprep_tc5_kernel<1>, zgrid, dim3(256), 0, s, P, x)
+                   : P.x_mode == BSB_INPUT_SILU_MUL  ? launch_pdl(zprep_tc5_kernel<2>, zgrid, dim3(256), 0, s, P, x)
+                                                      : launch_pdl(zprep_tc5_kernel<0>, zgrid, dim3(256), 0, s, P, x);
     if (le != cudaSuccess) {
       set_error("launch of zprep_tc5_kernel failed: %s", cudaGetErrorString(le));
       return BSB_ECUDA;
