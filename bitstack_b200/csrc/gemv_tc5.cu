@@ -76,7 +76,12 @@ struct alignas(64) TcParams {
   int step_base[kMaxGroup + 1];    // first work step of each weight; a step = (row group, block, chunk)
   int seg_base[kMaxGroup + 1];     // first row group of each weight (index of its counter)
   int blk_base[kMaxGroup + 1];
-  int steps_per_cta;               // every CTA takes this many consecutive steps (the last one fewer)
+  // CTAs 0 .. n_first-1 take steps_first consecutive steps each, the others steps_per_cta (the last one fewer).
+  // n_first > 0 only when unequal shares are selected (tuning knob): the first CTA to become resident on a
+  // multiprocessor runs ~1.3x faster than the second one while both are there (its older warps win the issue
+  // arbitration).
+  int n_first, steps_first;
+  int steps_per_cta;
   uint8_t* zops;     // [(weight,block)][chunk][16 words][rows][1 KB]
   float* kconst;     // [(weight,block)][chunk][rows][16]
   float* inv_scale;  // [(weight,block)][rows][16]
@@ -473,6 +478,14 @@ constexpr int kWarpMma = 8;     // warps 8, 9: MMA issuers 0, 1
 constexpr int kWarpLoad = 10;   // warp 10: tensor-memory allocation, sign tiles (TMA); warp 11: Z' slabs (bulk copies)
 constexpr int kWarpEpi = 12;    // warps 12-15: epilogue (tensor-memory lane quarters 0-3)
 
+__device__ __forceinline__ int first_step_of_cta(const TcParams& P, int c) {
+  return c < P.n_first ? c * P.steps_first : P.n_first * P.steps_first + (c - P.n_first) * P.steps_per_cta;
+}
+__device__ __forceinline__ int cta_of_step(const TcParams& P, int step) {
+  const int b = P.n_first * P.steps_first;
+  return step < b ? step / P.steps_first : P.n_first + (step - b) / P.steps_per_cta;
+}
+
 // position of a step in (weight, row group, block, chunk) order
 struct Walk {
   int wi, rg, js, ci, NB, n_rg;
@@ -523,8 +536,8 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
 
   pdl_trigger();   // the kernel after this one may be launched; it waits for this grid before it reads y
   const int NCH = P.n_chunks;
-  const int step0 = blockIdx.x * P.steps_per_cta;
-  const int total = min(P.steps_per_cta, P.step_base[P.n_weights] - step0);   // steps of this CTA
+  const int step0 = first_step_of_cta(P, blockIdx.x);
+  const int total = min((int)blockIdx.x < P.n_first ? P.steps_first : P.steps_per_cta, P.step_base[P.n_weights] - step0);   // steps of this CTA
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // trace slots: 0-3 producer group 0 (total, tile wait, ring wait, expand+store), 4-8 issuer 0 (total,
@@ -879,13 +892,12 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
   const int n_pending = S.n_pending;
   if (n_pending == 0) return;
   asm volatile("griddepcontrol.wait;" ::: "memory");     // the counters were zeroed by the Z' kernel
-  const int L = P.steps_per_cta;
   for (int q = 0; q < n_pending; ++q) {
     const int wi = S.pending[q][0], rg = S.pending[q][1];
     const bsb_weight& w = P.w[wi];
     const int per_rg = w.blocks * NCH;
     const int gs = P.step_base[wi] + rg * per_rg, ge = gs + per_rg;   // steps of the row group
-    const int c_first = gs / L, c_last = (ge - 1) / L;
+    const int c_first = cta_of_step(P, gs), c_last = cta_of_step(P, ge - 1);
     __syncthreads();
     if (tid == 0) {
       const int old = atomicAdd(&P.counters[P.seg_base[wi] + rg], 1);
@@ -901,7 +913,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
         float sum = 0.f;
         for (int c = c_first; c <= c_last; ++c) {
           // the row group is CTA c's first row segment unless it starts after c's first step
-          const int slot = (gs <= c * L) ? 0 : 1;
+          const int slot = (gs <= first_step_of_cta(P, c)) ? 0 : 1;
           sum += __ldcg(P.partials + (((int64_t)c * 2 + slot) * R + r) * kRows + tid);
         }
         if (w.bias) sum += __half2float(reinterpret_cast<const __half*>(w.bias)[m]);
@@ -923,6 +935,11 @@ struct TcPlan {
 static int g_force_rt = 0;   // 0 = choose, 1 / 2 = forced (tuning)
 static int g_target_ctas = 0;   // 0 = two per multiprocessor, else this many (tuning)
 constexpr int kMinStepsPair = 4;
+constexpr int kMinStepsUneven = 4;      // steps per CTA from which the two waves get different shares
+// steps of a first-wave CTA per 100 of a second-wave one.  140 makes an isolated launch 5-8 % faster (the two CTAs of a
+// multiprocessor then finish together) but a decode step 6 % SLOWER: with kernels queued back to back the first 148 CTAs
+// are not placed one per multiprocessor, and two long CTAs can share one.  Equal shares (100) are the default.
+static int g_older_share_pct = 100;
 
 // R = input rows per pass (1 or 2).  The status word sits at offset 0 of the workspace whatever the plan.
 void make_tc_plan(const bsb_weight* ws, int n, int R, TcPlan& pl) {
@@ -947,7 +964,23 @@ void make_tc_plan(const bsb_weight* ws, int n, int R, TcPlan& pl) {
   int L = (int)ceil_div64(steps, target);
   if (L < 1) L = 1;
   P.steps_per_cta = L;
-  const int grid = (int)ceil_div64(steps, L);
+  P.n_first = 0;
+  P.steps_first = L;
+  int grid = (int)ceil_div64(steps, L);
+  const int sms = sm_count();
+  if (g_older_share_pct > 100 && target == 2 * sms && steps >= (int64_t)target * kMinStepsUneven) {
+    // two waves of one CTA per multiprocessor: the second wave's share is 1 / (1 + older share)
+    const int64_t den = (int64_t)sms * (100 + g_older_share_pct);
+    const int L2 = (int)((steps * 100 + den / 2) / den);   // nearest
+    const int L1 = (int)ceil_div64(steps - (int64_t)sms * L2, sms);
+    if (L2 >= 1 && L1 >= L2) {
+      P.n_first = sms;
+      P.steps_first = L1;
+      P.steps_per_cta = L2;
+      const int64_t rest = steps - (int64_t)sms * L1;
+      grid = sms + (rest > 0 ? (int)ceil_div64(rest, L2) : 0);
+    }
+  }
   int segs = 0, blks = 0;
   int64_t st = 0;
   for (int i = 0; i < n; ++i) {
@@ -1039,6 +1072,7 @@ void gemv_tc5_set_pdl(int on) { g_pdl_enabled = on; }
 void gemv_tc5_set_dbg(int m) {
   if (m >= 200 && m <= 202) g_force_rt = m - 200;   // row tiles per CTA: 200 = choose, 201 / 202 = forced
   else if (m >= 1000 && m < 2000) g_target_ctas = m - 1000;   // grid size wanted (1000 = default)
+  else if (m >= 2100 && m <= 2300) g_older_share_pct = m - 2000;   // first-wave share in percent (2100 = equal)
   else g_dbg = m;
 }
 void gemv_tc5_set_trace(unsigned long long* p) { g_trace = p; }
