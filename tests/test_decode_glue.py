@@ -125,6 +125,24 @@ def test_input_transforms_match_the_separate_kernels(dev, rows):
     assert torch.equal(y, y_ref)       # same roundings of the input, same kernel: identical
 
 
+def test_decode_harness_small_batch_under_a_cuda_graph(dev):
+    """Batch 3 (row pairs + a single row in every projection), captured as a CUDA graph and replayed: same tokens and
+    logits as the eager unfused path."""
+    from bitstack_b200 import decode
+    shape = decode.LlamaShape("tiny", 2, 512, 4, 2, 1024, vocab=1000)
+    counts = decode.seeded_block_counts(shape, seed=4, lo=2, hi=4)
+    prompt = torch.randint(0, 1000, (3, 7), device=dev, generator=torch.Generator(device=dev).manual_seed(2))
+    ref = decode.BitStackLlamaDecoder(shape, counts, dev, seed=6, max_len=128, batch=3, fused_glue=False)
+    ref.prefill(prompt)
+    want = [ref.decode_step().clone() for _ in range(5)]
+    m = decode.BitStackLlamaDecoder(shape, counts, dev, seed=6, max_len=128, batch=3, fused_glue=True)
+    m.prefill(prompt)
+    m.capture()
+    got = [m.step().clone() for _ in range(5)]
+    torch.cuda.synchronize()
+    assert all(torch.equal(a, b) for a, b in zip(want, got)), (want, got)
+
+
 def test_greedy_step_is_argmax_with_first_index_ties(dev):
     from bitstack_b200 import glue
     g = torch.Generator(device=dev).manual_seed(9)
