@@ -10,11 +10,16 @@ per-weight block counts in [2, 16] trimmed to 5.5 GB of packed blocks, 512-token
 prompt, then K greedy steps.
 
 The printed JSON line carries: `value` (device-timed, CUDA-graph replay, inputs
-resident), `e2e` (host-driven `generate()` with a host<->device token round trip per
-step), `roofline` (the tcgen05 decode kernel: algorithmic bytes / event-timed launch
-duration vs the measured HBM copy bandwidth), `cpu_baseline` (the CPU oracle's
-restatement of the reference's unfused forward on a bounded sample of the same
-layers), `clocks`, `gpu_launches`.
+resident: the MEDIAN over `--repeats` repeats of the K-step region, each started from
+the same KV-cache length, with `min` / `max` / `repeats` beside it), `e2e` (host-driven
+loop with a host<->device token round trip per step), `roofline` (the tcgen05 decode
+kernel: algorithmic bytes / event-timed launch duration vs the measured HBM copy
+bandwidth), `prefill` (the 512- and 2048-token prompts through the rebuild + tcgen05
+GEMM path: tokens, ms, TFLOP/s of the projections, fraction of the measured bf16 burst
+peak), `cpu_baseline` (the CPU oracle's restatement of the reference's unfused forward
+on a bounded sample of the same layers), `clocks` (sampled across all repeats),
+`gpu_launches`, and `llama3_70b_bs16` (the 70B-architecture, batch-16 workload on the
+same GPUs: tokens/s, ms per step, packed bytes per rank).
 
 `--impl reference` times only the CPU restatement of the reference path (the
 reference itself is Python that cannot travel to the GPU box) on bounded samples.
@@ -56,12 +61,15 @@ def parse():
     ap.add_argument("--prompt-len", type=int, default=0)
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="CPU time budget of the cpu_baseline leg")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--repeats", type=int, default=10, help="repeats of the timed K-step region (the median is reported)")
+    ap.add_argument("--no-70b", action="store_true", help="skip the 70B-architecture batch-16 leg")
+    ap.add_argument("--steps-70b", type=int, default=8)
     return ap.parse_args()
 
 
-def workload_spec(args):
+def workload_spec(args, workload=None):
     from bitstack_b200 import decode
-    if args.workload == "llama3-8b":
+    if (workload or args.workload) == "llama3-8b":
         shape = decode.LLAMA3_8B
         counts_args = dict(seed=1234, lo=2, hi=16, target_bytes=TARGET_PACKED_BYTES)
         batch, prompt = 1, 512
@@ -134,8 +142,8 @@ def cpu_sample(shape, counts, budget_s, threads=None):
     sample of this workload's projections; returns extrapolated tokens/s."""
     from oracle import bitstack_oracle as orc
     from bitstack_b200 import decode
-    if threads:
-        torch.set_num_threads(threads)
+    # under torch.distributed.run OMP_NUM_THREADS is 1: use every host core whatever launched this process
+    torch.set_num_threads(threads or os.cpu_count() or 1)
     shapes = shape.proj_shapes()
     total_bytes = sum(c * decode.block_bytes(*shapes[n.split(".", 2)[2]]) for n, c in counts.items())
     # smallest projections first so that a tiny budget still covers a few of them
@@ -213,6 +221,102 @@ def _progress(msg):
         print(f"[rank {os.environ.get('RANK', '0')}] {msg}", file=sys.stderr, flush=True)
 
 
+def _projection_flops(shape, rows, world):
+    """2 * out * in * rows over the BitStack projections of one rank (the dense contraction; the rank-16
+    reconstruction the batch path also performs is not counted)."""
+    return sum(2.0 * o * i * rows / world for (o, i) in shape.proj_shapes().values()) * shape.n_layers
+
+
+def timed_decode(model, steps, repeats, barrier, world, dev, warmup):
+    """`repeats` timed regions of `steps` decode steps, every one starting at the same KV-cache length; returns the
+    per-repeat milliseconds (max over ranks)."""
+    pos0, tok0 = model.pos.clone(), model.tokens.clone()
+    for _ in range(max(warmup, 3)):
+        model.step()
+    out = []
+    for _ in range(repeats):
+        model.pos.copy_(pos0)
+        model.tokens.copy_(tok0)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for _ in range(steps):
+            model.step()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            torch.distributed.all_reduce(ms, op=torch.distributed.ReduceOp.MAX)
+        out.append(float(ms.item()))
+    model.pos.copy_(pos0)
+    model.tokens.copy_(tok0)
+    return out
+
+
+def timed_prefill(model, shape, batch, tokens, world, dev, peaks, barrier):
+    """One prompt of `tokens` tokens per sequence through the batch path (rebuild + tcgen05 GEMM), event-timed."""
+    gen = torch.Generator().manual_seed(5)
+    prompt = torch.randint(0, shape.vocab, (batch, tokens), generator=gen).to(dev)
+    model.prefill(prompt)                       # warm-up (scratch growth, first-use set-up)
+    best = None
+    for _ in range(3):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        model.prefill(prompt)
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            torch.distributed.all_reduce(ms, op=torch.distributed.ReduceOp.MAX)
+        best = float(ms.item()) if best is None else min(best, float(ms.item()))
+    fl = _projection_flops(shape, batch * tokens, world)
+    tf = fl / (best / 1e3) / 1e12
+    burst = peaks.get("bf16_tflops")
+    return {"tokens": batch * tokens, "ms": best, "projection_tflops_per_gpu": tf,
+            "frac_of_burst": (tf / burst) if burst else None,
+            "note": "whole prefill (projections + attention + glue), flops = 2*out*in*rows of the BitStack projections only"}
+
+
+def run_70b_leg(args, dev, rank, world, local, group, barrier):
+    """Config 5 on the same GPUs: 70B architecture, batch 16, 256-token prompts, seeded 4-12 blocks per weight."""
+    from bitstack_b200 import decode
+    shape, counts, batch, prompt = workload_spec(args, "llama3-70b")
+    steps = max(1, min(args.steps_70b, args.steps))
+    max_len = (prompt + steps * 3 + 8 + 127) // 128 * 128
+    t_build = time.perf_counter()
+    model = decode.BitStackLlamaDecoder(shape, counts, dev, seed=9, max_len=max_len, batch=batch, rank=rank,
+                                        world_size=world, group=group)
+    gen = torch.Generator().manual_seed(13)
+    prompt_ids = torch.randint(0, shape.vocab, (batch, prompt), generator=gen).to(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    model.prefill(prompt_ids)
+    barrier()
+    e0.record()
+    model.prefill(prompt_ids)
+    e1.record()
+    barrier()
+    prefill_ms = e0.elapsed_time(e1)
+    model.decode_step()
+    torch.cuda.synchronize()
+    if not args.no_graph:
+        model.capture()
+    ms = timed_decode(model, steps, 3, barrier, world, dev, 3)
+    med = float(np.median(ms))
+    from bitstack_b200 import _lib
+    _lib.check_device_status()
+    out = {"tokens_per_s": steps * batch / (med / 1e3), "ms_per_step": med / steps, "steps": steps, "repeats": 3,
+           "min_tokens_per_s": steps * batch / (max(ms) / 1e3), "max_tokens_per_s": steps * batch / (min(ms) / 1e3),
+           "batch": batch, "prompt_len": prompt, "packed_block_bytes": decode.packed_bytes(shape, counts),
+           "packed_block_bytes_per_rank": model.weight_bytes(), "n_gpus": world,
+           "prefill_ms": prefill_ms, "prefill_projection_tflops_per_gpu": _projection_flops(shape, batch * prompt, world) / (prefill_ms / 1e3) / 1e12,
+           "build_s": time.perf_counter() - t_build}
+    model._graph = None
+    del model
+    torch.cuda.empty_cache()
+    return out
+
+
 def run_ours(args):
     from bitstack_b200 import _lib, decode
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -231,9 +335,14 @@ def run_ours(args):
     _progress("process group ready")
     lib = _lib.load()
     if os.environ.get("BSB_PDL") == "0":
-        lib.bsb_debug_set_mode(100)
+        lib.bsb_set_dependent_launch(0)
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
     shape, counts, batch, prompt = workload_spec(args)
-    max_len = prompt + args.steps + args.warmup + 16
+    max_len = max(prompt, 2048 if not args.layers else prompt) + args.steps + args.warmup + 16
     max_len = (max_len + 127) // 128 * 128
     model = decode.BitStackLlamaDecoder(shape, counts, dev, seed=7, max_len=max_len, batch=batch,
                                         rank=rank, world_size=world, group=group)
@@ -245,8 +354,12 @@ def run_ours(args):
             torch.distributed.barrier()
         torch.cuda.synchronize()
 
-    # ---- device-timed value ------------------------------------------------------------
+    # ---- prefill through the batch path (tensor-pipe figure) -------------------------------
     _progress("model built")
+    prefill = {}
+    for toks in sorted({prompt, 2048 if not args.layers else prompt}):
+        prefill[f"{toks}_tokens"] = timed_prefill(model, shape, batch, toks, world, dev, peaks, barrier)
+    # ---- device-timed value ------------------------------------------------------------
     model.prefill(prompt_host.to(dev))
     torch.cuda.synchronize()
     _progress("prefill done")
@@ -258,24 +371,12 @@ def run_ours(args):
     if not args.no_graph:
         model.capture()
         _progress("graph captured")
-    for _ in range(max(args.warmup, 3)):
-        model.step()
-    barrier()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    for _ in range(args.steps):
-        model.step()
-    e1.record()
-    barrier()
-    ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
-    if world > 1:
-        torch.distributed.all_reduce(ms, op=torch.distributed.ReduceOp.MAX)
-    ms = float(ms.item())
+    ms_all = timed_decode(model, args.steps, max(1, args.repeats), barrier, world, dev, args.warmup)
     clocks = sampler.stop() if rank == 0 else None
+    ms = float(np.median(ms_all))
     value = args.steps * batch / (ms / 1000.0)
     _progress("timed region done")
 
@@ -295,15 +396,11 @@ def run_ours(args):
     if world > 1:
         torch.distributed.all_reduce(e2e_s, op=torch.distributed.ReduceOp.MAX)
     e2e = args.steps * batch / float(e2e_s.item())
+    _lib.check_device_status()
     _progress("e2e done")
 
     # ---- roofline of the dominant kernel (eager step, events around each launch) -----------
     roof = None
-    peaks = {}
-    try:
-        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-    except Exception:
-        pass
     peak, which = (peaks["hbm_gbs"], "measured") if "hbm_gbs" in peaks else (6650.0, "fallback")
     # every rank runs the profiled eager step (it contains the all-reduces); rank 0 reports its own timings
     model._graph, g = None, model._graph
@@ -343,10 +440,24 @@ def run_ours(args):
                     "traffic": float(np.mean(launch_bytes)) * NCU_TRAFFIC_PER_ALGORITHMIC_BYTE,
                     "traffic_source": "ncu dram read+write of one 14336x4096 16-block launch (132.6 MB for 126.9 MB algorithmic), scaled by algorithmic bytes",
                     "launches": int(n.value), "avg_launch_us": float(durs.mean() * 1000.0),
-                    "algorithmic_bytes_per_launch": float(np.mean(launch_bytes))}
+                    "algorithmic_bytes_per_launch": float(np.mean(launch_bytes)),
+                    "step_level": {"achieved": decode.packed_bytes(shape, counts) / world / (ms / args.steps / 1e3) / 1e9,
+                                   "note": "packed block bytes of one rank over the whole graph-replayed step (glue, attention and head included)"}}
         else:
             roof = {"bound": "hbm", "kernel": "gemv_tc5_kernel", "achieved": None, "peak": peak, "unit": "GB/s", "frac": None,
                     "traffic": None, "note": f"{n.value} decode-kernel launches profiled in one step (batch {batch}: rows > 6 use the rebuild+GEMM path)"}
+
+    # ---- the 70B-architecture batch-16 workload on the same GPUs ----------------------------
+    model._graph = None
+    del model
+    torch.cuda.empty_cache()
+    big = None
+    if not args.no_70b and not args.layers and args.workload == "llama3-8b":
+        try:
+            big = run_70b_leg(args, dev, rank, world, local, group, barrier)
+        except Exception as e:   # the headline must survive a failure of the extra leg
+            big = {"error": f"{type(e).__name__}: {e}"[:300]}
+        _progress("70B leg done")
 
     # ---- CPU restatement on a bounded sample ---------------------------------------------
     cpu = None
@@ -354,19 +465,22 @@ def run_ours(args):
         cpu = cpu_sample(shape, counts, args.cpu_seconds)
         cpu["value"] *= batch
     if rank == 0:
+        vals = [args.steps * batch / (m / 1000.0) for m in ms_all]
+        sm = clocks.get("sm_mhz") if clocks else None
         line = {"metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
                 "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": "e4m3 tensor-core operands, f32 accumulate, fp16 storage/outputs",
                 "data": "synthetic", "config": config_dict(args, shape, counts, batch, prompt),
+                "repeats": len(vals), "min": min(vals), "max": max(vals),
+                "ms_per_step_x_sm_mhz": (ms / args.steps * sm) if sm else None,
                 "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": 8 * batch, "d2h_bytes_per_step": 8 * batch},
-                "gpu_launches": int(launches_per_step * args.steps), "roofline": roof, "cpu_baseline": cpu, "clocks": clocks,
-                "graph": not args.no_graph}
+                "gpu_launches": int(launches_per_step * args.steps), "roofline": roof, "prefill": prefill,
+                "llama3_70b_bs16": big, "cpu_baseline": cpu, "clocks": clocks, "graph": not args.no_graph}
         print(json.dumps(line), flush=True)
     if world > 1:
         # Tearing NCCL down while captured graphs still reference its kernels was seen to block
-        # forever at exit: drop the graph, drain the device, agree that everyone is done, then
+        # forever at exit: drop the graphs, drain the device, agree that everyone is done, then
         # leave without running the communicator destructors.
-        model._graph = None
         torch.cuda.synchronize()
         torch.distributed.barrier()
         sys.stdout.flush()

@@ -6,8 +6,8 @@ Public surface (mirrors the reference's operator API):
     forward_grouped           several projections of one input in one launch sequence
     loader                    budget selection (compression_config.json) and partial safetensors loading
 """
-from .linear import BitStackLinear, forward_grouped, forward_grouped_transformed, get_workspace, transform_supported
+from .linear import BitStackLinear, forward_grouped, get_workspace
 from .pack import pack_sign, unpack_sign
 from . import loader
 
-__all__ = ["BitStackLinear", "forward_grouped", "forward_grouped_transformed", "transform_supported", "get_workspace", "pack_sign", "unpack_sign", "loader"]
+__all__ = ["BitStackLinear", "forward_grouped", "get_workspace", "pack_sign", "unpack_sign", "loader"]

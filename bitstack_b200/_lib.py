@@ -11,7 +11,7 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("BITSTACK_B200_LIB") or os.path.join(_HERE, "libbitstack_b200.so")
 
-ALGO_AUTO, ALGO_GENERAL, ALGO_GEMV_MMA, ALGO_REBUILD_GEMM, ALGO_GEMV_TC5 = 0, 1, 2, 3, 4
+ALGO_AUTO, ALGO_GENERAL, ALGO_REBUILD_GEMM, ALGO_GEMV_TC5 = 0, 1, 3, 4
 
 
 class BsbWeight(C.Structure):
@@ -22,18 +22,6 @@ class BsbWeight(C.Structure):
         ("q_block_stride", C.c_int64), ("u_block_stride", C.c_int64), ("vt_block_stride", C.c_int64),
         ("out_features", C.c_int32), ("in_features", C.c_int32), ("k", C.c_int32), ("blocks", C.c_int32),
     ]
-
-
-class BsbInputTransform(C.Structure):
-    """Mirror of `struct bsb_input_transform`."""
-    _fields_ = [
-        ("mode", C.c_int32), ("eps", C.c_float),
-        ("x2", C.c_void_p), ("norm_weight", C.c_void_p), ("h_out", C.c_void_p),
-        ("x2_stride", C.c_int64), ("h_out_stride", C.c_int64),
-    ]
-
-
-INPUT_PLAIN, INPUT_ADD_RMSNORM, INPUT_SILU_MUL = 0, 1, 2
 
 
 class BitStackLibraryError(RuntimeError):
@@ -55,8 +43,8 @@ SIGNATURES = {
     "bsb_vt_absmax": (C.c_int, [_WP, _P, _P]),
     "bsb_linear_workspace_bytes": (_I64, [_WP, _I64, C.c_int]),
     "bsb_linear_forward": (C.c_int, [_WP, _P, _I64, _I64, _P, _I64, _P, _I64, C.c_int, _P]),
+    "bsb_linear_forward_partial": (C.c_int, [_WP, _P, _I64, _I64, _P, _I64, _P, _I64, C.c_int, _P]),
     "bsb_linear_forward_grouped": (C.c_int, [_WP, _I32, _P, _I64, _I64, C.POINTER(_P), C.POINTER(_I64), _P, _I64, C.c_int, _P]),
-    "bsb_linear_forward_grouped_tf": (C.c_int, [_WP, _I32, _P, _I64, _I64, C.POINTER(BsbInputTransform), C.POINTER(_P), C.POINTER(_I64), _P, _I64, _P]),
     "bsb_linear_grouped_workspace_bytes": (_I64, [_WP, _I32, _I64, C.c_int]),
     "bsb_add_rmsnorm": (C.c_int, [_P, _P, _P, C.c_float, _P, _I64, _I32, _P]),
     "bsb_rope_cache": (C.c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _I32, _I32, _I32, _I32, _I32, _P]),
@@ -66,11 +54,10 @@ SIGNATURES = {
     "bsb_silu_mul": (C.c_int, [_P, _P, _P, _I64, _P]),
     "bsb_noalloc_scratch_bytes": (_I64, []),
     "bsb_linear_forward_noalloc": (C.c_int, [_WP, _P, _I64, _I64, _P, _I64, _P]),
-    "bsb_debug_gemv_status": (C.c_int, [_WP, _I32, _P, C.POINTER(C.c_int32)]),
-    "bsb_debug_gemm_status": (C.c_int, [_WP, _P, C.POINTER(C.c_int32)]),
+    "bsb_read_status": (C.c_int, [C.POINTER(C.c_int32), _I32]),
+    "bsb_set_wait_limit_ms": (C.c_int, [_I32]),
+    "bsb_set_dependent_launch": (C.c_int, [_I32]),
     "bsb_debug_launch_count": (_I64, []),
-    "bsb_debug_set_trace": (C.c_int, [_P]),
-    "bsb_debug_set_mode": (C.c_int, [_I32]),
     "bsb_debug_profile_start": (C.c_int, [_I32]),
     "bsb_debug_profile_stop": (C.c_int, [C.POINTER(C.c_float), _I32, C.POINTER(_I32)]),
     "bsb_linear_forward_host": (C.c_int, [_WP, _P, _I64, _P, _P, _P, _P, _I64, C.c_int, _P]),
@@ -95,9 +82,22 @@ def load():
     return lib
 
 
+class BitStackDeviceTimeout(BitStackLibraryError):
+    """A time-bounded wait inside a kernel gave up; the outputs of that call are NaN."""
+
+
 def check(rc: int, what: str):
     if rc != 0:
         msg = load().bsb_last_error().decode(errors="replace")
         if rc == -1:
             raise ValueError(f"{what}: {msg}")
+        if rc == -5:
+            raise BitStackDeviceTimeout(f"{what}: {msg}")
         raise BitStackLibraryError(f"{what} failed ({rc}): {msg}")
+
+
+def check_device_status(clear: bool = True) -> None:
+    """Synchronises the current device and raises BitStackDeviceTimeout if any kernel of the library gave up a wait
+    since the status was last cleared.  Call it wherever the host waits for results anyway."""
+    code = C.c_int32(0)
+    check(load().bsb_read_status(C.byref(code), 1 if clear else 0), "device status")

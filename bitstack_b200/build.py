@@ -15,7 +15,10 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libbitstack_b200.so")
-SOURCES = ["capi.cu", "pack_kernels.cu", "general_kernels.cu", "rebuild_gemm.cu", "gemv_mma.cu", "gemv_tc5.cu", "gemm_tc5.cu", "decode_glue.cu"]
+# side build with -DBSB_TUNING: the same library plus timing-experiment modes and a fault-injection mode of the decode
+# kernel (bsb_tuning_set_mode / bsb_tuning_set_trace); the tests of the give-up path load it, the product never does
+TUNING_LIB = os.path.join(HERE, "libbitstack_b200_tuning.so")
+SOURCES = ["capi.cu", "pack_kernels.cu", "general_kernels.cu", "rebuild_gemm.cu", "gemv_tc5.cu", "gemm_tc5.cu", "decode_glue.cu"]
 HEADERS = [os.path.join(CSRC, "common.cuh"), os.path.join(os.path.dirname(HERE), "include", "bitstack_b200.h")]
 FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",
          "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
@@ -63,5 +66,11 @@ def build(force: bool = False, verbose: bool = False, extra_flags=None, lib_path
     return lib_path
 
 
+def build_tuning(force: bool = False, verbose: bool = False) -> str:
+    return build(force=force, verbose=verbose, extra_flags=["-DBSB_TUNING"], lib_path=TUNING_LIB, objdir_name="build_tuning")
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    if "--tuning" in sys.argv:
+        print(build_tuning(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

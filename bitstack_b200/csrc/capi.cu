@@ -21,7 +21,7 @@ static unsigned long long g_launches = 0;
 void count_launch() { __atomic_fetch_add(&g_launches, 1ull, __ATOMIC_RELAXED); }
 
 // profiling hook: a bounded list of event pairs recorded around the tcgen05 decode kernel
-int g_pdl_enabled = 1;   // programmatic dependent launch between the library's kernels (1-1.5 us less per launch in graph replay)
+int g_pdl_enabled = 1;   // programmatic dependent launch between the library's kernels (bsb_set_dependent_launch)
 static const int kMaxProfile = 4096;
 static cudaEvent_t g_prof_ev[2 * kMaxProfile];
 static int g_prof_cap = 0, g_prof_n = 0;
@@ -50,7 +50,31 @@ int sm_count() {
   return cached[dev];
 }
 
-static int check_weight(const bsb_weight* w) {
+// ---- sticky device status -----------------------------------------------------------------------
+// One word per device, in the library image (zero when the library is loaded).  Kernels store into it only with
+// atomicCAS(word, 0, code), so the first event stays until bsb_read_status() fetches and clears it.
+static __device__ int g_status_word;
+
+int* device_status_word() {
+  static int* cached[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    set_error("no usable current device for the status word");
+    return nullptr;
+  }
+  if (cached[dev] == nullptr) {
+    void* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_status_word);
+    if (e != cudaSuccess) {
+      set_error("cudaGetSymbolAddress(status word) failed: %s", cudaGetErrorString(e));
+      return nullptr;
+    }
+    cached[dev] = (int*)p;
+  }
+  return cached[dev];
+}
+
+int check_weight(const bsb_weight* w) {
   BSB_CHECK_ARG(w != nullptr, "weight is NULL");
   BSB_CHECK_ARG(w->out_features >= 0 && w->in_features >= 0 && w->k >= 1 && w->blocks >= 0,
                 "bad weight dims out=%d in=%d k=%d blocks=%d", w->out_features, w->in_features, w->k, w->blocks);
@@ -71,43 +95,43 @@ static const int kDecodeRowsMax = 6;
 static int pick_algo(const bsb_weight& w, int64_t rows, int algo) {
   if (algo != BSB_ALGO_AUTO) return algo;
   if (rows <= kDecodeRowsMax && gemv_tc5_supported(w)) return BSB_ALGO_GEMV_TC5;   // two rows per pass: cheaper than rebuilding W up to here
-  if (rows <= 4 && gemv_mma_supported(w)) return BSB_ALGO_GEMV_MMA;
   if (rebuild_supported(w) && gemm_supported(rows, w.out_features, w.in_features)) return BSB_ALGO_REBUILD_GEMM;
   return BSB_ALGO_GENERAL;
 }
 
 static int64_t workspace_for(const bsb_weight& w, int64_t rows, int algo) {
   switch (pick_algo(w, rows, algo)) {
-    case BSB_ALGO_GEMV_MMA:
-      return gemv_mma_workspace_bytes(&w, 1);
     case BSB_ALGO_GEMV_TC5:
       return gemv_tc5_workspace_bytes(&w, 1, rows >= 2 ? 2 : 1);
     case BSB_ALGO_REBUILD_GEMM:
-      return align_up64((int64_t)w.out_features * w.in_features * 2, 256) + 256;   // fp16 W, then the GEMM's status word
+      return align_up64((int64_t)w.out_features * w.in_features * 2, 256);   // the rebuilt fp16 W
     default:
       return 0;
   }
 }
 
 // fp16 zero / bias fill for weights with no active block
-__global__ void fill_bias_kernel(__half* y, int64_t rows, int64_t y_stride, int M, const __half* bias) {
+__global__ void fill_bias_kernel(__half* y, float* y32, int64_t rows, int64_t y_stride, int M, const __half* bias) {
   const int64_t total = rows * M;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t r = i / M;
     const int m = (int)(i % M);
-    y[r * y_stride + m] = bias ? bias[m] : __float2half(0.f);
+    const __half v = bias ? bias[m] : __float2half(0.f);
+    if (y32) y32[r * y_stride + m] = __half2float(v);
+    else y[r * y_stride + m] = v;
   }
 }
 
-static int forward_one(const bsb_weight& w, const __half* x, int64_t rows, int64_t x_stride, __half* y,
+// exactly one of y (fp16 output) and y32 (fp32 partial sums, the tensor-parallel variant) is non-null
+static int forward_one(const bsb_weight& w, const __half* x, int64_t rows, int64_t x_stride, __half* y, float* y32,
                        int64_t y_stride, void* workspace, int64_t workspace_bytes, int algo, cudaStream_t s) {
   if (rows == 0 || w.out_features == 0) return BSB_OK;
-  BSB_CHECK_ARG(x != nullptr && y != nullptr, "x or y is NULL");
+  BSB_CHECK_ARG(x != nullptr && (y != nullptr) != (y32 != nullptr), "x or y is NULL");
   BSB_CHECK_ARG(x_stride >= w.in_features && y_stride >= w.out_features, "row stride smaller than the row");
   if (w.blocks == 0 || w.in_features == 0) {
     const int64_t total = rows * w.out_features;
     fill_bias_kernel<<<(unsigned)min((int64_t)1024, ceil_div64(total, 256)), 256, 0, s>>>(
-        y, rows, y_stride, w.out_features, reinterpret_cast<const __half*>(w.bias));
+        y, y32, rows, y_stride, w.out_features, reinterpret_cast<const __half*>(w.bias));
     return check_launch("fill_bias_kernel");
   }
   const int a = pick_algo(w, rows, algo);
@@ -118,24 +142,15 @@ static int forward_one(const bsb_weight& w, const __half* x, int64_t rows, int64
   }
   switch (a) {
     case BSB_ALGO_GENERAL:
-      return launch_general_forward(w, x, rows, x_stride, y, y_stride, s);
-    case BSB_ALGO_GEMV_MMA: {
-      BSB_CHECK_ARG(gemv_mma_supported(w), "GEMV_MMA: unsupported shape/alignment (out=%d in=%d k=%d)",
-                    w.out_features, w.in_features, w.k);
-      for (int64_t r = 0; r < rows; ++r) {
-        __half* yr = y + r * y_stride;
-        if (int rc = launch_gemv_mma(&w, 1, x + r * x_stride, &yr, workspace, workspace_bytes, s)) return rc;
-      }
-      return BSB_OK;
-    }
+      return launch_general_forward(w, x, rows, x_stride, y, y32, y_stride, s);
     case BSB_ALGO_GEMV_TC5: {
       BSB_CHECK_ARG(gemv_tc5_supported(w), "GEMV_TC5: unsupported shape/alignment (out=%d in=%d k=%d)",
                     w.out_features, w.in_features, w.k);
       // rows go through the kernel two at a time (one MMA serves both), a last odd row alone
       for (int64_t r = 0; r < rows;) {
         const int nr = (rows - r >= 2 && x_stride % 8 == 0) ? 2 : 1;
-        __half* yr = y + r * y_stride;
-        if (int rc = launch_gemv_tc5(&w, 1, x + r * x_stride, x_stride, nr, &yr, &y_stride, workspace, workspace_bytes, s)) return rc;
+        __half* yr = y32 ? reinterpret_cast<__half*>(y32 + r * y_stride) : y + r * y_stride;
+        if (int rc = launch_gemv_tc5(&w, 1, x + r * x_stride, x_stride, nr, &yr, &y_stride, workspace, workspace_bytes, s, y32 != nullptr)) return rc;
         r += nr;
       }
       return BSB_OK;
@@ -147,14 +162,11 @@ static int forward_one(const bsb_weight& w, const __half* x, int64_t rows, int64
       BSB_CHECK_ARG((uintptr_t)workspace % 16 == 0, "workspace must be 16-byte aligned");
       __half* wbuf = (__half*)workspace;
       if (int rc = launch_rebuild_weight(w, wbuf, s)) return rc;
-      const int64_t w_bytes = align_up64((int64_t)w.out_features * w.in_features * 2, 256);
-      if (gemm_tc5_supported(rows, w.out_features, w.in_features) && (uintptr_t)y % 16 == 0 && y_stride % 8 == 0 &&
-          (uintptr_t)x % 16 == 0 && x_stride % 8 == 0 && workspace_bytes >= w_bytes + 256) {
-        int* status = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(workspace) + w_bytes);
-        BSB_CUDA(cudaMemsetAsync(status, 0, 4, s));
+      if (gemm_tc5_supported(rows, w.out_features, w.in_features) && ((uintptr_t)y | (uintptr_t)y32) % 16 == 0 && y_stride % 8 == 0 &&
+          (uintptr_t)x % 16 == 0 && x_stride % 8 == 0)
         return launch_gemm_tc5(x, rows, x_stride, wbuf, w.out_features, w.in_features,
-                               reinterpret_cast<const __half*>(w.bias), y, y_stride, status, s);
-      }
+                               reinterpret_cast<const __half*>(w.bias), y, y32, y_stride, s);
+      BSB_CHECK_ARG(y32 == nullptr, "partial-sum output needs 16-byte aligned rows (x, y and their strides)");
       // outputs that are not 16-byte aligned: the warp-level (mma.sync) kernel
       return launch_gemm_xwt(x, rows, x_stride, wbuf, w.out_features, w.in_features,
                              reinterpret_cast<const __half*>(w.bias), y, y_stride, s);
@@ -222,8 +234,16 @@ int bsb_linear_forward(const bsb_weight* w, const uint16_t* x, int64_t rows, int
                        int64_t y_stride, void* workspace, int64_t workspace_bytes, int algo, void* stream) {
   if (int rc = check_weight(w)) return rc;
   BSB_CHECK_ARG(rows >= 0, "negative row count");
-  return forward_one(*w, (const __half*)x, rows, x_stride, (__half*)y, y_stride, workspace, workspace_bytes,
+  return forward_one(*w, (const __half*)x, rows, x_stride, (__half*)y, nullptr, y_stride, workspace, workspace_bytes,
                      algo, (cudaStream_t)stream);
+}
+
+int bsb_linear_forward_partial(const bsb_weight* w, const uint16_t* x, int64_t rows, int64_t x_stride, float* y,
+                               int64_t y_stride, void* workspace, int64_t workspace_bytes, int algo, void* stream) {
+  if (int rc = check_weight(w)) return rc;
+  BSB_CHECK_ARG(rows >= 0, "negative row count");
+  return forward_one(*w, (const __half*)x, rows, x_stride, nullptr, y, y_stride, workspace, workspace_bytes, algo,
+                     (cudaStream_t)stream);
 }
 
 int bsb_linear_forward_grouped(const bsb_weight* ws, int32_t n_weights, const uint16_t* x, int64_t rows,
@@ -237,66 +257,28 @@ int bsb_linear_forward_grouped(const bsb_weight* ws, int32_t n_weights, const ui
   }
   cudaStream_t s = (cudaStream_t)stream;
   // one fused launch sequence when every member qualifies for the decode kernel
-  const bool use_tc5 = (algo == BSB_ALGO_AUTO || algo == BSB_ALGO_GEMV_TC5);
-  bool fused = (use_tc5 || algo == BSB_ALGO_GEMV_MMA) && rows >= 1 && rows <= (use_tc5 ? kDecodeRowsMax : 4) && n_weights <= 4;
-  for (int i = 0; i < n_weights && fused; ++i)
-    fused = ws[i].blocks > 0 && ws[i].out_features > 0 &&
-            (use_tc5 ? gemv_tc5_supported(ws[i]) : gemv_mma_supported(ws[i]));
+  bool fused = (algo == BSB_ALGO_AUTO || algo == BSB_ALGO_GEMV_TC5) && rows >= 1 && rows <= kDecodeRowsMax && n_weights <= 4;
+  for (int i = 0; i < n_weights && fused; ++i) fused = ws[i].blocks > 0 && ws[i].out_features > 0 && gemv_tc5_supported(ws[i]);
   if (fused) {
-    const int64_t need = use_tc5 ? gemv_tc5_workspace_bytes(ws, n_weights, rows >= 2 ? 2 : 1) : gemv_mma_workspace_bytes(ws, n_weights);
+    const int64_t need = gemv_tc5_workspace_bytes(ws, n_weights, rows >= 2 ? 2 : 1);
     if (workspace == nullptr || workspace_bytes < need) {
       set_error("workspace of %lld bytes needed, %lld given", (long long)need, (long long)workspace_bytes);
       return BSB_EWORKSPACE;
     }
     for (int64_t r = 0; r < rows;) {
-      const int nr = (use_tc5 && rows - r >= 2 && x_stride % 8 == 0) ? 2 : 1;   // two rows per pass of the tcgen05 kernel
+      const int nr = (rows - r >= 2 && x_stride % 8 == 0) ? 2 : 1;   // two rows per pass of the decode kernel
       __half* yr[4];
       for (int i = 0; i < n_weights; ++i) yr[i] = (__half*)ys[i] + r * y_strides[i];
-      const int rc = use_tc5
-          ? launch_gemv_tc5(ws, n_weights, (const __half*)x + r * x_stride, x_stride, nr, yr, y_strides, workspace, workspace_bytes, s)
-          : launch_gemv_mma(ws, n_weights, (const __half*)x + r * x_stride, yr, workspace, workspace_bytes, s);
-      if (rc) return rc;
+      if (int rc = launch_gemv_tc5(ws, n_weights, (const __half*)x + r * x_stride, x_stride, nr, yr, y_strides, workspace, workspace_bytes, s))
+        return rc;
       r += nr;
     }
     return BSB_OK;
   }
   for (int i = 0; i < n_weights; ++i) {
-    if (int rc = forward_one(ws[i], (const __half*)x, rows, x_stride, (__half*)ys[i], y_strides[i], workspace,
+    if (int rc = forward_one(ws[i], (const __half*)x, rows, x_stride, (__half*)ys[i], nullptr, y_strides[i], workspace,
                              workspace_bytes, algo, s))
       return rc;
-  }
-  return BSB_OK;
-}
-
-int bsb_linear_forward_grouped_tf(const bsb_weight* ws, int32_t n_weights, const uint16_t* x, int64_t rows,
-                                  int64_t x_stride, const bsb_input_transform* tf, uint16_t* const* ys,
-                                  const int64_t* y_strides, void* workspace, int64_t workspace_bytes, void* stream) {
-  BSB_CHECK_ARG(n_weights >= 1 && n_weights <= 4 && ws && ys && y_strides && x && tf, "bad group arguments");
-  BSB_CHECK_ARG(rows >= 1 && rows <= kDecodeRowsMax, "input transforms run on the decode path: 1..%d rows (got %lld)",
-                kDecodeRowsMax, (long long)rows);
-  for (int i = 0; i < n_weights; ++i) {
-    if (int rc = check_weight(&ws[i])) return rc;
-    BSB_CHECK_ARG(ws[i].in_features == ws[0].in_features, "grouped weights must share in_features");
-    BSB_CHECK_ARG(ws[i].blocks > 0 && ws[i].out_features > 0 && gemv_tc5_supported(ws[i]),
-                  "input transforms need the decode kernel: weight %d has no active block or an unsupported shape/alignment", i);
-  }
-  BSB_CHECK_ARG((uintptr_t)x % 16 == 0 && (rows == 1 || x_stride % 8 == 0), "x rows must be 16-byte aligned");
-  const int64_t need = gemv_tc5_workspace_bytes(ws, n_weights, rows >= 2 ? 2 : 1);
-  if (workspace == nullptr || workspace_bytes < need) {
-    set_error("workspace of %lld bytes needed, %lld given", (long long)need, (long long)workspace_bytes);
-    return BSB_EWORKSPACE;
-  }
-  for (int64_t r = 0; r < rows;) {
-    const int nr = (rows - r >= 2) ? 2 : 1;
-    __half* yr[4];
-    for (int i = 0; i < n_weights; ++i) yr[i] = (__half*)ys[i] + r * y_strides[i];
-    bsb_input_transform t = *tf;     // this pass's rows of the transform operands
-    if (t.x2) t.x2 += r * t.x2_stride;
-    if (t.h_out) t.h_out += r * t.h_out_stride;
-    if (int rc = launch_gemv_tc5(ws, n_weights, (const __half*)x + r * x_stride, x_stride, nr, yr, y_strides, workspace,
-                                 workspace_bytes, (cudaStream_t)stream, &t))
-      return rc;
-    r += nr;
   }
   return BSB_OK;
 }
@@ -304,46 +286,52 @@ int bsb_linear_forward_grouped_tf(const bsb_weight* ws, int32_t n_weights, const
 int64_t bsb_linear_grouped_workspace_bytes(const bsb_weight* ws, int32_t n_weights, int64_t rows, int algo) {
   if (!ws || n_weights < 1 || rows < 0) return -1;
   int64_t need = 0;
-  const bool use_tc5 = (algo == BSB_ALGO_AUTO || algo == BSB_ALGO_GEMV_TC5);
-  bool fused = (use_tc5 || algo == BSB_ALGO_GEMV_MMA) && rows >= 1 && rows <= (use_tc5 ? kDecodeRowsMax : 4) && n_weights <= 4;
+  bool fused = (algo == BSB_ALGO_AUTO || algo == BSB_ALGO_GEMV_TC5) && rows >= 1 && rows <= kDecodeRowsMax && n_weights <= 4;
   for (int i = 0; i < n_weights; ++i) {
     if (check_weight(&ws[i]) != BSB_OK) return -1;
-    fused = fused && ws[i].blocks > 0 && ws[i].out_features > 0 &&
-            (use_tc5 ? gemv_tc5_supported(ws[i]) : gemv_mma_supported(ws[i]));
+    fused = fused && ws[i].blocks > 0 && ws[i].out_features > 0 && gemv_tc5_supported(ws[i]);
     if (ws[i].blocks > 0 && rows > 0) need = max(need, workspace_for(ws[i], rows, algo));
   }
-  if (fused) need = max(need, use_tc5 ? gemv_tc5_workspace_bytes(ws, n_weights, rows >= 2 ? 2 : 1) : gemv_mma_workspace_bytes(ws, n_weights));
+  if (fused) need = max(need, gemv_tc5_workspace_bytes(ws, n_weights, rows >= 2 ? 2 : 1));
   return need;
 }
 
-int bsb_debug_gemv_status(const bsb_weight* ws, int32_t n_weights, const void* workspace, int32_t* status_out) {
-  BSB_CHECK_ARG(ws && workspace && status_out, "NULL argument");
-  const int64_t off = gemv_tc5_status_offset(ws, n_weights);
-  BSB_CHECK_ARG(off >= 0, "bad group size");
-  BSB_CUDA(cudaMemcpy(status_out, (const uint8_t*)workspace + off, 4, cudaMemcpyDeviceToHost));
+int bsb_read_status(int32_t* code_out, int32_t clear) {
+  BSB_CHECK_ARG(code_out != nullptr, "NULL argument");
+  int* word = device_status_word();
+  if (word == nullptr) return BSB_ECUDA;
+  BSB_CUDA(cudaDeviceSynchronize());   // every stream of the device: the word is shared by all of them
+  BSB_CUDA(cudaMemcpy(code_out, word, 4, cudaMemcpyDeviceToHost));
+  if (clear && *code_out != 0) BSB_CUDA(cudaMemset(word, 0, 4));
+  if (*code_out != 0) {
+    set_error("a time-bounded wait gave up on the device (code %d): the outputs of that call are NaN", *code_out);
+    return BSB_ETIMEOUT;
+  }
   return BSB_OK;
 }
 
-int bsb_debug_gemm_status(const bsb_weight* w, const void* workspace, int32_t* status_out) {
-  BSB_CHECK_ARG(w && workspace && status_out, "NULL argument");
-  const int64_t off = align_up64((int64_t)w->out_features * w->in_features * 2, 256);
-  BSB_CUDA(cudaMemcpy(status_out, (const uint8_t*)workspace + off, 4, cudaMemcpyDeviceToHost));
+int bsb_set_wait_limit_ms(int32_t ms) {
+  BSB_CHECK_ARG(ms >= 1 && ms <= 60000, "wait limit must be 1..60000 ms");
+  gemv_tc5_set_wait_limit_ns((unsigned long long)ms * 1000000ull);
   return BSB_OK;
 }
 
-int bsb_debug_set_trace(void* device_buffer) {
+int bsb_set_dependent_launch(int32_t on) {
+  g_pdl_enabled = on ? 1 : 0;
+  return BSB_OK;
+}
+
+#ifdef BSB_TUNING
+// tuning build only (not declared in the public header): timing experiments and the cycle trace of the decode kernel
+int bsb_tuning_set_trace(void* device_buffer) {
   gemv_tc5_set_trace((unsigned long long*)device_buffer);
   return BSB_OK;
 }
-
-int bsb_debug_set_mode(int32_t mode) {
-  if (mode == 100 || mode == 101) {   // programmatic dependent launch off / on
-    gemv_tc5_set_pdl(mode - 100);
-    return BSB_OK;
-  }
+int bsb_tuning_set_mode(int32_t mode) {
   gemv_tc5_set_dbg(mode);
   return BSB_OK;
 }
+#endif
 
 int64_t bsb_debug_launch_count(void) { return (int64_t)g_launches; }
 
@@ -379,11 +367,17 @@ int bsb_linear_forward_host(const bsb_weight* w, const uint16_t* host_x, int64_t
   BSB_CHECK_ARG(host_x && host_y && dev_x && dev_y, "NULL buffer");
   cudaStream_t s = (cudaStream_t)stream;
   BSB_CUDA(cudaMemcpyAsync(dev_x, host_x, (size_t)rows * w->in_features * 2, cudaMemcpyHostToDevice, s));
-  if (int rc = forward_one(*w, (const __half*)dev_x, rows, w->in_features, (__half*)dev_y, w->out_features,
+  if (int rc = forward_one(*w, (const __half*)dev_x, rows, w->in_features, (__half*)dev_y, nullptr, w->out_features,
                            workspace, workspace_bytes, algo, s))
     return rc;
   BSB_CUDA(cudaMemcpyAsync(host_y, dev_y, (size_t)rows * w->out_features * 2, cudaMemcpyDeviceToHost, s));
+  int32_t code = 0;
+  BSB_CUDA(cudaMemcpyAsync(&code, device_status_word(), 4, cudaMemcpyDeviceToHost, s));
   BSB_CUDA(cudaStreamSynchronize(s));
+  if (code != 0) {   // the call's outputs are NaN; the word stays set until bsb_read_status() clears it
+    set_error("a time-bounded wait gave up on the device (code %d)", code);
+    return BSB_ETIMEOUT;
+  }
   return BSB_OK;
 }
 

@@ -75,12 +75,21 @@ static inline int64_t align_up64(int64_t a, int64_t b) { return ceil_div64(a, b)
 // number of multiprocessors of the current device (cached per device)
 int sm_count();
 
+// dimension and block-stride checks shared by every entry point that takes a weight
+int check_weight(const bsb_weight* w);
+
+// Device address of the library's sticky status word for the current device (looked up once per device with
+// cudaGetSymbolAddress; nullptr + error text when that fails).  A kernel whose time-bounded wait gives up stores
+// a non-zero code there with atomicCAS(word, 0, code): the first event stays until bsb_read_status() clears it.
+int* device_status_word();
+
 // ---- launchers implemented in the kernel translation units -------------------
 int launch_pack_sign(const int8_t* sign, int64_t n, uint8_t* packed, int32_t* bad, cudaStream_t s);
 int launch_unpack_sign(const uint8_t* packed, int64_t n, int8_t* out, cudaStream_t s);
 
+// exactly one of y (fp16 output) and y32 (fp32 partial sums of a tensor-parallel shard) is non-null here and below
 int launch_general_forward(const bsb_weight& w, const __half* x, int64_t rows, int64_t x_stride,
-                           __half* y, int64_t y_stride, cudaStream_t s);
+                           __half* y, float* y32, int64_t y_stride, cudaStream_t s);
 int launch_general_reconstruct(const bsb_weight& w, __half* w_out, cudaStream_t s);
 
 // fast reconstruction (k == 16, in % 32 == 0, out % 16 == 0)
@@ -93,29 +102,22 @@ int launch_gemm_xwt(const __half* x, int64_t rows, int64_t x_stride, const __hal
                     int out_features, int in_features, const __half* bias, __half* y,
                     int64_t y_stride, cudaStream_t s);
 
-// the same product on the tcgen05 tensor cores (TMA-fed, accumulators in tensor memory); `status` is a
-// device word that a wait which gives up raises (may be nullptr)
+// the same product on the tcgen05 tensor cores (TMA-fed, accumulators in tensor memory)
 bool gemm_tc5_supported(int64_t rows, int out_features, int in_features);
 int launch_gemm_tc5(const __half* x, int64_t rows, int64_t x_stride, const __half* w, int out_features,
-                    int in_features, const __half* bias, __half* y, int64_t y_stride, int* status, cudaStream_t s);
+                    int in_features, const __half* bias, __half* y, float* y32, int64_t y_stride, cudaStream_t s);
 
-// decode path: packed signs streamed into fp8 tensor-core MMAs
+// decode path (tcgen05: sign operand expanded into tensor memory)
 int launch_vt_absmax(const bsb_weight& w, float* out, cudaStream_t s);
-bool gemv_mma_supported(const bsb_weight& w);
-int64_t gemv_mma_workspace_bytes(const bsb_weight* ws, int n_weights);
-int launch_gemv_mma(const bsb_weight* ws, int n_weights, const __half* x, __half* const* ys,
-                    void* workspace, int64_t workspace_bytes, cudaStream_t s);
-
-// decode path, tcgen05 generation (A operand in tensor memory)
 bool gemv_tc5_supported(const bsb_weight& w);
 int64_t gemv_tc5_workspace_bytes(const bsb_weight* ws, int n_weights, int rows_per_pass);   // rows_per_pass: 1 or 2
+void gemv_tc5_set_wait_limit_ns(unsigned long long ns);
+#ifdef BSB_TUNING
 void gemv_tc5_set_trace(unsigned long long* device_buffer);
 void gemv_tc5_set_dbg(int mode);
-void gemv_tc5_set_pdl(int on);
-int64_t gemv_tc5_status_offset(const bsb_weight* ws, int n_weights);
-// `tf` (may be nullptr): input transform applied while the Z' operand is built, see bsb_input_transform
+#endif
+// out_f32: the ys point at fp32 rows (partial sums of a tensor-parallel shard) instead of fp16 ones
 int launch_gemv_tc5(const bsb_weight* ws, int n_weights, const __half* x, int64_t x_stride, int rows, __half* const* ys,
-                    const int64_t* y_strides, void* workspace, int64_t workspace_bytes, cudaStream_t s,
-                    const bsb_input_transform* tf = nullptr);
+                    const int64_t* y_strides, void* workspace, int64_t workspace_bytes, cudaStream_t s, bool out_f32 = false);
 
 }  // namespace bsb

@@ -116,10 +116,11 @@ struct alignas(64) GemmParams {
   CUtensorMap map_x;   // fp16 [rows][in], box 64 x 128
   CUtensorMap map_w;   // fp16 [out][in], box 64 x BN
   const __half* bias;
-  __half* y;
+  __half* y;           // fp16 output, or
+  float* y32;          // fp32 output (partial sums of a tensor-parallel shard): exactly one of the two is set
   int64_t y_stride;
   int rows, out_features, in_features;
-  int* status;         // device word raised when a wait gives up (may be nullptr)
+  int* status;         // the library's sticky status word: the first wait that gives up leaves its code there
 };
 
 template <int BN>
@@ -175,7 +176,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc5_kernel(const __grid_cons
         const int m0 = (tile % row_tiles) * kBM, n0 = (tile / row_tiles) * BN;
         for (int k = 0; k < k_steps; ++k, ++it) {
           const int s = it % kStages, n = it / kStages;
-          if (n >= 1 && !mbar_wait(&empty[s], (n - 1) & 1)) { if (P.status) atomicExch(P.status, 21); ok = false; break; }
+          if (n >= 1 && !mbar_wait(&empty[s], (n - 1) & 1)) { if (P.status) atomicCAS(P.status, 0, 21); ok = false; break; }
           mbar_expect_tx(&full[s], kABytes + kBBytes);
           // rows and K past the end of a tensor read as zeros
           tma_load_2d(sa + s * kABytes, &P.map_x, k * kBK, m0, &full[s]);
@@ -192,12 +193,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc5_kernel(const __grid_cons
     for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++t_idx) {
       const int ab = t_idx % kAcc, use = t_idx / kAcc;
       // the epilogue must have emptied this accumulator (its use before this one)
-      if (use >= 1 && !mbar_wait(&dempty[ab], (use - 1) & 1)) { if (leader && P.status) atomicExch(P.status, 24); ok = false; break; }
+      if (use >= 1 && !mbar_wait(&dempty[ab], (use - 1) & 1)) { if (leader && P.status) atomicCAS(P.status, 0, 24); ok = false; break; }
       tc_fence_after();
       const uint32_t dcol = tbase + ab * BN;
       for (int k = 0; k < k_steps; ++k, ++it) {
         const int s = it % kStages;
-        if (!mbar_wait(&full[s], (it / kStages) & 1)) { if (leader && P.status) atomicExch(P.status, 22); ok = false; break; }
+        if (!mbar_wait(&full[s], (it / kStages) & 1)) { if (leader && P.status) atomicCAS(P.status, 0, 22); ok = false; break; }
         tc_fence_after();
         if (leader) {
           const uint64_t adesc = make_desc_sw128(smem_u32(sa + s * kABytes));
@@ -222,11 +223,27 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc5_kernel(const __grid_cons
       bool ok = mbar_wait(&dfull[ab], use & 1);
       ok = __all_sync(0xFFFFFFFFu, ok ? 1 : 0) != 0;
       if (!ok) {
-        if (lane == 0 && P.status) atomicExch(P.status, 23);
+        if (lane == 0 && P.status) atomicCAS(P.status, 0, 23);
+        // this tile and the CTA's remaining ones are marked NaN: a timed-out call must not pass for a result
+        const uint32_t nan2 = 0x7E007E00u;
+        for (int t2 = tile; t2 < n_tiles; t2 += gridDim.x) {
+          const int r2 = (t2 % row_tiles) * kBM + quarter * 32 + lane, c2 = (t2 / row_tiles) * BN;
+          if (r2 < P.rows)
+            for (int n = c2; n < min(c2 + BN, P.out_features); n += 8) {
+              if (P.y32) {
+                const float qn = __int_as_float(0x7FC00000);
+                *reinterpret_cast<float4*>(P.y32 + (int64_t)r2 * P.y_stride + n) = make_float4(qn, qn, qn, qn);
+                *reinterpret_cast<float4*>(P.y32 + (int64_t)r2 * P.y_stride + n + 4) = make_float4(qn, qn, qn, qn);
+              } else {
+                *reinterpret_cast<uint4*>(P.y + (int64_t)r2 * P.y_stride + n) = make_uint4(nan2, nan2, nan2, nan2);
+              }
+            }
+        }
         break;
       }
       tc_fence_after();
       __half* yrow = P.y + (int64_t)row * P.y_stride;
+      float* yrow32 = P.y32 + (int64_t)row * P.y_stride;
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         uint32_t d[32];
@@ -239,6 +256,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc5_kernel(const __grid_cons
             if (n < P.out_features) {           // out_features is a multiple of 8
               uint4 out;
               __half2* o = reinterpret_cast<__half2*>(&out);
+              float f[8];
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
                 float a = __uint_as_float(d[v * 8 + 2 * q]), b = __uint_as_float(d[v * 8 + 2 * q + 1]);
@@ -247,8 +265,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc5_kernel(const __grid_cons
                   b += __half2float(P.bias[n + 2 * q + 1]);
                 }
                 o[q] = __floats2half2_rn(a, b);
+                f[2 * q] = a;
+                f[2 * q + 1] = b;
               }
-              *reinterpret_cast<uint4*>(yrow + n) = out;
+              if (P.y32) {
+                *reinterpret_cast<float4*>(yrow32 + n) = make_float4(f[0], f[1], f[2], f[3]);
+                *reinterpret_cast<float4*>(yrow32 + n + 4) = make_float4(f[4], f[5], f[6], f[7]);
+              } else {
+                *reinterpret_cast<uint4*>(yrow + n) = out;
+              }
             }
           }
         }
@@ -330,21 +355,24 @@ bool gemm_tc5_supported(int64_t rows, int out_features, int in_features) {
 }
 
 int launch_gemm_tc5(const __half* x, int64_t rows, int64_t x_stride, const __half* w, int out_features,
-                    int in_features, const __half* bias, __half* y, int64_t y_stride, int* status, cudaStream_t s) {
+                    int in_features, const __half* bias, __half* y, float* y32, int64_t y_stride, cudaStream_t s) {
   BSB_CHECK_ARG(gemm_tc5_supported(rows, out_features, in_features), "gemm: unsupported shape (rows=%lld out=%d in=%d)",
                 (long long)rows, out_features, in_features);
   BSB_CHECK_ARG((uintptr_t)x % 16 == 0 && x_stride % 8 == 0 && (uintptr_t)w % 16 == 0,
                 "gemm: x and W must be 16-byte aligned with row strides that are multiples of 8");
-  BSB_CHECK_ARG((uintptr_t)y % 16 == 0 && y_stride % 8 == 0, "gemm: y must be 16-byte aligned with a row stride that is a multiple of 8");
+  BSB_CHECK_ARG((y != nullptr) != (y32 != nullptr), "gemm: exactly one of the fp16 and the fp32 output");
+  BSB_CHECK_ARG(((uintptr_t)y | (uintptr_t)y32) % 16 == 0 && y_stride % 8 == 0, "gemm: y must be 16-byte aligned with a row stride that is a multiple of 8");
   GemmParams P;
   memset(&P, 0, sizeof(P));
   P.bias = bias;
   P.y = y;
+  P.y32 = y32;
   P.y_stride = y_stride;
   P.rows = (int)rows;
   P.out_features = out_features;
   P.in_features = in_features;
-  P.status = status;
+  P.status = device_status_word();
+  if (P.status == nullptr) return BSB_ECUDA;
   // wide tiles when they still give every multiprocessor a CTA; narrower ones for small problems,
   // which are bound by streaming W and want many CTAs in flight
   const int64_t row_tiles = ceil_div64(rows, kBM);

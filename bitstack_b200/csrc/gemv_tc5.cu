@@ -5,7 +5,7 @@
 // Replaces, for single-row inputs, every fused level of the reference forward
 // (bitstack/modules/BitStackLinear.py:116-157).
 //
-// Math (see also gemv_mma.cu).  For block j, Z_j[n,r] = Vt_j[r,n] x[n] and
+// Math.  For block j, Z_j[n,r] = Vt_j[r,n] x[n] and
 //     y[m] = sum_j sum_r U_j[m,r] D_j[m,r],   D_j[m,r] = sum_n S_j[m,n] Z_j[n,r].
 // A 32-bit word of packed signs (32 columns of one row) is expanded by eight logic
 // instructions into eight registers of four e4m3 numbers: register i holds, in byte
@@ -26,6 +26,10 @@
 #include <cuda.h>
 #include <cuda_fp8.h>
 
+#if defined(BSB_TRACE) && !defined(BSB_TUNING)
+#define BSB_TUNING
+#endif
+
 #include "common.cuh"
 
 namespace bsb {
@@ -45,7 +49,7 @@ constexpr int kTmemCols = 256;                  // 4 x 32 (D: 2 issuers x 2 buff
 constexpr int kMaxGroup = 4;
 constexpr float kTargetMax = 320.f;
 constexpr float kMinD = 0.75f;
-constexpr uint64_t kWaitLimitNs = 200ull * 1000 * 1000;
+constexpr unsigned long long kDefaultWaitNs = 200ull * 1000 * 1000;   // default limit of every wait (bsb_set_wait_limit_ms)
 
 __constant__ float kV0[8] = {8.f, 4.f, 2.f, 0.75f, 0.375f, 0.09375f, 0.f, 1.f};
 __constant__ float kD[8] = {1.f, 1.f, 1.f, 0.75f, 1.125f, 1.40625f, 2.f, -2.f};
@@ -58,20 +62,12 @@ struct alignas(64) TcParams {
   CUtensorMap sign_map[kMaxGroup];   // u8 [blocks][out][in/8], box 1 x 128 x 64, 64-byte swizzle
   bsb_weight w[kMaxGroup];
   const float* vt_absmax[kMaxGroup];
-  __half* y[kMaxGroup];
+  __half* y[kMaxGroup];            // fp16 rows, or fp32 rows when out_f32 is set
+  int out_f32;                     // outputs are fp32 partial sums of a tensor-parallel shard (no rounding)
   int n_weights;
   int rows;                        // input rows of this pass (1 or 2): the B operand holds 32 columns per row
   int64_t x_stride;                // elements between input rows
   int64_t y_stride[kMaxGroup];     // elements between output rows
-  // input transform applied while Z' is built (bsb_input_mode): 0 = x as given; 1 = x = rmsnorm(x + x2) * norm_w with
-  // the sum x + x2 (fp16) also written to h_out; 2 = x = silu(x) * x2
-  int x_mode;
-  const __half* x2;                // second operand of the transform (may be nullptr in mode 1), rows x2_stride apart
-  int64_t x2_stride;
-  const __half* norm_w;
-  float eps;
-  __half* h_out;                   // mode 1: the updated residual stream, rows h_out_stride apart
-  int64_t h_out_stride;
   int n_chunks;                    // ceil(in / 512)
   int step_base[kMaxGroup + 1];    // first work step of each weight; a step = (row group, block, chunk)
   int seg_base[kMaxGroup + 1];     // first row group of each weight (index of its counter)
@@ -86,9 +82,13 @@ struct alignas(64) TcParams {
   float* kconst;     // [(weight,block)][chunk][rows][16]
   float* inv_scale;  // [(weight,block)][rows][16]
   int* counters;     // [row group]: CTAs that have delivered their partial sums
-  int* status;       // 0 = fine, else the code of the wait that gave up
-  unsigned long long* trace;  // optional [CTA][16] cycle counters (debug), or nullptr
-  int dbg;           // 0 = normal; 1 = MMA side only, 2 = producer side only (timing experiments, wrong results)
+  int* status;       // the library's sticky status word of this device: 0 = fine, else the code of the first wait that gave up
+  unsigned long long wait_ns;   // time limit of every wait
+#ifdef BSB_TUNING
+  unsigned long long* trace;  // optional [CTA][16] cycle counters, or nullptr
+  int dbg;           // 0 = normal; 1 = MMA side only, 2 = producer side only (timing experiments, wrong results); 3 = the Z' loader
+                     // never loads (the waits behind it run out: exercises the give-up path)
+#endif
   float* partials;   // [CTA][2][rows][RT * 128]: sums of a row group that the CTA shares with other CTAs
 };
 
@@ -114,52 +114,39 @@ __device__ __forceinline__ uint64_t global_ns() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
-// time-bounded wait; false = gave up
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-#pragma unroll 1
-  for (int i = 0; i < 256; ++i)
-    if (mbar_test(bar, parity)) return true;
+// mbarrier.try_wait suspends the thread in hardware until the phase completes or a short, implementation-defined
+// time has passed: a waiting role costs almost no issue slots.
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+               : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// time-bounded wait; false = gave up after `limit_ns`
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned long long limit_ns) {
+  if (mbar_try(bar, parity)) return true;
   const uint64_t t0 = global_ns();
 #pragma unroll 1
   while (true) {
 #pragma unroll 1
-    for (int i = 0; i < 32; ++i) {
-      if (mbar_test(bar, parity)) return true;
-      __nanosleep(40);
-    }
-    if (global_ns() - t0 > kWaitLimitNs) return false;
+    for (int i = 0; i < 16; ++i)
+      if (mbar_try(bar, parity)) return true;
+    if (global_ns() - t0 > limit_ns) return false;
   }
 }
-// Wait for roles that have slack (epilogue, loader): one lane polls with a growing sleep, so the
-// barrier words, the issue slots and the special-register path stay free for the warps on the
-// critical path; the other lanes then observe the completed phase once (their own acquire).
-__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity) {
-  if (mbar_test(bar, parity)) return true;
-  uint32_t sleep_ns = 64;
-  uint64_t t0 = 0;
-#pragma unroll 1
-  for (int n = 1;; ++n) {
-    __nanosleep(sleep_ns);
-    if (mbar_test(bar, parity)) return true;
-    if (sleep_ns < 512) sleep_ns *= 2;
-    if ((n & 63) == 0) {
-      const uint64_t now = global_ns();
-      if (t0 == 0) t0 = now;
-      else if (now - t0 > kWaitLimitNs) return false;
-    }
-  }
-}
-__device__ __forceinline__ bool mbar_wait_warp_relaxed(uint64_t* bar, uint32_t parity) {
+// Wait of a whole warp in which one lane does the waiting (roles with slack: epilogue); the other lanes then
+// observe the completed phase once (their own acquire).
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, unsigned long long limit_ns) {
   int ok = 1;
-  if ((threadIdx.x & 31) == 0) ok = mbar_wait_relaxed(bar, parity) ? 1 : 0;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, limit_ns) ? 1 : 0;
   ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
   if (ok) ok = mbar_test(bar, parity) ? 1 : 0;
   return __all_sync(0xFFFFFFFFu, ok) != 0;
 }
-// producer-group wait: every lane polls for itself -- electing one poller per warp adds a
-// shuffle and a second test to the hand-off, which measured 25 % slower on the whole kernel
-__device__ __forceinline__ bool mbar_wait_group(uint64_t* bar, uint32_t parity) {
-  return __all_sync(0xFFFFFFFFu, mbar_wait(bar, parity) ? 1 : 0) != 0;
+// producer-group wait: every lane waits for itself (electing one waiting lane per warp adds a shuffle and a
+// second test to the hand-off, which measured slower on the whole kernel)
+__device__ __forceinline__ bool mbar_wait_group(uint64_t* bar, uint32_t parity, unsigned long long limit_ns) {
+  return __all_sync(0xFFFFFFFFu, mbar_wait(bar, parity, limit_ns) ? 1 : 0) != 0;
 }
 __device__ __forceinline__ void tmem_alloc(uint32_t* dst, int cols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst)), "r"(cols) : "memory");
@@ -246,14 +233,29 @@ __device__ __forceinline__ void expand_word_c(uint32_t word, const uint32_t (&c)
   r[4] = expand_c<4>(word, c[4]); r[5] = expand_c<5>(word, c[5]); r[6] = expand_c<6>(word, c[6]); r[7] = expand_c<7>(word, c[7]);
 }
 
+// ------------------------------------------------------------------ max |vt| per (block, rank)
+// grid = (16 ranks, blocks).  Sets the scale of the e4m3 operand; a pure function of the stored factors.
+__global__ void __launch_bounds__(256) vt_absmax_kernel(bsb_weight w, float* __restrict__ out) {
+  const int r = blockIdx.x, j = blockIdx.y;
+  const __half* vt = reinterpret_cast<const __half*>(w.vt) + (int64_t)j * w.vt_block_stride + (int64_t)r * w.in_features;
+  float m = 0.f;
+  for (int n = threadIdx.x; n < w.in_features; n += blockDim.x) m = fmaxf(m, fabsf(__half2float(vt[n])));
+  __shared__ float red[8];
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < 8; ++i) m = fmaxf(m, red[i]);
+    out[j * 16 + r] = m;
+  }
+}
+
 // ------------------------------------------------------------------ Z' preparation
 // grid = (n_chunks, total blocks, input rows), 256 threads.  Operand tile of word w (32 columns):
 // byte offset (n%8)*16 + (n/8)*256 + (k%16) + (k/16)*128 with n = 16*piece + rank and
 // k = 4*i + c for the column 8c+7-i of the word.
-// MODE = the input transform (bsb_input_transform.mode), a template parameter so that the plain path carries none of it
-template <int MODE>
 __global__ void __launch_bounds__(256) zprep_tc5_kernel(const __grid_constant__ TcParams P, const __half* __restrict__ x) {
-  __shared__ float red[8], red2[8];
+  __shared__ float red[8];
   __shared__ float kred[16][16];
 
   const int chunk = blockIdx.x;
@@ -267,104 +269,43 @@ __global__ void __launch_bounds__(256) zprep_tc5_kernel(const __grid_constant__ 
   // of x, fetched straight into registers -- no staging, one barrier in the whole kernel
   const int word = tid >> 4, r = tid & 15;
   const int col0 = chunk * kChunkCols + word * 32;
-
-  // x and the scratch of the previous call are safe to touch once the kernels before this one are
-  // done; then the decode kernel of this call may be scheduled (it waits before touching anything
-  // written here)
-  pdl_wait();
-  pdl_trigger();
-
   const int R = P.rows, row = blockIdx.z;
-  x += (int64_t)row * P.x_stride;
-  if (blockIdx.x == 0 && blockIdx.y == 0 && row == 0) {
-    for (int i = tid; i < P.seg_base[P.n_weights]; i += blockDim.x) P.counters[i] = 0;
-    if (tid == 0) *P.status = 0;
-  }
-  // 8 consecutive values of the transform's pre-normalisation input: x (mode 0), silu(x) * x2 rounded as the
-  // stand-alone kernel rounds it (mode 2), or the fp16 sum x + x2 (mode 1)
-  constexpr int mode = MODE;
-  const __half* x2 = P.x2 ? P.x2 + (int64_t)row * P.x2_stride : nullptr;
-  auto load8 = [&](int i8) -> uint4 {
-    uint4 a = __ldg(reinterpret_cast<const uint4*>(x) + i8);
-    if (mode == 0 || x2 == nullptr) return a;
-    const uint4 b = __ldg(reinterpret_cast<const uint4*>(x2) + i8);
-    __half2* ah = reinterpret_cast<__half2*>(&a);
-    const __half2* bh = reinterpret_cast<const __half2*>(&b);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float2 fa = __half22float2(ah[i]), fb = __half22float2(bh[i]);
-      if (mode == 1) {
-        ah[i] = __floats2half2_rn(fa.x + fb.x, fa.y + fb.y);
-      } else {
-        const float2 sf = __half22float2(__floats2half2_rn(fa.x / (1.f + __expf(-fa.x)), fa.y / (1.f + __expf(-fa.y))));
-        ah[i] = __floats2half2_rn(sf.x * fb.x, sf.y * fb.y);
-      }
-    }
-    return a;
-  };
-  // issue every load first: Vt and x words of this thread, then the pass over x for max |x|
+  const bool in_range = col0 < N;   // in_features is a multiple of 128, so a word is inside or outside as a whole
+
+  // The decode kernel of this call may be scheduled at once (it prefetches sign tiles, which depend on nothing, and
+  // waits for this grid before it touches anything written here).  The factors are constants of the weight: they are
+  // fetched before the wait for the kernels in front of this one, whose outputs are x and the scratch of the previous call.
+  pdl_trigger();
   uint4 vq[4], xq[4];
   const __half* vt = reinterpret_cast<const __half*>(w.vt) + (int64_t)j * w.vt_block_stride + (int64_t)r * N;
-  const bool in_range = col0 < N;   // in_features is a multiple of 128, so a word is inside or outside as a whole
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    vq[i] = in_range ? __ldg(reinterpret_cast<const uint4*>(vt + col0) + i) : make_uint4(0, 0, 0, 0);
-    xq[i] = in_range ? load8(col0 / 8 + i) : make_uint4(0, 0, 0, 0);
-  }
-  float xm = 0.f, ss = 0.f;
-  const bool writer = (mode == 1 && P.h_out != nullptr && blockIdx.x == 0 && blockIdx.y == 0);
+  for (int i = 0; i < 4; ++i) vq[i] = in_range ? __ldg(reinterpret_cast<const uint4*>(vt + col0) + i) : make_uint4(0, 0, 0, 0);
+  const float vmax = P.vt_absmax[wi][j * 16 + r];
+  pdl_wait();
+
+  x += (int64_t)row * P.x_stride;
+  if (blockIdx.x == 0 && blockIdx.y == 0 && row == 0)
+    for (int i = tid; i < P.seg_base[P.n_weights]; i += blockDim.x) P.counters[i] = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) xq[i] = in_range ? __ldg(reinterpret_cast<const uint4*>(x) + col0 / 8 + i) : make_uint4(0, 0, 0, 0);
+  // max |x| over the whole row: sets the scale of the e4m3 operand
+  float xm = 0.f;
   for (int n8 = tid; n8 < N / 8; n8 += blockDim.x) {
-    const uint4 q = load8(n8);
+    const uint4 q = __ldg(reinterpret_cast<const uint4*>(x) + n8);
     const __half2* h = reinterpret_cast<const __half2*>(&q);
-    if (mode == 1) {
-      if (writer) reinterpret_cast<uint4*>(P.h_out + (int64_t)row * P.h_out_stride)[n8] = q;
-      const uint4 wv = __ldg(reinterpret_cast<const uint4*>(P.norm_w) + n8);
-      const __half2* wh = reinterpret_cast<const __half2*>(&wv);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float2 f = __half22float2(h[i]), g = __half22float2(wh[i]);
-        ss += f.x * f.x + f.y * f.y;
-        xm = fmaxf(xm, fmaxf(fabsf(f.x * g.x), fabsf(f.y * g.y)));
-      }
-    } else {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float2 f = __half22float2(__habs2(h[i]));
-        xm = fmaxf(xm, fmaxf(f.x, f.y));
-      }
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __half22float2(__habs2(h[i]));
+      xm = fmaxf(xm, fmaxf(f.x, f.y));
     }
   }
-  for (int o = 16; o > 0; o >>= 1) {
-    xm = fmaxf(xm, __shfl_xor_sync(0xFFFFFFFFu, xm, o));
-    ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
-  }
-  if (lane == 0) { red[warp] = xm; red2[warp] = ss; }
+  for (int o = 16; o > 0; o >>= 1) xm = fmaxf(xm, __shfl_xor_sync(0xFFFFFFFFu, xm, o));
+  if (lane == 0) red[warp] = xm;
   __syncthreads();
   xm = red[0];
-  ss = red2[0];
 #pragma unroll
-  for (int i = 1; i < 8; ++i) { xm = fmaxf(xm, red[i]); ss += red2[i]; }
-  if (mode == 1) {
-    // x = (x + x2) * rsqrt(mean square + eps) * norm_w, rounded to fp16 like the stand-alone kernel; the bound on
-    // |x| is taken a hair larger to cover that rounding
-    const float inv = rsqrtf(ss / (float)N + P.eps);
-    xm = xm * inv * 1.001f;
-    if (in_range) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const uint4 wv = __ldg(reinterpret_cast<const uint4*>(P.norm_w + col0) + i);
-        const __half2* wh = reinterpret_cast<const __half2*>(&wv);
-        __half2* xh = reinterpret_cast<__half2*>(&xq[i]);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 f = __half22float2(xh[e]), g = __half22float2(wh[e]);
-          xh[e] = __floats2half2_rn(f.x * inv * g.x, f.y * inv * g.y);
-        }
-      }
-    }
-  }
+  for (int i = 1; i < 8; ++i) xm = fmaxf(xm, red[i]);
 
-  const float vmax = P.vt_absmax[wi][j * 16 + r];
   const float bound = vmax * xm;
   const float scale = (bound > 0.f) ? (kTargetMax * kMinD) / (2.f * bound) : 1.f;
   const float inv_scale = 1.f / scale;
@@ -435,6 +376,14 @@ __global__ void __launch_bounds__(256) zprep_tc5_kernel(const __grid_constant__ 
 #define TR_BEGIN(var) do { } while (0)
 #define TR_ADD(slot, var) do { } while (0)
 #endif
+// timing experiments of the tuning build select a mode at run time; the product build has none of it
+#ifdef BSB_TUNING
+#define DBG_IS(n) (P.dbg == (n))
+#else
+#define DBG_IS(n) false
+#endif
+// a wait gave up: record the first such event of the device (sticky until the host reads it) and mark the CTA
+#define GIVE_UP(code) do { atomicCAS(P.status, 0, (code)); S.failed = 1; } while (0)
 
 // ------------------------------------------------------------------ main kernel
 // Work is the sequence of STEPS (weight, row group, block, chunk) in that order, a step being one
@@ -467,8 +416,11 @@ struct __align__(1024) SmemLayout {
   uint8_t zs[kSlabs][kChunkBytes * R];  // Z' operand slabs (bulk-copied)
   uint8_t sg[kSignTiles * kSignTileBytes];   // sign tiles: row r at r*64, 16-byte piece p at ((p ^ ((r>>1)&3)) * 16)
   uint64_t afull[2][2], aempty[2][2], zfull[kSlabs], zempty[kSlabs], sfull[6], sempty[6], dfull[2][2], dempty[2];
+#ifdef BSB_TRACE
   unsigned long long trace[16];
+#endif
   uint32_t tmem_base;
+  int failed;                           // a wait of this CTA gave up: its outputs are marked NaN
   int n_pending;
   int pending[2][2];                    // row groups shared with other CTAs (at most the first and the last): weight, row group
   int last;
@@ -478,6 +430,12 @@ constexpr int kWarpMma = 8;     // warps 8, 9: MMA issuers 0, 1
 constexpr int kWarpLoad = 10;   // warp 10: tensor-memory allocation, sign tiles (TMA); warp 11: Z' slabs (bulk copies)
 constexpr int kWarpEpi = 12;    // warps 12-15: epilogue (tensor-memory lane quarters 0-3)
 
+// one output element: fp16 (rounded once), or fp32 when the call delivers partial sums
+__device__ __forceinline__ void store_y(const TcParams& P, int wi, int r, int m, float v) {
+  const int64_t i = (int64_t)r * P.y_stride[wi] + m;
+  if (P.out_f32) reinterpret_cast<float*>(P.y[wi])[i] = v;
+  else P.y[wi][i] = __float2half_rn(v);
+}
 __device__ __forceinline__ int first_step_of_cta(const TcParams& P, int c) {
   return c < P.n_first ? c * P.steps_first : P.n_first * P.steps_first + (c - P.n_first) * P.steps_per_cta;
 }
@@ -543,19 +501,24 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
   // trace slots: 0-3 producer group 0 (total, tile wait, ring wait, expand+store), 4-8 issuer 0 (total,
   // Z' wait, operand wait, accumulator wait, issue), 9-10 epilogue (accumulator wait, total), 11 loader
   // wait, 12 CTA total, 13 set-up
+#ifdef BSB_TRACE
   unsigned long long* tr = (P.trace && lane == 0 && (warp == 0 || warp == kWarpMma || warp == kWarpLoad || warp == kWarpEpi))
                                ? P.trace + (int64_t)blockIdx.x * 16 : nullptr;
-  (void)tr;
+#endif
   TR_BEGIN(t_cta);
+  const unsigned long long wait_ns = P.wait_ns;
 
   // ---- set-up ---------------------------------------------------------------------
   if (warp == kWarpLoad) {
     tmem_alloc(&S.tmem_base, kTmemCols);
     tmem_relinquish();
   }
+#ifdef BSB_TRACE
   if (tid < 14) S.trace[tid] = 0;
+#endif
   if (tid == 0) {
     S.n_pending = 0;
+    S.failed = 0;
 #ifdef BSB_TRACE
     S.trace[14] = global_ns();   // wall-clock start / end of the CTA body (slots 14, 15)
 #endif
@@ -586,7 +549,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
       for (int g = 0; g < total; ++g) {
         const int slot = g % kNS, n = g / kNS;
         TR_BEGIN(t0);
-        if (n >= 1 && !mbar_wait_relaxed(&S.sempty[slot], (n - 1) & 1)) { atomicExch(P.status, 7); break; }
+        if (n >= 1 && !mbar_wait(&S.sempty[slot], (n - 1) & 1, wait_ns)) { GIVE_UP(7); break; }
         TR_ADD(11, t0);
         mbar_expect_tx(&S.sfull[slot], kSlotBytes);
 #pragma unroll
@@ -598,13 +561,13 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
     }
   } else if (warp == kWarpLoad + 1) {
     // ---- Z' loader: one 16 KB bulk copy per step ---------------------------------------------
-    if (lane == 0 && P.dbg != 2) {
+    if (lane == 0 && !DBG_IS(2) && !DBG_IS(3)) {
       asm volatile("griddepcontrol.wait;" ::: "memory");
       Walk wk;
       wk.init(P, step0, kRows);
       for (int g = 0; g < total; ++g) {
         const int slot = g % kNZr, n = g / kNZr;
-        if (n >= 1 && !mbar_wait_relaxed(&S.zempty[slot], (n - 1) & 1)) { atomicExch(P.status, 1); break; }
+        if (n >= 1 && !mbar_wait(&S.zempty[slot], (n - 1) & 1, wait_ns)) { GIVE_UP(1); break; }
         const uint8_t* zsrc = P.zops + ((int64_t)(P.blk_base[wk.wi] + wk.js) * NCH + wk.ci) * kSlabBytes;
         mbar_expect_tx(&S.zfull[slot], kSlabBytes);
         bulk_g2s(S.zs[slot], zsrc, kSlabBytes, &S.zfull[slot]);
@@ -617,9 +580,11 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
     // The whole warp runs the loop and the waits (a warp-wide poll costs the same issue slots as a
     // one-lane poll) so that addresses and descriptors stay warp-uniform values; one elected lane
     // issues the MMAs and commits.
-    if (P.dbg != 2) {
+    if (!DBG_IS(2)) {
       const int e = warp - kWarpMma;
+#ifdef BSB_TRACE
       if (e != 0) tr = nullptr;
+#endif
       const bool leader = elect_one();
       const uint32_t idesc = make_idesc_f8(128, kDCols);
       Walk wk;
@@ -632,13 +597,13 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
         const int b = bs % kND;
         if (first && bs >= kND) {
           TR_BEGIN(t0);
-          if (!mbar_wait(&S.dempty[b], ((bs / kND) - 1) & 1)) { if (leader) atomicExch(P.status, 6); ok = false; break; }
+          if (!mbar_wait(&S.dempty[b], ((bs / kND) - 1) & 1, wait_ns)) { if (leader) GIVE_UP(6); ok = false; break; }
           TR_ADD(7, t0);
           tc_fence_after();
         }
         const int zslot = g % kNZr;
         TR_BEGIN(t1);
-        if (!mbar_wait(&S.zfull[zslot], (g / kNZr) & 1)) { if (leader) atomicExch(P.status, 2); ok = false; break; }
+        if (!mbar_wait(&S.zfull[zslot], (g / kNZr) & 1, wait_ns)) { if (leader) GIVE_UP(2); ok = false; break; }
         TR_ADD(5, t1);
         const uint32_t zaddr = smem_u32(S.zs[zslot]) + (RT == 1 ? (uint32_t)e * 8u * 1024u * R : 0u);
         const uint32_t dcol = tbase + (e * kND + b) * kDCols;
@@ -646,7 +611,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
         for (int pp = 0; pp < kPP; ++pp, ++it) {
           const int slot = it & 1;
           TR_BEGIN(t2);
-          if (P.dbg != 1 && !mbar_wait(&S.afull[e][slot], (it >> 1) & 1)) { if (leader) atomicExch(P.status, 3); ok = false; break; }
+          if (!DBG_IS(1) && !mbar_wait(&S.afull[e][slot], (it >> 1) & 1, wait_ns)) { if (leader) GIVE_UP(3); ok = false; break; }
           TR_ADD(6, t2);
           TR_BEGIN(t3);
           tc_fence_after();
@@ -677,9 +642,11 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
   } else if (warp < kWarpMma) {
     // ---- producer group e: one sign row per thread.  RT == 1: bytes 32e .. 32e+31 of the row
     //      of the only tile; RT == 2: all 64 bytes of the row of tile e ----------------------
-    if (P.dbg != 1) {
+    if (!DBG_IS(1)) {
       const int e = warp >> 2;
+#ifdef BSB_TRACE
       if (e != 0) tr = nullptr;
+#endif
       const int rtid = tid & (kTileRows - 1);
       const uint32_t lane_base = tbase + ((uint32_t)((warp & 3) * 32) << 16) + colA + e * 64;
       const int sw = (rtid >> 1) & 3;   // 64-byte swizzle of the TMA tile
@@ -695,9 +662,9 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
       for (int g = 0; g < total && ok; ++g) {
         const int slot_s = g % kNS;
         TR_BEGIN(t0);
-        const bool landed = mbar_wait_group(&S.sfull[slot_s], (g / kNS) & 1);
+        const bool landed = mbar_wait_group(&S.sfull[slot_s], (g / kNS) & 1, wait_ns);
         TR_ADD(1, t0);
-        if (!landed) { atomicExch(P.status, 8); ok = false; break; }
+        if (!landed) { GIVE_UP(8); ok = false; break; }
         const uint8_t* srow = S.sg + slot_s * kSlotBytes + tile_off;
         // two 16-byte pieces are in registers at a time; the slot may be refilled once all 256
         // readers have taken their last piece
@@ -716,11 +683,11 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
 #pragma unroll
           for (int q = 0; q < 4; ++q) expand_word_c(wd[q], cc, r + q * 8);
           TR_ADD(3, t2);
-          if (it >= 2 && P.dbg != 2) {
+          if (it >= 2 && !DBG_IS(2)) {
             TR_BEGIN(t1);
-            const bool got = mbar_wait_group(&S.aempty[e][slot], ((it >> 1) - 1) & 1);
+            const bool got = mbar_wait_group(&S.aempty[e][slot], ((it >> 1) - 1) & 1, wait_ns);
             TR_ADD(2, t1);
-            if (!got) { atomicExch(P.status, 4); ok = false; break; }
+            if (!got) { GIVE_UP(4); ok = false; break; }
             tc_fence_after();
           }
           // store and hand over at once: with only two stages per issuer every nanosecond of
@@ -728,7 +695,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
           tmem_st32(lane_base + slot * 32, r);
           tmem_wait_st();
           tc_fence_before();
-          if (P.dbg != 2) mbar_arrive(&S.afull[e][slot]);
+          if (!DBG_IS(2)) mbar_arrive(&S.afull[e][slot]);
         }
       }
       TR_ADD(0, t_prod);
@@ -736,7 +703,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
   } else if (warp >= kWarpEpi) {
     // ---- epilogue warps: y[m] += sum_r U_j[m,r] (T[m,r] / s_r - K_r) per block segment; T = sum
     //      of the hi and lo pieces (RT == 1: of both issuers' accumulators) ------------------
-    if (P.dbg == 0) {
+    if (!DBG_IS(1) && !DBG_IS(2)) {
     asm volatile("griddepcontrol.wait;" ::: "memory");   // constants below come from the Z' kernel
     const int quarter = warp & 3;                     // tensor-memory lanes this warp may read
     const int rtid = quarter * 32 + lane;
@@ -783,14 +750,14 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
       }
       TR_BEGIN(t0);
       if (RT == 1) {
-        const bool both = mbar_wait_warp_relaxed(&S.dfull[0][b], (bs / kND) & 1) && mbar_wait_warp_relaxed(&S.dfull[1][b], (bs / kND) & 1);
-        if (!both) { if (lane == 0) atomicExch(P.status, 5); ok = false; break; }
+        const bool both = mbar_wait_warp(&S.dfull[0][b], (bs / kND) & 1, wait_ns) && mbar_wait_warp(&S.dfull[1][b], (bs / kND) & 1, wait_ns);
+        if (!both) { if (lane == 0) GIVE_UP(5); ok = false; break; }
       }
       TR_ADD(9, t0);
 #pragma unroll
       for (int t = 0; t < RT; ++t) {
         if (RT == 2) {
-          if (!mbar_wait_warp_relaxed(&S.dfull[t][b], (bs / kND) & 1)) { if (lane == 0) atomicExch(P.status, 5); ok = false; break; }
+          if (!mbar_wait_warp(&S.dfull[t][b], (bs / kND) & 1, wait_ns)) { if (lane == 0) GIVE_UP(5); ok = false; break; }
         }
         tc_fence_after();
         const uint32_t* uw = reinterpret_cast<const uint32_t*>(&uq[t][0]);
@@ -843,7 +810,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
               if (m < M) {
                 float v = yacc[t][r];
                 if (w.bias) v += __half2float(reinterpret_cast<const __half*>(w.bias)[m]);
-                P.y[wk.wi][(int64_t)r * P.y_stride[wk.wi] + m] = __float2half_rn(v);
+                store_y(P, wk.wi, r, m, v);
               }
             } else {
               part[r * kRows + t * kTileRows + rtid] = yacc[t][r];
@@ -866,27 +833,60 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
       wk.advance(P, kRows, len);
     }
     TR_ADD(10, t_epi);
-    if (!ok) {
-      // a wait gave up: mark what this CTA would have written (NaN), nothing is reduced from it
-      S.n_pending = 0;
-    }
     }
   }
 
   // ---- tear-down: tensor memory is released only after every role is done ---------------
   tc_fence_before();
   __syncthreads();
+#ifdef BSB_TRACE
   if (warp == 0) TR_ADD(12, t_cta);
   if (P.trace) {
-#ifdef BSB_TRACE
     if (tid == 0) S.trace[15] = global_ns();
-#endif
     __syncthreads();
     if (tid < 16) P.trace[(int64_t)blockIdx.x * 16 + tid] = S.trace[tid];
   }
+#endif
   if (warp == kWarpLoad) {
     __syncwarp();
     tmem_dealloc(tbase, kTmemCols);
+  }
+  // ---- a wait of this CTA gave up: everything the CTA was to produce becomes NaN (outputs it owns alone directly,
+  //      shared row groups through its partial sums), so a timed-out call can never pass for a result ----
+  if (S.failed) {
+    const float nan = __int_as_float(0x7FC00000);
+    int g = 0, n_pend = 0;
+    bool first_seg = true;
+    while (g < total) {
+      Walk wk;
+      wk.init(P, step0 + g, kRows);
+      const int rem = (wk.NB - wk.js) * NCH - wk.ci;   // steps left in this row group
+      const int len = min(rem, total - g);
+      const bool direct = (wk.js == 0 && wk.ci == 0) && len == rem;
+      const bsb_weight& w = P.w[wk.wi];
+      float* part = P.partials + ((int64_t)blockIdx.x * 2 + (first_seg ? 0 : 1)) * (R * kRows);
+      if (tid < kRows) {
+        const int m = wk.rg * kRows + tid;
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          if (!direct) part[r * kRows + tid] = nan;
+          else if (m < w.out_features) store_y(P, wk.wi, r, m, nan);
+        }
+      }
+      if (!direct) {
+        if (tid == 0) {
+          S.pending[n_pend][0] = wk.wi;
+          S.pending[n_pend][1] = wk.rg;
+        }
+        ++n_pend;
+      }
+      first_seg = false;
+      g += len;
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) S.n_pending = n_pend;
+    __syncthreads();
   }
   // ---- shared row groups: the last CTA to deliver adds the partial sums in CTA order ------
   const int n_pending = S.n_pending;
@@ -917,7 +917,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
           sum += __ldcg(P.partials + (((int64_t)c * 2 + slot) * R + r) * kRows + tid);
         }
         if (w.bias) sum += __half2float(reinterpret_cast<const __half*>(w.bias)[m]);
-        P.y[wi][(int64_t)r * P.y_stride[wi] + m] = __float2half_rn(sum);
+        store_y(P, wi, r, m, sum);
       }
     }
   }
@@ -929,19 +929,20 @@ struct TcPlan {
   int total_blocks, total_items;
   int row_tiles;                    // RT: 128-row tiles per CTA (1 or 2)
   int64_t absmax_off[kMaxGroup];
-  int64_t status_off;
 };
 
-static int g_force_rt = 0;   // 0 = choose, 1 / 2 = forced (tuning)
-static int g_target_ctas = 0;   // 0 = two per multiprocessor, else this many (tuning)
 constexpr int kMinStepsPair = 4;
+#ifdef BSB_TUNING
+static int g_force_rt = 0;      // 0 = choose, 1 / 2 = forced
+static int g_target_ctas = 0;   // 0 = two per multiprocessor, else this many
 constexpr int kMinStepsUneven = 4;      // steps per CTA from which the two waves get different shares
 // steps of a first-wave CTA per 100 of a second-wave one.  140 makes an isolated launch 5-8 % faster (the two CTAs of a
 // multiprocessor then finish together) but a decode step 6 % SLOWER: with kernels queued back to back the first 148 CTAs
-// are not placed one per multiprocessor, and two long CTAs can share one.  Equal shares (100) are the default.
+// are not placed one per multiprocessor, and two long CTAs can share one.  Equal shares (100) are the product's choice.
 static int g_older_share_pct = 100;
+#endif
 
-// R = input rows per pass (1 or 2).  The status word sits at offset 0 of the workspace whatever the plan.
+// R = input rows per pass (1 or 2).
 void make_tc_plan(const bsb_weight* ws, int n, int R, TcPlan& pl) {
   TcParams& P = pl.P;
   memset(&P, 0, sizeof(P));
@@ -950,7 +951,11 @@ void make_tc_plan(const bsb_weight* ws, int n, int R, TcPlan& pl) {
   const int N = ws[0].in_features;
   P.n_chunks = (int)ceil_div64(N, kChunkCols);
   // CTAs wanted: two per multiprocessor (both stay resident and share its tensor pipe)
+#ifdef BSB_TUNING
   const int target = g_target_ctas > 0 ? g_target_ctas : sm_count() * 2;
+#else
+  const int target = sm_count() * 2;
+#endif
   int64_t steps1 = 0, steps2 = 0;
   for (int i = 0; i < n; ++i) {
     steps1 += ceil_div64(ws[i].out_features, kTileRows) * ws[i].blocks * P.n_chunks;
@@ -958,7 +963,9 @@ void make_tc_plan(const bsb_weight* ws, int n, int R, TcPlan& pl) {
   }
   // two row tiles per CTA halve the Z' traffic; taken when every CTA still gets a few steps
   int RT = (steps2 >= (int64_t)target * kMinStepsPair) ? 2 : 1;
+#ifdef BSB_TUNING
   if (g_force_rt) RT = g_force_rt;
+#endif
   pl.row_tiles = RT;
   const int64_t steps = RT == 2 ? steps2 : steps1;
   int L = (int)ceil_div64(steps, target);
@@ -967,6 +974,7 @@ void make_tc_plan(const bsb_weight* ws, int n, int R, TcPlan& pl) {
   P.n_first = 0;
   P.steps_first = L;
   int grid = (int)ceil_div64(steps, L);
+#ifdef BSB_TUNING
   const int sms = sm_count();
   if (g_older_share_pct > 100 && target == 2 * sms && steps >= (int64_t)target * kMinStepsUneven) {
     // two waves of one CTA per multiprocessor: the second wave's share is 1 / (1 + older share)
@@ -981,6 +989,7 @@ void make_tc_plan(const bsb_weight* ws, int n, int R, TcPlan& pl) {
       grid = sms + (rest > 0 ? (int)ceil_div64(rest, L2) : 0);
     }
   }
+#endif
   int segs = 0, blks = 0;
   int64_t st = 0;
   for (int i = 0; i < n; ++i) {
@@ -1001,8 +1010,7 @@ void make_tc_plan(const bsb_weight* ws, int n, int R, TcPlan& pl) {
   const int64_t part_floats = (int64_t)grid * 2 * R * RT * kTileRows;
   pl.total_blocks = blks;
   pl.total_items = items;
-  pl.status_off = 0;
-  int64_t off = 256;
+  int64_t off = 0;
   const int64_t z_off = off;
   off = align_up64(off + (int64_t)blks * P.n_chunks * kChunkBytes * R, 256);
   const int64_t k_off = off;
@@ -1066,9 +1074,18 @@ static int make_sign_map(const bsb_weight& w, CUtensorMap* map) {
   return BSB_OK;
 }
 
+int launch_vt_absmax(const bsb_weight& w, float* out, cudaStream_t s) {
+  BSB_CHECK_ARG(w.k == 16, "vt_absmax: only k == 16");
+  if (w.blocks == 0) return BSB_OK;
+  vt_absmax_kernel<<<dim3(16, w.blocks), 256, 0, s>>>(w, out);
+  return check_launch("vt_absmax_kernel");
+}
+
+static unsigned long long g_wait_ns = kDefaultWaitNs;
+void gemv_tc5_set_wait_limit_ns(unsigned long long ns) { g_wait_ns = ns; }
+#ifdef BSB_TUNING
 static unsigned long long* g_trace = nullptr;
 static int g_dbg = 0;
-void gemv_tc5_set_pdl(int on) { g_pdl_enabled = on; }
 void gemv_tc5_set_dbg(int m) {
   if (m >= 200 && m <= 202) g_force_rt = m - 200;   // row tiles per CTA: 200 = choose, 201 / 202 = forced
   else if (m >= 1000 && m < 2000) g_target_ctas = m - 1000;   // grid size wanted (1000 = default)
@@ -1076,9 +1093,10 @@ void gemv_tc5_set_dbg(int m) {
   else g_dbg = m;
 }
 void gemv_tc5_set_trace(unsigned long long* p) { g_trace = p; }
+#endif
 
 bool gemv_tc5_supported(const bsb_weight& w) {
-  return w.k == 16 && w.blocks >= 1 && w.in_features % 128 == 0 && w.out_features >= 1 &&
+  return w.k == 16 && w.blocks >= 1 && w.in_features >= 128 && w.in_features % 128 == 0 && w.out_features >= 1 &&
          ((uintptr_t)w.qweight % 16 == 0) && (w.q_block_stride % 16 == 0) &&
          ((uintptr_t)w.vt % 16 == 0) && (w.vt_block_stride % 8 == 0) &&
          ((uintptr_t)w.u % 16 == 0) && (w.u_block_stride % 8 == 0);
@@ -1091,24 +1109,11 @@ int64_t gemv_tc5_workspace_bytes(const bsb_weight* ws, int n_weights, int rows_p
   return pl.bytes;
 }
 
-int64_t gemv_tc5_status_offset(const bsb_weight* ws, int n_weights) {
-  (void)ws;
-  return (n_weights < 1 || n_weights > kMaxGroup) ? -1 : 0;
-}
-
 // rows = 1 or 2 input rows in one pass: x rows x_stride apart, row r of weight i goes to ys[i] + r * y_strides[i]
 // (y_strides may be nullptr when rows == 1)
 int launch_gemv_tc5(const bsb_weight* ws, int n_weights, const __half* x, int64_t x_stride, int rows, __half* const* ys,
-                    const int64_t* y_strides, void* workspace, int64_t workspace_bytes, cudaStream_t s,
-                    const bsb_input_transform* tf) {
+                    const int64_t* y_strides, void* workspace, int64_t workspace_bytes, cudaStream_t s, bool out_f32) {
   BSB_CHECK_ARG(n_weights >= 1 && n_weights <= kMaxGroup, "gemv: 1..%d weights per group", kMaxGroup);
-  if (tf != nullptr && tf->mode != BSB_INPUT_PLAIN) {
-    BSB_CHECK_ARG(tf->mode == BSB_INPUT_ADD_RMSNORM || tf->mode == BSB_INPUT_SILU_MUL, "gemv: unknown input transform %d", tf->mode);
-    BSB_CHECK_ARG(tf->mode != BSB_INPUT_SILU_MUL || tf->x2 != nullptr, "gemv: silu*mul needs the second operand");
-    BSB_CHECK_ARG(tf->mode != BSB_INPUT_ADD_RMSNORM || tf->norm_weight != nullptr, "gemv: rmsnorm needs its weight");
-    BSB_CHECK_ARG(((uintptr_t)tf->x2 | (uintptr_t)tf->norm_weight | (uintptr_t)tf->h_out) % 16 == 0 && tf->x2_stride % 8 == 0 &&
-                  tf->h_out_stride % 8 == 0, "gemv: transform operands must be 16-byte aligned");
-  }
   BSB_CHECK_ARG(rows == 1 || (rows == 2 && y_strides != nullptr && x_stride % 8 == 0), "gemv: 1 or 2 rows per pass (16-byte aligned rows)");
   for (int i = 0; i < n_weights; ++i) {
     BSB_CHECK_ARG(gemv_tc5_supported(ws[i]), "gemv: weight %d has an unsupported shape/alignment", i);
@@ -1138,19 +1143,15 @@ int launch_gemv_tc5(const bsb_weight* ws, int n_weights, const __half* x, int64_
   P.inv_scale = (float*)(base + (int64_t)(uintptr_t)P.inv_scale);
   P.counters = (int*)(base + (int64_t)(uintptr_t)P.counters);
   P.partials = (float*)(base + (int64_t)(uintptr_t)P.partials);
-  P.status = (int*)(base + pl.status_off);
+  P.status = device_status_word();
+  if (P.status == nullptr) return BSB_ECUDA;
+  P.wait_ns = g_wait_ns;
+#ifdef BSB_TUNING
   P.trace = g_trace;
   P.dbg = g_dbg;
+#endif
   P.x_stride = x_stride;
-  if (tf != nullptr) {
-    P.x_mode = tf->mode;
-    P.x2 = reinterpret_cast<const __half*>(tf->x2);
-    P.x2_stride = tf->x2_stride;
-    P.norm_w = reinterpret_cast<const __half*>(tf->norm_weight);
-    P.eps = tf->eps;
-    P.h_out = reinterpret_cast<__half*>(tf->h_out);
-    P.h_out_stride = tf->h_out_stride;
-  }
+  P.out_f32 = out_f32 ? 1 : 0;
   for (int i = 0; i < n_weights; ++i) {
     P.y[i] = ys[i];
     P.y_stride[i] = y_strides ? y_strides[i] : 0;
@@ -1165,9 +1166,7 @@ int launch_gemv_tc5(const bsb_weight* ws, int n_weights, const __half* x, int64_
   }
   {
     const dim3 zgrid(P.n_chunks, pl.total_blocks, rows);
-    cudaError_t le = P.x_mode == BSB_INPUT_ADD_RMSNORM ? launch_pdl(zprep_tc5_kernel<1>, zgrid, dim3(256), 0, s, P, x)
-                   : P.x_mode == BSB_INPUT_SILU_MUL  ? launch_pdl(zprep_tc5_kernel<2>, zgrid, dim3(256), 0, s, P, x)
-                                                      : launch_pdl(zprep_tc5_kernel<0>, zgrid, dim3(256), 0, s, P, x);
+    cudaError_t le = launch_pdl(zprep_tc5_kernel, zgrid, dim3(256), 0, s, P, x);
     if (le != cudaSuccess) {
       set_error("launch of zprep_tc5_kernel failed: %s", cudaGetErrorString(le));
       return BSB_ECUDA;
@@ -1214,6 +1213,7 @@ extern "C" int bsb_linear_forward_noalloc(const bsb_weight* w, const uint16_t* x
                                           uint16_t* y, int64_t y_stride, void* stream) {
   using namespace bsb;
   BSB_CHECK_ARG(w != nullptr && x != nullptr && y != nullptr, "NULL argument");
+  if (int rc = check_weight(w)) return rc;   // same dimension / block-stride checks as every other forward entry
   BSB_CHECK_ARG(rows >= 1, "at least one input row is needed");
   BSB_CHECK_ARG(w->blocks >= 1 && gemv_tc5_supported(*w),
                 "noalloc forward: needs k == 16, in_features %% 128 == 0, 16-byte aligned tensors, >= 1 active block");

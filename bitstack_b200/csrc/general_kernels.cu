@@ -21,7 +21,8 @@ constexpr int kRankChunk = 16;
 // one warp per (x row, output feature)
 __global__ void __launch_bounds__(256) general_forward_kernel(bsb_weight w, const __half* __restrict__ x,
                                                               int64_t rows, int64_t x_stride,
-                                                              __half* __restrict__ y, int64_t y_stride) {
+                                                              __half* __restrict__ y, float* __restrict__ y32,
+                                                              int64_t y_stride) {
   const int lane = threadIdx.x & 31;
   const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int64_t total = rows * (int64_t)w.out_features;
@@ -60,7 +61,8 @@ __global__ void __launch_bounds__(256) general_forward_kernel(bsb_weight w, cons
   }
   if (lane == 0) {
     if (w.bias) acc += __half2float(reinterpret_cast<const __half*>(w.bias)[m]);
-    y[row * y_stride + m] = __float2half_rn(acc);
+    if (y32) y32[row * y_stride + m] = acc;   // partial-sum output of a tensor-parallel shard: no rounding
+    else y[row * y_stride + m] = __float2half_rn(acc);
   }
 }
 
@@ -89,12 +91,12 @@ __global__ void __launch_bounds__(256) general_reconstruct_kernel(bsb_weight w, 
 }  // namespace
 
 int launch_general_forward(const bsb_weight& w, const __half* x, int64_t rows, int64_t x_stride,
-                           __half* y, int64_t y_stride, cudaStream_t s) {
+                           __half* y, float* y32, int64_t y_stride, cudaStream_t s) {
   const int64_t warps = rows * (int64_t)w.out_features;
   if (warps == 0) return BSB_OK;
   const int64_t blocks = ceil_div64(warps, 8);
   BSB_CHECK_ARG(blocks < (1ll << 31), "general forward: too many output elements (%lld)", (long long)warps);
-  general_forward_kernel<<<(unsigned)blocks, 256, 0, s>>>(w, x, rows, x_stride, y, y_stride);
+  general_forward_kernel<<<(unsigned)blocks, 256, 0, s>>>(w, x, rows, x_stride, y, y32, y_stride);
   return check_launch("general_forward_kernel");
 }
 

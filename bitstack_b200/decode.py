@@ -9,9 +9,12 @@ named like the reference names them (`layer.{i}.self_attn.q_proj`, ...,
 bitstack/utils/decompose.py:14).  The glue ops are plain torch calls; one decode
 step can be captured in a CUDA graph (device-side position and token feedback).
 
-With `world_size > 1` the projections are sharded for tensor parallelism: output
-rows for q/k/v/gate/up, input columns for o/down, one all-reduce after each of the
-two column-sharded projections of a layer.
+With `world_size > 1` the projections are sharded for tensor parallelism
+(`bitstack_b200.sharding`): every rank draws the SAME full weight of a projection from the
+seed and keeps its output rows (q/k/v/gate/up) or input columns (o/down), so the sharded
+model computes what the single-device model computes.  The two column-sharded projections
+of a layer deliver fp32 partial sums that are all-reduced and rounded to fp16 once; the LM
+head is sharded by vocabulary (local maximum per rank, one small all-gather).
 """
 from __future__ import annotations
 
@@ -23,7 +26,8 @@ import torch
 import torch.nn.functional as F
 
 from . import glue
-from .linear import BitStackLinear, forward_grouped, forward_grouped_transformed, transform_supported
+from . import _lib, sharding
+from .linear import BitStackLinear, forward_grouped
 
 PROJ_NAMES = ("self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj", "self_attn.o_proj",
               "mlp.gate_proj", "mlp.up_proj", "mlp.down_proj")
@@ -87,15 +91,26 @@ def packed_bytes(shape: LlamaShape, counts: Dict[str, int]) -> int:
     return sum(c * block_bytes(*shapes[n.split(".", 2)[2]]) for n, c in counts.items())
 
 
-def _random_bitstack(out_f, in_f, blocks, device, gen, name, fused_level):
+COLUMN_SHARDED = ("self_attn.o_proj", "mlp.down_proj")   # input columns split over ranks: partial-sum outputs
+
+
+def _random_bitstack(out_f, in_f, blocks, device, gen, name, fused_level, shard=None, rank=0, world=1):
     """Random-init module with the storage format of a loaded, stacked checkpoint:
-    Bernoulli(0.5) packed signs, |N(0, 0.05)| fp16 factors."""
+    Bernoulli(0.5) packed signs, |N(0, 0.05)| fp16 factors.  `shard` ("rows" / "cols") with world > 1: the full
+    weight is drawn (identically on every rank) and this rank's shard of it is kept."""
+    q = torch.randint(0, 256, (blocks, out_f * in_f // 8), dtype=torch.uint8, device=device, generator=gen)
+    u = (torch.randn(blocks, out_f, 16, device=device, generator=gen) * 0.05).abs().half()
+    vt = (torch.randn(blocks, 16, in_f, device=device, generator=gen) * 0.05).abs().half()
+    if world > 1 and shard == "rows":
+        q, u, vt = sharding.shard_rows(q, u, vt, out_f, in_f, rank, world)
+        out_f //= world
+    elif world > 1 and shard == "cols":
+        q, u, vt = sharding.shard_cols(q, u, vt, out_f, in_f, rank, world)
+        in_f //= world
     m = BitStackLinear(w_bit=0, in_features=in_f, out_features=out_f, k=16, bias=False, no_avd=False,
                        dev=device, fused_level=fused_level)
     m.name = name
-    m.qweight = torch.randint(0, 256, (blocks, out_f * in_f // 8), dtype=torch.uint8, device=device, generator=gen)
-    m.u = (torch.randn(blocks, out_f, 16, device=device, generator=gen) * 0.05).abs().half()
-    m.vt = (torch.randn(blocks, 16, in_f, device=device, generator=gen) * 0.05).abs().half()
+    m.qweight, m.u, m.vt = q, u, vt
     m.w_bit = blocks
     m._stacked_blocks = blocks
     return m
@@ -108,17 +123,16 @@ class BitStackLlamaDecoder:
                  batch=1, fused_level=6, rank=0, world_size=1, group=None, fused_glue=True):
         self.shape, self.device, self.max_len, self.batch = shape, torch.device(device), max_len, batch
         self.fused_glue = fused_glue
-        # Applying the norms / SiLU*up inside the projection calls (forward_grouped_transformed) saves their launches but
-        # lengthens the operand-preparation kernel, which every call waits for: measured 223 tokens/s (norms fused) and
-        # 207 (norms and SiLU*up fused) against 236 with the stand-alone kernels on the 8B workload.  Off by default.
-        self.fuse_norm = False
-        self.fuse_silu = False
         self.rank, self.world, self.group = rank, world_size, group
         s = shape
-        assert s.n_kv_heads % world_size == 0 and s.intermediate % (128 * world_size) == 0
+        assert s.n_kv_heads % world_size == 0 and s.intermediate % (128 * world_size) == 0 and s.vocab % world_size == 0
         gen = torch.Generator(device=self.device).manual_seed(seed)  # same seed on every rank: replicated tensors agree
         self.embed = (torch.randn(s.vocab, s.hidden, device=self.device, generator=gen) * 0.02).half()
-        self.lm_head = (torch.randn(s.vocab, s.hidden, device=self.device, generator=gen) * 0.02).half()
+        lm_head = (torch.randn(s.vocab, s.hidden, device=self.device, generator=gen) * 0.02).half()
+        # the head is sharded by vocabulary: rank p scores tokens [p V/P, (p+1) V/P)
+        self.vocab_local = s.vocab // world_size
+        self.lm_head = lm_head[rank * self.vocab_local:(rank + 1) * self.vocab_local].contiguous() if world_size > 1 else lm_head
+        del lm_head
         self.final_norm = torch.ones(s.hidden, dtype=torch.float16, device=self.device)
         self.layers = []
         shapes = s.proj_shapes()
@@ -128,13 +142,11 @@ class BitStackLlamaDecoder:
                    "post_norm": torch.ones(s.hidden, dtype=torch.float16, device=self.device)}
             for p in PROJ_NAMES:
                 out_f, in_f = shapes[p]
-                if p in ("self_attn.o_proj", "mlp.down_proj"):
-                    in_f //= W      # input-column shard: partial sums, all-reduced
-                else:
-                    out_f //= W     # output-row shard
-                lgen = torch.Generator(device=self.device).manual_seed(seed * 1000003 + i * 16 + PROJ_NAMES.index(p) + 7919 * rank)
+                # one seed per projection, the same on every rank: all ranks cut their shard out of the same weight
+                lgen = torch.Generator(device=self.device).manual_seed(seed * 1000003 + i * 16 + PROJ_NAMES.index(p))
                 lay[p] = _random_bitstack(out_f, in_f, block_counts[f"layer.{i}.{p}"], self.device, lgen,
-                                          f"layer.{i}.{p}", fused_level)
+                                          f"layer.{i}.{p}", fused_level,
+                                          shard="cols" if p in COLUMN_SHARDED else "rows", rank=rank, world=W)
             self.layers.append(lay)
         hd = s.head_dim
         self.kv_local = s.n_kv_heads // W
@@ -161,10 +173,25 @@ class BitStackLlamaDecoder:
         rot = torch.cat([-x[..., half:], x[..., :half]], dim=-1)
         return x * cos + rot * sin
 
-    def _allreduce(self, t):
-        if self.world > 1:
-            torch.distributed.all_reduce(t, group=self.group)
-        return t
+    def _row_parallel(self, mod, x):
+        """A column-sharded projection (o / down): on one device the plain forward; tensor parallel, fp32 partial sums
+        of this rank's input columns, summed over the ranks and rounded to fp16 once."""
+        if self.world == 1:
+            return mod(x)
+        part = mod.forward_partial(x)
+        torch.distributed.all_reduce(part, group=self.group)
+        return part.half()
+
+    def _next_token(self, logits):
+        """Greedy token from this rank's vocabulary shard of the logits [B, V/P]: local maximum, one all-gather of
+        (value, index) pairs, first index of the global maximum (as argmax over the whole vocabulary gives)."""
+        val, idx = logits.float().max(dim=-1)
+        idx = idx + self.rank * self.vocab_local
+        pair = torch.stack([val, idx.float()], dim=-1)                     # [B, 2]; token ids < 2^24 are exact in fp32
+        allp = torch.empty(self.world, *pair.shape, dtype=pair.dtype, device=pair.device)
+        torch.distributed.all_gather_into_tensor(allp, pair, group=self.group)
+        best = allp[..., 0].max(dim=0)                                      # max returns the first (lowest-rank) maximum
+        return allp[..., 1].gather(0, best.indices.unsqueeze(0)).squeeze(0).long()
 
     def _layer(self, i, h, positions, pos_index, mask):
         """h: [B, T, hidden]; positions: [T] long tensor of absolute positions."""
@@ -182,10 +209,10 @@ class BitStackLlamaDecoder:
         self.v_cache[i].index_copy_(2, pos_index, v)
         att = F.scaled_dot_product_attention(q, self.k_cache[i], self.v_cache[i], attn_mask=mask, enable_gqa=True)
         att = att.transpose(1, 2).reshape(B, T, self.q_local * hd)
-        h = h + self._allreduce(lay["self_attn.o_proj"](att))
+        h = h + self._row_parallel(lay["self_attn.o_proj"], att)
         x = F.rms_norm(h, (s.hidden,), lay["post_norm"], s.rms_eps)
         g, u = forward_grouped([lay["mlp.gate_proj"], lay["mlp.up_proj"]], x)
-        h = h + self._allreduce(lay["mlp.down_proj"](F.silu(g) * u))
+        h = h + self._row_parallel(lay["mlp.down_proj"], F.silu(g) * u)
         return h
 
     def _forward(self, token_ids, positions):
@@ -206,20 +233,10 @@ class BitStackLlamaDecoder:
         h = self.embed.index_select(0, self.tokens).contiguous()            # [B, hidden], residual stream
         fused_att = hd in (64, 128) and self.max_len <= 8192
         mask = None if fused_att else (self.arange <= self.pos).view(1, 1, 1, self.max_len)
-        # optionally (fuse_norm) the norms are applied while the projections' operand is prepared: no launch of their
-        # own; the residual stream then ping-pongs between two buffers
-        lay0 = self.layers[0]
-        fuse_in = (self.fuse_norm and transform_supported([lay0["mlp.down_proj"]], B) and
-                   transform_supported([lay0["self_attn.q_proj"], lay0["self_attn.k_proj"], lay0["self_attn.v_proj"]], B))
-        h_alt = torch.empty_like(h) if fuse_in else None
         delta = None                                                         # output of the previous MLP, not yet added to h
         for i, lay in enumerate(self.layers):
             qkv = [lay["self_attn.q_proj"], lay["self_attn.k_proj"], lay["self_attn.v_proj"]]
-            if fuse_in:
-                q, k, v = forward_grouped_transformed(qkv, h, add=delta, norm_weight=lay["in_norm"], eps=s.rms_eps, h_out=h_alt)
-                h, h_alt = h_alt, h
-            else:
-                q, k, v = forward_grouped(qkv, glue.add_rmsnorm(h, delta, lay["in_norm"], s.rms_eps))
+            q, k, v = forward_grouped(qkv, glue.add_rmsnorm(h, delta, lay["in_norm"], s.rms_eps))
             if fused_att:
                 att = glue.decode_attention(q, k, v, self.cos, self.sin, self.pos, self.k_cache[i], self.v_cache[i],
                                             self.q_local, self.kv_local, hd)
@@ -228,18 +245,9 @@ class BitStackLlamaDecoder:
                                 self.q_local, self.kv_local, hd)
                 att = F.scaled_dot_product_attention(q.view(B, self.q_local, 1, hd), self.k_cache[i], self.v_cache[i],
                                                      attn_mask=mask, enable_gqa=True).reshape(B, self.q_local * hd)
-            o = self._allreduce(lay["self_attn.o_proj"](att))
-            gu = [lay["mlp.gate_proj"], lay["mlp.up_proj"]]
-            if fuse_in:
-                g, u = forward_grouped_transformed(gu, h, add=o, norm_weight=lay["post_norm"], eps=s.rms_eps, h_out=h_alt)
-                h, h_alt = h_alt, h
-                if self.fuse_silu:
-                    delta = self._allreduce(forward_grouped_transformed([lay["mlp.down_proj"]], g, silu_mul=u)[0])
-                else:
-                    delta = self._allreduce(lay["mlp.down_proj"](glue.silu_mul(g, u)))
-            else:
-                g, u = forward_grouped(gu, glue.add_rmsnorm(h, o, lay["post_norm"], s.rms_eps))
-                delta = self._allreduce(lay["mlp.down_proj"](glue.silu_mul(g, u)))
+            o = self._row_parallel(lay["self_attn.o_proj"], att)
+            g, u = forward_grouped([lay["mlp.gate_proj"], lay["mlp.up_proj"]], glue.add_rmsnorm(h, o, lay["post_norm"], s.rms_eps))
+            delta = self._row_parallel(lay["mlp.down_proj"], glue.silu_mul(g, u))
         x = glue.add_rmsnorm(h, delta, self.final_norm, s.rms_eps)
         return x @ self.lm_head.t()
 
@@ -250,7 +258,7 @@ class BitStackLlamaDecoder:
         B, T = prompt_ids.shape
         positions = torch.arange(T, device=self.device)
         logits = self._forward(prompt_ids, positions)
-        self.tokens.copy_(logits.argmax(-1))
+        self.tokens.copy_(logits.argmax(-1) if self.world == 1 else self._next_token(logits))
         self.pos.fill_(T)
         return self.tokens.clone()
 
@@ -259,11 +267,11 @@ class BitStackLlamaDecoder:
         """One greedy token for every sequence; position and token feedback stay on the device."""
         if self.fused_glue:
             logits = self._decode_fused()
-            if logits.dtype == torch.float16 and logits.dim() == 2 and logits.stride(1) == 1:
+            if self.world == 1 and logits.dtype == torch.float16 and logits.dim() == 2 and logits.stride(1) == 1:
                 return glue.greedy_step(logits, self.tokens, self.pos)
         else:
             logits = self._forward(self.tokens.view(-1, 1), self.pos)
-        self.tokens.copy_(logits.argmax(-1))
+        self.tokens.copy_(logits.argmax(-1) if self.world == 1 else self._next_token(logits))
         self.pos.add_(1)
         return self.tokens
 
@@ -304,4 +312,6 @@ class BitStackLlamaDecoder:
             toks = self.step()
             out[t].copy_(toks, non_blocking=True)
             torch.cuda.current_stream(self.device).synchronize()
+        with torch.cuda.device(self.device):
+            _lib.check_device_status()   # a kernel that gave up a wait would have produced NaN outputs: fail loudly
         return out[:steps].t().contiguous()

@@ -56,7 +56,7 @@ def main() -> None:
         raise SystemExit("layer_bench needs a CUDA device")
     dev = torch.device("cuda:0")
     lib = _lib.load()
-    lib.bsb_debug_set_mode(101 if a.pdl else 100)
+    lib.bsb_set_dependent_launch(1 if a.pdl else 0)
     mod = synthetic_projection(a.out, a.inp, a.blocks, a.level, dev)
     x = torch.randn(a.rows, a.inp, device=dev).half()
     flush = None if a.no_flush else torch.empty(512 << 20, dtype=torch.uint8, device=dev)

@@ -9,9 +9,12 @@ reference staged its Triton kernels -- and extra levels pin one kernel:
 
     0-5, 6  automatic choice (decode kernel, two rows per pass, for <= 6 rows; rebuild + tcgen05 GEMM above)
     7       shape-agnostic CUDA-core kernel
-    8       decode kernel, warp-level MMA generation, any row count
-    9       rebuild fp16 weight + dense MMA
-    10      decode kernel, tcgen05 generation (sign operand in tensor memory)
+    9       rebuild fp16 weight + tcgen05 GEMM
+    10      decode kernel (tcgen05, sign operand in tensor memory), any row count
+
+Differences from the reference's levels that a caller can observe: level 5 there takes 3-D inputs only and ignores
+the bias (bitstack/modules/BitStackLinear.py:150-157); here every level takes any leading shape and adds the bias.
+Level 4's fp16 atomics make the reference non-deterministic; here the same call is bit-identical run to run.
 
 There is no CPU path: inputs must be CUDA fp16 tensors.  `no_avd=True` (the
 reference's ablation without sign matrices) is not supported.
@@ -28,21 +31,35 @@ from .pack import pack_sign, unpack_sign
 
 _LEVEL_TO_ALGO = {0: _lib.ALGO_AUTO, 1: _lib.ALGO_AUTO, 2: _lib.ALGO_AUTO, 3: _lib.ALGO_AUTO,
                   4: _lib.ALGO_AUTO, 5: _lib.ALGO_AUTO, 6: _lib.ALGO_AUTO,
-                  7: _lib.ALGO_GENERAL, 8: _lib.ALGO_GEMV_MMA, 9: _lib.ALGO_REBUILD_GEMM,
-                  10: _lib.ALGO_GEMV_TC5}
+                  7: _lib.ALGO_GENERAL, 9: _lib.ALGO_REBUILD_GEMM, 10: _lib.ALGO_GEMV_TC5}
 
 # scratch memory per (device index, stream handle); grown on demand, never shrunk
 _workspaces: dict = {}
+# scratch tensors whose address a captured CUDA graph may hold: kept alive for the life of the process
+_pinned_workspaces: list = []
 
 
 def get_workspace(device: torch.device, nbytes: int) -> torch.Tensor:
-    """A cached uint8 scratch tensor of at least `nbytes` for the current stream of `device`."""
+    """A cached uint8 scratch tensor of at least `nbytes` for the current stream of `device`.
+
+    A scratch tensor handed out while its stream is being captured has its address baked into the graph.  It is
+    therefore never freed: when a later request on that stream needs more, a new tensor serves the new calls and the
+    old one stays allocated for the graph's replays.  Growing during a capture is refused (the allocation would land
+    in the graph's private pool): run the step once eagerly before capturing it."""
     key = (device.index, torch.cuda.current_stream(device).cuda_stream)
-    ws = _workspaces.get(key)
-    if ws is None or ws.numel() < nbytes:
-        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
-        _workspaces[key] = ws
-    return ws
+    ent = _workspaces.get(key)          # [tensor, seen_by_a_capture]
+    capturing = torch.cuda.is_current_stream_capturing()
+    if ent is None or ent[0].numel() < nbytes:
+        if capturing:
+            raise RuntimeError(f"the scratch buffer of this stream must grow to {nbytes} bytes during a graph capture; "
+                               "run the same calls once outside the capture first")
+        if ent is not None and ent[1]:
+            _pinned_workspaces.append(ent[0])
+        ent = [torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device), False]
+        _workspaces[key] = ent
+    if capturing:
+        ent[1] = True
+    return ent[0]
 
 
 class BitStackLinear(nn.Module):
@@ -59,6 +76,7 @@ class BitStackLinear(nn.Module):
         self.name = None
         self._stacked_blocks = 0   # number of blocks held in the stacked tensors
         self._vt_absmax = None
+        self._vt_key = None
         self._desc = None
         for i in range(self.w_bit):
             self.register_buffer(f"qweight_{i}", torch.zeros((out_features * in_features) // 8, dtype=torch.uint8, device=dev))
@@ -105,6 +123,12 @@ class BitStackLinear(nn.Module):
         if bias:
             qlinear.bias = linear.bias.detach().to(torch.float16)
         return qlinear
+
+    def _load_from_state_dict(self, *args, **kwargs):
+        # new buffer contents: everything derived from them is recomputed on the next forward
+        super()._load_from_state_dict(*args, **kwargs)
+        self._vt_absmax = None
+        self._desc = None
 
     # ---------------------------------------------------------------- block count
     def pop_one_bit(self):
@@ -183,7 +207,15 @@ class BitStackLinear(nn.Module):
             self._stacked_blocks = self.u.shape[0]
         if self.qweight.device != device:
             raise ValueError(f"input on {device} but weights on {self.qweight.device}")
-        if self._vt_absmax is None or self._vt_absmax.device != device:
+        # max |vt| sets the scale of the decode kernel's fp8 operand: it must follow the CONTENT of vt, so the cache is
+        # keyed on the tensor's version counter (bumped by every in-place write: copy_, load_state_dict, ...)
+        try:
+            version = self.vt._version
+        except RuntimeError:        # inference-mode tensors keep no version counter: recompute on every call
+            version = object()
+        vt_key = (self.vt.data_ptr(), version, self._stacked_blocks)
+        if self._vt_absmax is None or self._vt_absmax.device != device or self._vt_key != vt_key:
+            self._vt_key = vt_key
             self._desc = None
             self._vt_absmax = torch.empty(self._stacked_blocks, self.k, dtype=torch.float32, device=device)
             if self.k == 16 and self._stacked_blocks > 0:
@@ -212,7 +244,7 @@ class BitStackLinear(nn.Module):
         if self.w_bit < 0 or self.w_bit > self._stacked_blocks:
             raise ValueError(f"w_bit={self.w_bit} but only {self._stacked_blocks} blocks are loaded")
         key = (self.w_bit, self.qweight.data_ptr(), self.u.data_ptr(), self.vt.data_ptr(),
-               None if self.bias is None else self.bias.data_ptr())
+               None if self.bias is None else self.bias.data_ptr(), self._vt_absmax.data_ptr())
         if self._desc is None or self._desc[0] != key:
             self._desc = (key, self._make_desc(self.w_bit))
         return self._desc[1]
@@ -230,7 +262,13 @@ class BitStackLinear(nn.Module):
         return w
 
     @torch.no_grad()
-    def forward(self, x):
+    def forward_partial(self, x):
+        """Tensor-parallel variant of `forward`: the product as fp32 partial sums (no rounding to fp16), for a module
+        that holds an input-column shard of a projection; the caller all-reduces and rounds once."""
+        return self.forward(x, _partial=True)
+
+    @torch.no_grad()
+    def forward(self, x, _partial=False):
         if self.fused_level not in _LEVEL_TO_ALGO:
             raise ValueError(f"Invalid fused_level: {self.fused_level}")
         if not x.is_cuda:
@@ -244,16 +282,17 @@ class BitStackLinear(nn.Module):
             x2 = x2.contiguous()
         rows = x2.shape[0]
         d = self.weight_desc(x.device)
-        y = torch.empty(rows, self.out_features, dtype=torch.float16, device=x.device)
+        y = torch.empty(rows, self.out_features, dtype=torch.float32 if _partial else torch.float16, device=x.device)
         lib = _lib.load()
         with torch.cuda.device(x.device):
             need = lib.bsb_linear_workspace_bytes(C.byref(d), rows, algo)
             if need < 0:
                 raise ValueError("bsb_linear_workspace_bytes rejected the arguments: " + lib.bsb_last_error().decode())
             ws = get_workspace(x.device, need)
-            rc = lib.bsb_linear_forward(C.byref(d), x2.data_ptr(), rows, x2.stride(0) if rows > 1 else self.in_features,
-                                        y.data_ptr(), self.out_features, ws.data_ptr(), ws.numel(), algo,
-                                        torch.cuda.current_stream(x.device).cuda_stream)
+            fn = lib.bsb_linear_forward_partial if _partial else lib.bsb_linear_forward
+            rc = fn(C.byref(d), x2.data_ptr(), rows, x2.stride(0) if rows > 1 else self.in_features,
+                    y.data_ptr(), self.out_features, ws.data_ptr(), ws.numel(), algo,
+                    torch.cuda.current_stream(x.device).cuda_stream)
         _lib.check(rc, "bsb_linear_forward")
         return y.reshape(*x.shape[:-1], self.out_features)
 
@@ -283,57 +322,4 @@ def forward_grouped(modules, x, algo=_lib.ALGO_AUTO):
                                             yptrs, ystr, ws.data_ptr(), ws.numel(), algo,
                                             torch.cuda.current_stream(x.device).cuda_stream)
     _lib.check(rc, "bsb_linear_forward_grouped")
-    return [y.reshape(*x.shape[:-1], m.out_features) for y, m in zip(ys, modules)]
-
-
-def transform_supported(modules, rows: int) -> bool:
-    """Whether `forward_grouped_transformed` can take these modules and this many rows (decode path only)."""
-    return 1 <= rows <= 6 and 1 <= len(modules) <= 4 and all(
-        m.k == 16 and m.in_features % 128 == 0 and m.w_bit > 0 and m.in_features == modules[0].in_features for m in modules)
-
-
-def forward_grouped_transformed(modules, x, *, add=None, norm_weight=None, eps=1e-5, h_out=None, silu_mul=None):
-    """`forward_grouped` on a transformed input, without a separate launch for the transform:
-
-        norm_weight given:  the projections see rmsnorm(x + add) * norm_weight (add may be None); the fp16 sum
-                            x + add is written to `h_out` (same shape as x; must not alias x or add) if given
-        silu_mul given:     the projections see silu(x) * silu_mul
-
-    x: [rows, in_features] fp16 CUDA, rows <= 6 (see `transform_supported`).  Returns the list of outputs."""
-    assert (norm_weight is None) != (silu_mul is None), "exactly one of norm_weight / silu_mul"
-    x2 = x.reshape(-1, x.shape[-1])
-    assert x2.is_cuda and x2.dtype == torch.float16 and x2.stride(-1) == 1
-    rows, n = x2.shape[0], len(modules)
-    tf = _lib.BsbInputTransform()
-    other = add if norm_weight is not None else silu_mul
-    if other is not None:
-        other = other.reshape(rows, -1)
-        assert other.dtype == torch.float16 and other.shape == x2.shape and other.stride(-1) == 1
-        tf.x2, tf.x2_stride = other.data_ptr(), other.stride(0)
-    if norm_weight is not None:
-        assert norm_weight.dtype == torch.float16 and norm_weight.is_contiguous() and norm_weight.numel() == x2.shape[1]
-        tf.mode, tf.norm_weight, tf.eps = _lib.INPUT_ADD_RMSNORM, norm_weight.data_ptr(), float(eps)
-        if h_out is not None:
-            ho = h_out.reshape(rows, -1)
-            assert ho.dtype == torch.float16 and ho.shape == x2.shape and ho.stride(-1) == 1
-            assert ho.data_ptr() != x2.data_ptr() and (other is None or ho.data_ptr() != other.data_ptr())
-            tf.h_out, tf.h_out_stride = ho.data_ptr(), ho.stride(0)
-    else:
-        tf.mode = _lib.INPUT_SILU_MUL
-    descs = (_lib.BsbWeight * n)()
-    for i, m in enumerate(modules):
-        C.memmove(C.byref(descs[i]), C.byref(m.weight_desc(x.device)), C.sizeof(_lib.BsbWeight))
-    ys = [torch.empty(rows, m.out_features, dtype=torch.float16, device=x.device) for m in modules]
-    yptrs = (C.c_void_p * n)(*[y.data_ptr() for y in ys])
-    ystr = (C.c_int64 * n)(*[m.out_features for m in modules])
-    lib = _lib.load()
-    with torch.cuda.device(x.device):
-        need = lib.bsb_linear_grouped_workspace_bytes(descs, n, rows, _lib.ALGO_AUTO)
-        if need < 0:
-            raise ValueError("grouped workspace query rejected the arguments: " + lib.bsb_last_error().decode())
-        ws = get_workspace(x.device, need)
-        rc = lib.bsb_linear_forward_grouped_tf(descs, n, x2.data_ptr(), rows, x2.stride(0) if rows > 1 else x2.shape[-1],
-                                               C.byref(tf), yptrs, ystr, ws.data_ptr(), ws.numel(),
-                                               torch.cuda.current_stream(x.device).cuda_stream)
-    _lib.check(rc, "bsb_linear_forward_grouped_tf")
     return [y.reshape(*x.shape[:-1], m.out_features) for y, m in zip(ys, modules)]

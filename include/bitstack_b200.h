@@ -34,6 +34,7 @@ extern "C" {
 #define BSB_ECUDA (-2)     /* a CUDA runtime call or launch failed */
 #define BSB_EWORKSPACE (-3)/* scratch buffer missing or too small */
 #define BSB_ELIMIT (-4)    /* size beyond a documented maximum */
+#define BSB_ETIMEOUT (-5)  /* a time-bounded wait inside a kernel gave up; that call's outputs are NaN */
 
 /* One stacked BitStack weight.  Strides are between consecutive blocks:
  * q_block_stride in bytes, u/vt_block_stride in fp16 elements.  `blocks` is the
@@ -59,9 +60,8 @@ typedef struct bsb_weight {
 enum {
   BSB_ALGO_AUTO = 0,
   BSB_ALGO_GENERAL = 1,   /* any shape, CUDA cores, fp32 */
-  BSB_ALGO_GEMV_MMA = 2,  /* decode: packed signs streamed into fp8 tensor-core MMAs */
-  BSB_ALGO_REBUILD_GEMM = 3, /* batch/prefill: rebuild fp16 W tiles, dense MMA */
-  BSB_ALGO_GEMV_TC5 = 4   /* decode: tcgen05 / tensor-memory variant */
+  BSB_ALGO_REBUILD_GEMM = 3, /* batch/prefill: rebuild fp16 W, then the tcgen05 GEMM */
+  BSB_ALGO_GEMV_TC5 = 4   /* decode (1-6 rows): packed signs expanded into tensor memory, tcgen05 fp8 MMAs */
 };
 
 int bsb_version(void);
@@ -108,6 +108,17 @@ int bsb_linear_forward(const bsb_weight* w, const uint16_t* x, int64_t rows, int
                        uint16_t* y, int64_t y_stride, void* workspace, int64_t workspace_bytes,
                        int algo, void* stream);
 
+/* Tensor-parallel variant of bsb_linear_forward: the same product written as fp32 PARTIAL SUMS, not rounded to
+ * fp16.  A projection whose input columns are sharded over P devices (the o / down projections of a decoder layer)
+ * yields one partial per device; the caller adds them (one all-reduce) and rounds ONCE, as a single device would.
+ * No counterpart in the reference, which has no tensor parallelism (its forward is
+ * bitstack/modules/BitStackLinear.py:88-157 on one device).  y: fp32 [rows][out], row stride y_stride elements,
+ * 16-byte aligned rows; a bias, if the weight has one, is added (give it to one shard only).  Same scratch as
+ * bsb_linear_forward. */
+int bsb_linear_forward_partial(const bsb_weight* w, const uint16_t* x, int64_t rows, int64_t x_stride,
+                               float* y, int64_t y_stride, void* workspace, int64_t workspace_bytes,
+                               int algo, void* stream);
+
 /* Several weights applied to the SAME x in one launch sequence (q/k/v, gate/up
  * of a decoder layer; the reference calls the module once per projection,
  * bitstack/modules/BitStackLinear.py:88-103).  All weights share in_features.
@@ -116,31 +127,6 @@ int bsb_linear_forward_grouped(const bsb_weight* ws, int32_t n_weights, const ui
                                int64_t rows, int64_t x_stride, uint16_t* const* ys,
                                const int64_t* y_strides, void* workspace, int64_t workspace_bytes,
                                int algo, void* stream);
-
-/* Input transform of bsb_linear_forward_grouped_tf: what the projections multiply is not x itself but
- *   BSB_INPUT_ADD_RMSNORM: rmsnorm(x + x2) * norm_weight (x2 may be NULL); the fp16 sum x + x2, the updated
- *                          residual stream, is also written to h_out (may be NULL; must not alias x or x2);
- *   BSB_INPUT_SILU_MUL:    silu(x) * x2.
- * Both are computed while the decode kernel's operand is prepared, with the roundings of the stand-alone
- * bsb_add_rmsnorm / bsb_silu_mul, so a decode step needs no separate launch for them.  No counterpart in the
- * reference (it leaves these ops to the Hugging Face modules around the projections). */
-enum { BSB_INPUT_PLAIN = 0, BSB_INPUT_ADD_RMSNORM = 1, BSB_INPUT_SILU_MUL = 2 };
-typedef struct bsb_input_transform {
-  int32_t mode;
-  float eps;                   /* rmsnorm epsilon */
-  const uint16_t* x2;          /* fp16 [rows][in_features], rows x2_stride apart */
-  const uint16_t* norm_weight; /* fp16 [in_features] */
-  uint16_t* h_out;             /* fp16 [rows][in_features], rows h_out_stride apart */
-  int64_t x2_stride;
-  int64_t h_out_stride;
-} bsb_input_transform;
-
-/* bsb_linear_forward_grouped with an input transform.  Decode path only: rows <= 6, every weight with k == 16,
- * in_features % 128 == 0 and 16-byte aligned tensors; anything else returns BSB_EINVAL (apply the transform with
- * the stand-alone kernels and call bsb_linear_forward_grouped).  Scratch: bsb_linear_grouped_workspace_bytes. */
-int bsb_linear_forward_grouped_tf(const bsb_weight* ws, int32_t n_weights, const uint16_t* x, int64_t rows,
-                                  int64_t x_stride, const bsb_input_transform* tf, uint16_t* const* ys,
-                                  const int64_t* y_strides, void* workspace, int64_t workspace_bytes, void* stream);
 
 /* Scratch bytes bsb_linear_forward_grouped needs. */
 int64_t bsb_linear_grouped_workspace_bytes(const bsb_weight* ws, int32_t n_weights, int64_t rows, int algo);
@@ -191,20 +177,30 @@ int bsb_silu_mul(const uint16_t* gate, const uint16_t* up, uint16_t* out, int64_
  *   - The first call on each device looks up the device address of the built-in area (with
  *     that device current); make that first call before starting any stream capture.
  *   - All calls share the one area, which keeps whatever the last call left there; the kernels
- *     re-initialise the counters and the status word they depend on at the start of every call.
+ *     re-initialise the counters they depend on at the start of every call.
  *     Two calls that overlap on the GPU (different streams, or different host threads without
  *     ordering) would overwrite each other's scratch: serialise them. */
 int64_t bsb_noalloc_scratch_bytes(void);
 int bsb_linear_forward_noalloc(const bsb_weight* w, const uint16_t* x, int64_t rows, int64_t x_stride,
                                uint16_t* y, int64_t y_stride, void* stream);
 
-/* Debug aid (no reference counterpart): after the work queued by a tcgen05 decode
- * call on `workspace` has finished, copies that call's device status word to
- * *status_out (host): 0 = every hand-off completed, otherwise the code of the
- * time-bounded wait that gave up.  Synchronises the device. */
-int bsb_debug_gemv_status(const bsb_weight* ws, int32_t n_weights, const void* workspace, int32_t* status_out);
-/* The same for the tcgen05 GEMM of a batch call (rows > 4) that used `workspace`. */
-int bsb_debug_gemm_status(const bsb_weight* w, const void* workspace, int32_t* status_out);
+/* Device-side failures (no reference counterpart; the reference fails loudly on the host,
+ * bitstack/modules/BitStackLinear.py:103,120,152, and so must this).  Every wait inside the tcgen05 kernels is
+ * time-bounded.  A wait that gives up (a hardware or driver fault, never expected in a healthy run) makes its
+ * CTA write NaN to every output it was responsible for and stores a code in a per-device status word that
+ * stays set until it is read -- later calls do not clear it.
+ *   bsb_read_status: synchronises the current device, copies the word to *code_out and, if `clear` is non-zero,
+ *     resets it.  Returns BSB_OK when the word is 0, BSB_ETIMEOUT otherwise.  Codes: 1-8 decode kernel (1 Z' ring,
+ *     2 Z' slab, 3/4 operand stage full/empty, 5/6 accumulator full/empty, 7/8 sign ring), 21-24 GEMM.
+ *     Call it wherever the host synchronises anyway (bsb_linear_forward_host does).
+ *   bsb_set_wait_limit_ms: the time limit of every such wait (default 200 ms), for kernels launched afterwards. */
+int bsb_read_status(int32_t* code_out, int32_t clear);
+int bsb_set_wait_limit_ms(int32_t ms);
+
+/* Programmatic dependent launch between the library's kernels (default on): every kernel allows its successor in
+ * the stream to be scheduled early and waits itself for its predecessors before touching memory, so launch
+ * latencies overlap.  0 switches it off (plain stream order), e.g. to time a kernel alone. */
+int bsb_set_dependent_launch(int32_t on);
 
 /* Measurement aids (no reference counterpart).  bsb_debug_launch_count: kernels this
  * library has launched so far in the process.  bsb_debug_profile_start/stop: while
@@ -212,20 +208,14 @@ int bsb_debug_gemm_status(const bsb_weight* w, const void* workspace, int32_t* s
  * the tcgen05 decode kernel (at most max_launches); stop waits for them and writes
  * the per-launch durations in milliseconds. */
 int64_t bsb_debug_launch_count(void);
-/* device_buffer: zeroed uint64 [CTAs][16] that the tcgen05 decode kernel fills with per-role
- * cycle counts (waits, issue, totals) for performance analysis; NULL switches it off. */
-int bsb_debug_set_trace(void* device_buffer);
-/* Timing experiments on the tcgen05 decode kernel: 0 = normal, 1 = tensor-core side only,
- * 2 = sign-streaming side only (modes 1 and 2 produce WRONG outputs by design); 100 / 101 switch
- * the programmatic dependent launch of the decode kernel off / on (default off). */
-int bsb_debug_set_mode(int32_t mode);
 int bsb_debug_profile_start(int32_t max_launches);
 int bsb_debug_profile_stop(float* ms_out, int32_t capacity, int32_t* n_out);
 
 /* Same forward with HOST x and y buffers: copies x to the device, runs the
  * forward, copies y back and waits for it -- the call a host-only user makes.
  * dev_x / dev_y are caller-provided device staging buffers of rows*in and
- * rows*out fp16 elements. */
+ * rows*out fp16 elements.  Returns BSB_ETIMEOUT if the device status word is set when the
+ * outputs arrive (see bsb_read_status). */
 int bsb_linear_forward_host(const bsb_weight* w, const uint16_t* host_x, int64_t rows,
                             uint16_t* host_y, uint16_t* dev_x, uint16_t* dev_y, void* workspace,
                             int64_t workspace_bytes, int algo, void* stream);

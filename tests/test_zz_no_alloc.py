@@ -49,16 +49,25 @@ def test_noalloc_forward_matches_regular_entry_point_twice():
         x = torch.from_numpy(x_np).to(dev)
         ref = mod(x)                                   # bsb_linear_forward, caller workspace
         d = mod.weight_desc(dev)
-        y = torch.full((rows, m), float("nan"), dtype=torch.float16, device=dev)
-        before = torch.cuda.memory_allocated(dev)
-        rc = lib.bsb_linear_forward_noalloc(C.byref(d), x.data_ptr(), rows, n, y.data_ptr(), m, stream)
-        assert rc == 0, lib.bsb_last_error()
-        torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated(dev) == before
-        err = (y.float() - ref.float()).abs().max().item()
-        assert err <= 2e-3 * ref.float().abs().max().item(), (m, n, nb, err)
-        y64 = orc.forward_f64(x_np, q, u, vt, nb)
-        assert orc.max_normalised_error(y.float().cpu().numpy(), y64) <= 4e-3
+        # once with the caller's precomputed max |vt|, once without it: the entry point then computes it into a
+        # corner of its built-in area
+        for absmax in (d.vt_absmax, None):
+            d2 = _lib.BsbWeight()
+            C.memmove(C.byref(d2), C.byref(d), C.sizeof(_lib.BsbWeight))
+            d2.vt_absmax = absmax
+            y = torch.full((rows, m), float("nan"), dtype=torch.float16, device=dev)
+            torch.cuda.synchronize()
+            free_before = torch.cuda.mem_get_info(dev)[0]      # the driver's own count: sees any cudaMalloc in the process
+            before = torch.cuda.memory_allocated(dev)
+            rc = lib.bsb_linear_forward_noalloc(C.byref(d2), x.data_ptr(), rows, n, y.data_ptr(), m, stream)
+            assert rc == 0, lib.bsb_last_error()
+            torch.cuda.synchronize()
+            assert torch.cuda.memory_allocated(dev) == before
+            assert torch.cuda.mem_get_info(dev)[0] >= free_before
+            err = (y.float() - ref.float()).abs().max().item()
+            assert err <= 2e-3 * ref.float().abs().max().item(), (m, n, nb, err)
+            y64 = orc.forward_f64(x_np, q, u, vt, nb)
+            assert orc.max_normalised_error(y.float().cpu().numpy(), y64) <= 4e-3
 
 
 def test_noalloc_rejects_what_does_not_fit():
@@ -86,3 +95,12 @@ def test_noalloc_rejects_what_does_not_fit():
     d2.in_features = 96
     rc = lib.bsb_linear_forward_noalloc(C.byref(d2), x.data_ptr(), 1, 96, y.data_ptr(), 64, None)
     assert rc == -1
+    # no input features at all, and a block stride shorter than a block: rejected on the host like everywhere else
+    d3 = mod2.weight_desc(dev)
+    d3.in_features = 0
+    assert lib.bsb_linear_forward_noalloc(C.byref(d3), x.data_ptr(), 1, 128, y.data_ptr(), 64, None) == -1
+    mod3, _ = _module(64, 128, 2, 4, dev)
+    d4 = mod3.weight_desc(dev)
+    d4.q_block_stride = 16
+    assert lib.bsb_linear_forward_noalloc(C.byref(d4), x.data_ptr(), 1, 128, y.data_ptr(), 64, None) == -1
+    assert b"q_block_stride" in lib.bsb_last_error()
