@@ -283,6 +283,44 @@ int bsb_linear_forward_grouped(const bsb_weight* ws, int32_t n_weights, const ui
   return BSB_OK;
 }
 
+int bsb_linear_forward_grouped_ex(const bsb_weight* ws, int32_t n_weights, const uint16_t* x, int64_t rows, int64_t x_stride,
+                                  const float* x_absmax, uint16_t* const* ys, const int64_t* y_strides,
+                                  const bsb_output_op* op, void* workspace, int64_t workspace_bytes, void* stream) {
+  BSB_CHECK_ARG(n_weights >= 1 && n_weights <= 4 && ws && ys && y_strides && x, "bad group arguments");
+  BSB_CHECK_ARG(rows >= 1 && rows <= kDecodeRowsMax, "the extended call runs on the decode path: 1..%d rows (got %lld)",
+                kDecodeRowsMax, (long long)rows);
+  for (int i = 0; i < n_weights; ++i) {
+    if (int rc = check_weight(&ws[i])) return rc;
+    BSB_CHECK_ARG(ws[i].in_features == ws[0].in_features, "grouped weights must share in_features");
+    BSB_CHECK_ARG(ws[i].blocks > 0 && ws[i].out_features > 0 && gemv_tc5_supported(ws[i]),
+                  "the extended call needs the decode kernel: weight %d has no active block or an unsupported shape/alignment", i);
+  }
+  BSB_CHECK_ARG(rows == 1 || x_stride % 8 == 0, "x rows must be 16-byte aligned");
+  const int64_t need = gemv_tc5_workspace_bytes(ws, n_weights, rows >= 2 ? 2 : 1);
+  if (workspace == nullptr || workspace_bytes < need) {
+    set_error("workspace of %lld bytes needed, %lld given", (long long)need, (long long)workspace_bytes);
+    return BSB_EWORKSPACE;
+  }
+  for (int64_t r = 0; r < rows;) {
+    const int nr = (rows - r >= 2) ? 2 : 1;
+    __half* yr[4];
+    for (int i = 0; i < n_weights; ++i) yr[i] = (__half*)ys[i] + r * y_strides[i];
+    bsb_output_op pass_op;
+    if (op != nullptr) {   // this pass's rows of the output op's buffers
+      pass_op = *op;
+      if (pass_op.h) pass_op.h += r * pass_op.h_stride;
+      if (pass_op.x_out) pass_op.x_out += r * pass_op.x_stride;
+      if (pass_op.x_absmax) pass_op.x_absmax += r;
+    }
+    if (int rc = launch_gemv_tc5(ws, n_weights, (const __half*)x + r * x_stride, x_stride, nr, yr, y_strides, workspace,
+                                 workspace_bytes, (cudaStream_t)stream, false, x_absmax ? x_absmax + r : nullptr,
+                                 op ? &pass_op : nullptr))
+      return rc;
+    r += nr;
+  }
+  return BSB_OK;
+}
+
 int64_t bsb_linear_grouped_workspace_bytes(const bsb_weight* ws, int32_t n_weights, int64_t rows, int algo) {
   if (!ws || n_weights < 1 || rows < 0) return -1;
   int64_t need = 0;
@@ -329,6 +367,10 @@ int bsb_tuning_set_trace(void* device_buffer) {
 }
 int bsb_tuning_set_mode(int32_t mode) {
   gemv_tc5_set_dbg(mode);
+  return BSB_OK;
+}
+int bsb_tuning_set_timeline(void* device_buffer, int32_t records) {
+  gemv_tc5_set_timeline((unsigned long long*)device_buffer, records);
   return BSB_OK;
 }
 #endif

@@ -45,14 +45,23 @@ inline int check_launch(const char* what) {
   return BSB_OK;
 }
 
-// Programmatic dependent launch.  Every kernel of the decode step starts with pdl_wait() (returns when
-// the kernels before it in the stream have completed and their writes are visible; a no-op for a normal
-// launch) followed by pdl_trigger() (the NEXT kernel's launch may be processed now: it will sit in its
-// own pdl_wait()).  Only the launch latency overlaps; no kernel touches memory before its wait.
+// Programmatic dependent launch.  Every kernel of the decode step starts with pdl_enter(): wait until the kernels
+// before it in the stream have completed and their writes are visible (a no-op for a normal launch), then let the
+// NEXT kernel be scheduled, which will sit in its own wait.  Launch latency overlaps; constants of a weight may be
+// fetched before the wait, nothing that another kernel writes is touched before it.
 extern int g_pdl_enabled;
 #ifdef __CUDACC__
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_enter() {
+#ifdef BSB_PDL_EARLY   // measurement variant: the successor is released before this kernel's own wait (a whole chain of
+  pdl_trigger();       // kernels becomes resident ahead of time); measured 7 % slower on a full decode step
+  pdl_wait();
+#else
+  pdl_wait();
+  pdl_trigger();
+#endif
+}
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
   cudaLaunchConfig_t cfg = {};
@@ -115,9 +124,12 @@ void gemv_tc5_set_wait_limit_ns(unsigned long long ns);
 #ifdef BSB_TUNING
 void gemv_tc5_set_trace(unsigned long long* device_buffer);
 void gemv_tc5_set_dbg(int mode);
+void gemv_tc5_set_timeline(unsigned long long* device_buffer, int records);
 #endif
-// out_f32: the ys point at fp32 rows (partial sums of a tensor-parallel shard) instead of fp16 ones
+// out_f32: the ys point at fp32 rows (partial sums of a tensor-parallel shard) instead of fp16 ones;
+// x_absmax: optional max |x| per row of this pass; op: optional output stage (its pointers are those of this pass's rows)
 int launch_gemv_tc5(const bsb_weight* ws, int n_weights, const __half* x, int64_t x_stride, int rows, __half* const* ys,
-                    const int64_t* y_strides, void* workspace, int64_t workspace_bytes, cudaStream_t s, bool out_f32 = false);
+                    const int64_t* y_strides, void* workspace, int64_t workspace_bytes, cudaStream_t s, bool out_f32 = false,
+                    const float* x_absmax = nullptr, const bsb_output_op* op = nullptr);
 
 }  // namespace bsb

@@ -5,82 +5,21 @@
 #include <cstdint>
 
 #include "common.cuh"
+#include "rowops.cuh"
 
 namespace bsb {
 namespace {
 
-// h[row] (+= delta[row]) ; y[row] = h[row] * rsqrt(mean(h^2) + eps) * weight      (fp32 inside)
-// one CTA per row; a thread keeps its 8-element vectors (16-byte loads) in registers, so the row is
-// read once, the norm weight is fetched before the reduction and nothing is staged in shared memory
-constexpr int kNormThreads = 512;
-constexpr int kNormVecs = 4;   // vectors per thread: rows up to 512 * 4 * 8 = 16384 elements
-__global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(__half* __restrict__ h, const __half* __restrict__ delta,
-                                                                   const __half* __restrict__ weight, float eps,
-                                                                   __half* __restrict__ y, int hidden) {
-  __shared__ float red[kNormThreads / 32];
-  pdl_wait();
-  pdl_trigger();
+// h[row] (+= delta[row]) ; y[row] = h[row] * rsqrt(mean(h^2) + eps) * weight; optionally max |y[row]|.
+// One CTA per row (rowops.cuh).
+__global__ void __launch_bounds__(kRowThreads) add_rmsnorm_kernel(__half* __restrict__ h, const __half* __restrict__ delta,
+                                                                  const __half* __restrict__ weight, float eps,
+                                                                  __half* __restrict__ y, int hidden, float* __restrict__ absmax) {
+  __shared__ float red[kRowThreads / 32];
+  pdl_enter();
   const int64_t row = blockIdx.x;
-  uint4* hr = reinterpret_cast<uint4*>(h + row * hidden);
-  const uint4* dr = delta ? reinterpret_cast<const uint4*>(delta + row * hidden) : nullptr;
-  const uint4* wr = reinterpret_cast<const uint4*>(weight);
-  const int nvec = hidden / 8;
-  uint4 hv[kNormVecs], dv[kNormVecs], wv[kNormVecs];
-#pragma unroll
-  for (int k = 0; k < kNormVecs; ++k) {
-    const int i = threadIdx.x + k * kNormThreads;
-    if (i < nvec) {
-      hv[k] = hr[i];
-      if (dr) dv[k] = __ldg(dr + i);
-      wv[k] = __ldg(wr + i);
-    }
-  }
-  float ss = 0.f;
-#pragma unroll
-  for (int k = 0; k < kNormVecs; ++k) {
-    const int i = threadIdx.x + k * kNormThreads;
-    if (i < nvec) {
-      __half2* hp = reinterpret_cast<__half2*>(&hv[k]);
-      if (dr) {
-        const __half2* dp = reinterpret_cast<const __half2*>(&dv[k]);
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const float2 a = __half22float2(hp[q]), d = __half22float2(dp[q]);
-          hp[q] = __floats2half2_rn(a.x + d.x, a.y + d.y);   // the residual stream stays fp16
-        }
-        hr[i] = hv[k];
-      }
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const float2 a = __half22float2(hp[q]);
-        ss += a.x * a.x + a.y * a.y;
-      }
-    }
-  }
-  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
-  __syncthreads();
-  float tot = 0.f;
-#pragma unroll
-  for (int i = 0; i < kNormThreads / 32; ++i) tot += red[i];
-  const float inv = rsqrtf(tot / (float)hidden + eps);
-  uint4* yr = reinterpret_cast<uint4*>(y + row * hidden);
-#pragma unroll
-  for (int k = 0; k < kNormVecs; ++k) {
-    const int i = threadIdx.x + k * kNormThreads;
-    if (i < nvec) {
-      const __half2* hp = reinterpret_cast<const __half2*>(&hv[k]);
-      const __half2* wp = reinterpret_cast<const __half2*>(&wv[k]);
-      uint4 out;
-      __half2* op = reinterpret_cast<__half2*>(&out);
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const float2 a = __half22float2(hp[q]), wq = __half22float2(wp[q]);
-        op[q] = __floats2half2_rn(a.x * inv * wq.x, a.y * inv * wq.y);
-      }
-      yr[i] = out;
-    }
-  }
+  add_rmsnorm_row<false>(h + row * hidden, delta ? delta + row * hidden : nullptr, weight, eps, y + row * hidden, hidden, red,
+                         absmax ? absmax + row : nullptr);
 }
 
 // one CTA per (batch row, head); heads [0, Hq) are query heads (rotated in place), then Hkv key
@@ -90,8 +29,7 @@ __global__ void __launch_bounds__(128) rope_cache_kernel(__half* __restrict__ q,
                                                          const __half* __restrict__ sin_t, const int64_t* __restrict__ pos_p,
                                                          __half* __restrict__ k_cache, __half* __restrict__ v_cache,
                                                          int Hq, int Hkv, int D, int max_len) {
-  pdl_wait();
-  pdl_trigger();
+  pdl_enter();
   const int b = blockIdx.y, head = blockIdx.x;
   const int64_t pos = *pos_p;
   if (pos < 0 || pos >= max_len) return;   // out of the cache: nothing is written
@@ -149,8 +87,7 @@ __global__ void __launch_bounds__(256) decode_attention_kernel(const __half* __r
   __shared__ float s_red[8];
   __shared__ float s_part[kRowsPerPass][D];
   __shared__ int s_last;
-  pdl_wait();
-  pdl_trigger();
+  pdl_enter();
   const int h = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int64_t pos = *pos_p;
@@ -298,8 +235,7 @@ __global__ void __launch_bounds__(1024) greedy_step_kernel(const __half* __restr
                                                            int64_t* __restrict__ tokens, int64_t* __restrict__ pos) {
   __shared__ float s_val[32];
   __shared__ int64_t s_idx[32];
-  pdl_wait();
-  pdl_trigger();
+  pdl_enter();
   const __half* row = logits + (int64_t)blockIdx.x * stride;
   float best = -INFINITY;
   int64_t best_i = INT64_MAX;
@@ -342,16 +278,13 @@ __global__ void __launch_bounds__(1024) greedy_step_kernel(const __half* __restr
   }
 }
 
-__global__ void __launch_bounds__(256) silu_mul_kernel(const __half2* __restrict__ g, const __half2* __restrict__ u,
-                                                       __half2* __restrict__ out, int64_t n2) {
-  pdl_wait();
-  pdl_trigger();
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n2; i += (int64_t)gridDim.x * blockDim.x) {
-    const float2 a = __half22float2(g[i]), b = __half22float2(u[i]);
-    const __half2 s = __floats2half2_rn(a.x / (1.f + __expf(-a.x)), a.y / (1.f + __expf(-a.y)));   // fp16 SiLU, as torch rounds it
-    const float2 sf = __half22float2(s);
-    out[i] = __floats2half2_rn(sf.x * b.x, sf.y * b.y);
-  }
+// out[row] = silu(gate[row]) * up[row]; optionally max |out[row]|.  One CTA per row (rowops.cuh).
+__global__ void __launch_bounds__(kRowThreads) silu_mul_kernel(const __half* __restrict__ g, const __half* __restrict__ u,
+                                                               __half* __restrict__ out, int n, float* __restrict__ absmax) {
+  __shared__ float red[kRowThreads / 32];
+  pdl_enter();
+  const int64_t row = blockIdx.x;
+  silu_mul_row<false>(g + row * n, u + row * n, out + row * n, n, red, absmax ? absmax + row : nullptr);
 }
 
 }  // namespace
@@ -361,16 +294,16 @@ using namespace bsb;
 
 extern "C" {
 
-int bsb_add_rmsnorm(uint16_t* h, const uint16_t* delta, const uint16_t* weight, float eps, uint16_t* y, int64_t rows,
-                    int32_t hidden, void* stream) {
+int bsb_add_rmsnorm(uint16_t* h, const uint16_t* delta, const uint16_t* weight, float eps, uint16_t* y, float* y_absmax,
+                    int64_t rows, int32_t hidden, void* stream) {
   BSB_CHECK_ARG(h && weight && y, "NULL buffer");
-  BSB_CHECK_ARG(rows >= 0 && hidden > 0 && hidden % 8 == 0 && hidden <= kNormThreads * kNormVecs * 8,
+  BSB_CHECK_ARG(rows >= 0 && hidden > 0 && hidden % 8 == 0 && hidden <= kRowThreads * kRowVecs * 8,
                 "hidden must be a multiple of 8 and <= 16384");
   BSB_CHECK_ARG(((uintptr_t)h | (uintptr_t)weight | (uintptr_t)y | (uintptr_t)delta) % 16 == 0, "buffers must be 16-byte aligned");
   if (rows == 0) return BSB_OK;
   BSB_CHECK_ARG(rows <= 65535 * 32, "too many rows");
-  BSB_CUDA(launch_pdl(add_rmsnorm_kernel, dim3((unsigned)rows), dim3(kNormThreads), 0, (cudaStream_t)stream,
-                      (__half*)h, (const __half*)delta, (const __half*)weight, eps, (__half*)y, hidden));
+  BSB_CUDA(launch_pdl(add_rmsnorm_kernel, dim3((unsigned)rows), dim3(kRowThreads), 0, (cudaStream_t)stream,
+                      (__half*)h, (const __half*)delta, (const __half*)weight, eps, (__half*)y, hidden, y_absmax));
   return check_launch("add_rmsnorm_kernel");
 }
 
@@ -430,15 +363,15 @@ int bsb_greedy_step(const uint16_t* logits, int64_t batch, int64_t vocab, int64_
   return check_launch("greedy_step_kernel");
 }
 
-int bsb_silu_mul(const uint16_t* gate, const uint16_t* up, uint16_t* out, int64_t n, void* stream) {
+int bsb_silu_mul(const uint16_t* gate, const uint16_t* up, uint16_t* out, float* out_absmax, int64_t rows, int32_t n,
+                 void* stream) {
   BSB_CHECK_ARG(gate && up && out, "NULL buffer");
-  BSB_CHECK_ARG(n >= 0 && n % 2 == 0, "element count must be even");
-  BSB_CHECK_ARG(((uintptr_t)gate | (uintptr_t)up | (uintptr_t)out) % 4 == 0, "buffers must be 4-byte aligned");
-  if (n == 0) return BSB_OK;
-  int64_t blocks = ceil_div64(n / 2, 256);
-  if (blocks > 1184) blocks = 1184;
-  BSB_CUDA(launch_pdl(silu_mul_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (const __half2*)gate,
-                      (const __half2*)up, (__half2*)out, n / 2));
+  BSB_CHECK_ARG(rows >= 0 && n >= 0 && n % 8 == 0, "row length must be a multiple of 8");
+  BSB_CHECK_ARG(((uintptr_t)gate | (uintptr_t)up | (uintptr_t)out) % 16 == 0, "buffers must be 16-byte aligned");
+  if (rows == 0 || n == 0) return BSB_OK;
+  BSB_CHECK_ARG(rows <= 65535 * 32, "too many rows");
+  BSB_CUDA(launch_pdl(silu_mul_kernel, dim3((unsigned)rows), dim3(kRowThreads), 0, (cudaStream_t)stream, (const __half*)gate,
+                      (const __half*)up, (__half*)out, n, out_absmax));
   return check_launch("silu_mul_kernel");
 }
 

@@ -31,6 +31,7 @@
 #endif
 
 #include "common.cuh"
+#include "rowops.cuh"
 
 namespace bsb {
 
@@ -62,6 +63,17 @@ struct alignas(64) TcParams {
   CUtensorMap sign_map[kMaxGroup];   // u8 [blocks][out][in/8], box 1 x 128 x 64, 64-byte swizzle
   bsb_weight w[kMaxGroup];
   const float* vt_absmax[kMaxGroup];
+  const float* x_absmax;           // optional max |x| per input row of this pass (from the kernel that produced x), or nullptr
+  // output stage, run by the last CTA to finish once every output of the call is in memory (bsb_output_op):
+  // 1: h += y[0]; x_out = rmsnorm(h) * norm_w     2: x_out = silu(y[0]) * y[1]     (rows of this pass)
+  int post_mode;
+  float post_eps;
+  __half* post_h;
+  const __half* post_norm_w;
+  __half* post_x;
+  float* post_absmax;
+  int64_t post_h_stride, post_x_stride;
+  int absmax_const;                // every vt_absmax came from the caller (a constant of the weight), none is computed in front of this call
   __half* y[kMaxGroup];            // fp16 rows, or fp32 rows when out_f32 is set
   int out_f32;                     // outputs are fp32 partial sums of a tensor-parallel shard (no rounding)
   int n_weights;
@@ -81,10 +93,11 @@ struct alignas(64) TcParams {
   uint8_t* zops;     // [(weight,block)][chunk][16 words][rows][1 KB]
   float* kconst;     // [(weight,block)][chunk][rows][16]
   float* inv_scale;  // [(weight,block)][rows][16]
-  int* counters;     // [row group]: CTAs that have delivered their partial sums
+  int* counters;     // [row group]: CTAs that have delivered their partial sums; then one more: CTAs that have finished
   int* status;       // the library's sticky status word of this device: 0 = fine, else the code of the first wait that gave up
   unsigned long long wait_ns;   // time limit of every wait
 #ifdef BSB_TUNING
+  unsigned long long* timeline;   // optional [8] wall-clock marks of this call (see TL_MIN / TL_MAX), or nullptr
   unsigned long long* trace;  // optional [CTA][16] cycle counters, or nullptr
   int dbg;           // 0 = normal; 1 = MMA side only, 2 = producer side only (timing experiments, wrong results); 3 = the Z' loader
                      // never loads (the waits behind it run out: exercises the give-up path)
@@ -114,6 +127,15 @@ __device__ __forceinline__ uint64_t global_ns() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
+// wall-clock marks of one call in the tuning build: slot 0 / 1 / 2 = first Z' CTA entered / first passed its wait / last
+// left; 3 = first decode CTA entered, 4 = first Z' slab consumed, 5 = last epilogue done, 6 = last decode CTA left
+#ifdef BSB_TUNING
+#define TL_MIN(slot) do { if (P.timeline) atomicMin(P.timeline + (slot), (unsigned long long)global_ns()); } while (0)
+#define TL_MAX(slot) do { if (P.timeline) atomicMax(P.timeline + (slot), (unsigned long long)global_ns()); } while (0)
+#else
+#define TL_MIN(slot) do { } while (0)
+#define TL_MAX(slot) do { } while (0)
+#endif
 // mbarrier.try_wait suspends the thread in hardware until the phase completes or a short, implementation-defined
 // time has passed: a waiting role costs almost no issue slots.
 __device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
@@ -251,12 +273,18 @@ __global__ void __launch_bounds__(256) vt_absmax_kernel(bsb_weight w, float* __r
 }
 
 // ------------------------------------------------------------------ Z' preparation
-// grid = (n_chunks, total blocks, input rows), 256 threads.  Operand tile of word w (32 columns):
-// byte offset (n%8)*16 + (n/8)*256 + (k%16) + (k/16)*128 with n = 16*piece + rank and
-// k = 4*i + c for the column 8c+7-i of the word.
-__global__ void __launch_bounds__(256) zprep_tc5_kernel(const __grid_constant__ TcParams P, const __half* __restrict__ x) {
-  __shared__ float red[8];
-  __shared__ float kred[16][16];
+// grid = (n_chunks, total blocks, input rows), 512 threads: thread = (32-column word, half of the eight bit classes,
+// rank).  Operand tile of word w (32 columns): byte offset (n%8)*16 + (n/8)*256 + (k%16) + (k/16)*128 with
+// n = 16*piece + rank and k = 4*i + c for the column 8c+7-i of the word (i = bit class, c = byte of the packed word).
+// Everything that does not depend on x (the factors, their maximum, the per-class multipliers) is fetched and
+// computed BEFORE the wait for the kernels in front; after it the chain is: load x, row maximum, one reciprocal,
+// two multiplies and the fp8 split per element, store.
+__constant__ float kTwoOverD[8] = {2.f / 1.f, 2.f / 1.f, 2.f / 1.f, 2.f / 0.75f, 2.f / 1.125f, 2.f / 1.40625f, 2.f / 2.f, 2.f / -2.f};
+constexpr int kZprepThreads = 512;
+
+__global__ void __launch_bounds__(kZprepThreads) zprep_tc5_kernel(const __grid_constant__ TcParams P, const __half* __restrict__ x) {
+  __shared__ float red[16];
+  __shared__ float kred[16][2][16];
 
   const int chunk = blockIdx.x;
   int wi = 0;
@@ -265,107 +293,122 @@ __global__ void __launch_bounds__(256) zprep_tc5_kernel(const __grid_constant__ 
   const int j = blockIdx.y - P.blk_base[wi];
   const int N = w.in_features;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  // thread = (32-column word, rank): all of its inputs are 64 contiguous bytes of one Vt row and
-  // of x, fetched straight into registers -- no staging, one barrier in the whole kernel
-  const int word = tid >> 4, r = tid & 15;
+  const int r = tid & 15, kh = (tid >> 4) & 1, word = tid >> 5;   // a warp = one word
   const int col0 = chunk * kChunkCols + word * 32;
   const int R = P.rows, row = blockIdx.z;
   const bool in_range = col0 < N;   // in_features is a multiple of 128, so a word is inside or outside as a whole
+  // this thread's columns: 8c + base + e (c = 0..3, e = 0..3), whose bit class is 7 - base - e = 4 kh + (3 - e)
+  const int base = kh ? 0 : 4;
 
-  // The decode kernel of this call may be scheduled at once (it prefetches sign tiles, which depend on nothing, and
-  // waits for this grid before it touches anything written here).  The factors are constants of the weight: they are
-  // fetched before the wait for the kernels in front of this one, whose outputs are x and the scratch of the previous call.
-  pdl_trigger();
-  uint4 vq[4], xq[4];
-  const __half* vt = reinterpret_cast<const __half*>(w.vt) + (int64_t)j * w.vt_block_stride + (int64_t)r * N;
+  if (tid == 0) TL_MIN(0);
+  uint2 vq[4];
+  const __half* vt = reinterpret_cast<const __half*>(w.vt) + (int64_t)j * w.vt_block_stride + (int64_t)r * N + col0 + base;
 #pragma unroll
-  for (int i = 0; i < 4; ++i) vq[i] = in_range ? __ldg(reinterpret_cast<const uint4*>(vt + col0) + i) : make_uint4(0, 0, 0, 0);
-  const float vmax = P.vt_absmax[wi][j * 16 + r];
-  pdl_wait();
+  for (int c = 0; c < 4; ++c) vq[c] = in_range ? __ldg(reinterpret_cast<const uint2*>(vt + 8 * c)) : make_uint2(0, 0);
+  // the maximum of |vt| is a constant of the weight when the caller passed it in; when it was computed into the
+  // scratch by a kernel in front of this one it may only be read after the wait
+  float vmax = P.absmax_const ? P.vt_absmax[wi][j * 16 + r] : 0.f;
+  float vtd[4][4];   // vt * 2 / d_class
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const __half2* h = reinterpret_cast<const __half2*>(&vq[c]);
+    const float2 a = __half22float2(h[0]), b = __half22float2(h[1]);
+    vtd[c][0] = a.x; vtd[c][1] = a.y; vtd[c][2] = b.x; vtd[c][3] = b.y;
+  }
+  // x and the scratch of the previous call are safe to touch once the kernels before this one are done; then the
+  // decode kernel of this call may be scheduled (it waits for this grid before it touches anything written here)
+  pdl_enter();
+  if (tid == 0) TL_MIN(1);
+  if (!P.absmax_const) vmax = P.vt_absmax[wi][j * 16 + r];
 
   x += (int64_t)row * P.x_stride;
   if (blockIdx.x == 0 && blockIdx.y == 0 && row == 0)
-    for (int i = tid; i < P.seg_base[P.n_weights]; i += blockDim.x) P.counters[i] = 0;
+    for (int i = tid; i <= P.seg_base[P.n_weights]; i += blockDim.x) P.counters[i] = 0;   // the last one counts finished CTAs
+  uint2 xq[4];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) xq[i] = in_range ? __ldg(reinterpret_cast<const uint4*>(x) + col0 / 8 + i) : make_uint4(0, 0, 0, 0);
-  // max |x| over the whole row: sets the scale of the e4m3 operand
+  for (int c = 0; c < 4; ++c) xq[c] = in_range ? __ldg(reinterpret_cast<const uint2*>(x + col0 + base + 8 * c)) : make_uint2(0, 0);
+  // max |x| over the whole row sets the scale of the e4m3 operand: taken from the producer of x when it delivered
+  // it, else computed here (every CTA reads the whole row; CTAs start at different places so that they do not all
+  // ask the same L2 lines at the same moment)
   float xm = 0.f;
-  for (int n8 = tid; n8 < N / 8; n8 += blockDim.x) {
-    const uint4 q = __ldg(reinterpret_cast<const uint4*>(x) + n8);
-    const __half2* h = reinterpret_cast<const __half2*>(&q);
+  if (P.x_absmax != nullptr) {
+    xm = P.x_absmax[row];
+  } else {
+    const int nvec = N / 8;
+    const int rot = (int)((blockIdx.x * 37u + blockIdx.y * 101u) * 64u % (unsigned)nvec);
+    for (int i = tid; i < nvec; i += kZprepThreads) {
+      int n8 = i + rot;
+      if (n8 >= nvec) n8 -= nvec;
+      const uint4 q = __ldg(reinterpret_cast<const uint4*>(x) + n8);
+      const __half2* h = reinterpret_cast<const __half2*>(&q);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float2 f = __half22float2(__habs2(h[i]));
-      xm = fmaxf(xm, fmaxf(f.x, f.y));
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = __half22float2(__habs2(h[k]));
+        xm = fmaxf(xm, fmaxf(f.x, f.y));
+      }
     }
-  }
-  for (int o = 16; o > 0; o >>= 1) xm = fmaxf(xm, __shfl_xor_sync(0xFFFFFFFFu, xm, o));
-  if (lane == 0) red[warp] = xm;
-  __syncthreads();
-  xm = red[0];
+    for (int o = 16; o > 0; o >>= 1) xm = fmaxf(xm, __shfl_xor_sync(0xFFFFFFFFu, xm, o));
+    if (lane == 0) red[warp] = xm;
+    __syncthreads();
+    xm = red[0];
 #pragma unroll
-  for (int i = 1; i < 8; ++i) xm = fmaxf(xm, red[i]);
+    for (int i = 1; i < kZprepThreads / 32; ++i) xm = fmaxf(xm, red[i]);
+  }
+  if (tid == 0) TL_MAX(7);
 
   const float bound = vmax * xm;
-  const float scale = (bound > 0.f) ? (kTargetMax * kMinD) / (2.f * bound) : 1.f;
+  const float scale = (bound > 0.f) ? __fdividef(kTargetMax * kMinD * 0.5f, bound) : 1.f;
   const float inv_scale = 1.f / scale;
   if (chunk == 0 && tid < 16) P.inv_scale[((int64_t)blockIdx.y * R + row) * 16 + r] = inv_scale;
 
-  // z[lc] = vt * x for the 32 columns of the word
-  float z[32];
-  {
-    const __half2* vh = reinterpret_cast<const __half2*>(vq);
-    const __half2* xh = reinterpret_cast<const __half2*>(xq);
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const float2 a = __half22float2(vh[i]), b = __half22float2(xh[i]);
-      z[2 * i] = a.x * b.x;
-      z[2 * i + 1] = a.y * b.y;
-    }
-  }
   // the operand tile of a word holds the rows one after the other (row i = B columns 32i .. 32i+31)
   uint8_t* tile = P.zops + (((int64_t)blockIdx.y * P.n_chunks + chunk) * 16 + word) * (1024 * R) + row * 1024;
   float c_sum = 0.f, z_sum = 0.f;
+  uint32_t hi[4], lo[4];
+  float xf[4][4];
 #pragma unroll
-  for (int kh = 0; kh < 2; ++kh) {
-    uint32_t hi[4], lo[4];
-#pragma unroll
-    for (int il = 0; il < 4; ++il) {
-      const int cls = 4 * kh + il;
-      const float mul = 2.f * scale / kD[cls];
-      const float v0 = kV0[cls];
-      uint32_t h32 = 0, l32 = 0;
-#pragma unroll
-      for (int cp = 0; cp < 2; ++cp) {   // two columns per conversion instruction
-        const float za = z[8 * (2 * cp) + 7 - cls], zb = z[8 * (2 * cp + 1) + 7 - cls];
-        const float2 zp = make_float2(za * mul, zb * mul);
-        const __nv_fp8x2_storage_t qh = __nv_cvt_float2_to_fp8x2(zp, __NV_SATFINITE, __NV_E4M3);
-        const float2 fh = __half22float2(__half2(__nv_cvt_fp8x2_to_halfraw2(qh, __NV_E4M3)));
-        const __nv_fp8x2_storage_t ql = __nv_cvt_float2_to_fp8x2(make_float2(zp.x - fh.x, zp.y - fh.y), __NV_SATFINITE, __NV_E4M3);
-        const float2 fl = __half22float2(__half2(__nv_cvt_fp8x2_to_halfraw2(ql, __NV_E4M3)));
-        c_sum = fmaf(v0, (fh.x + fl.x) + (fh.y + fl.y), c_sum);
-        z_sum += za + zb;
-        h32 |= (uint32_t)qh << (16 * cp);
-        l32 |= (uint32_t)ql << (16 * cp);
-      }
-      hi[il] = h32;
-      lo[il] = l32;
-    }
-    // n = r (hi) and n = 16 + r (lo); 16 consecutive k bytes starting at 16*kh
-    const int off_hi = (r % 8) * 16 + (r / 8) * 256 + kh * 128;
-    const int off_lo = (r % 8) * 16 + ((16 + r) / 8) * 256 + kh * 128;
-    *reinterpret_cast<uint4*>(tile + off_hi) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-    *reinterpret_cast<uint4*>(tile + off_lo) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+  for (int c = 0; c < 4; ++c) {
+    const __half2* h = reinterpret_cast<const __half2*>(&xq[c]);
+    const float2 a = __half22float2(h[0]), b = __half22float2(h[1]);
+    xf[c][0] = a.x; xf[c][1] = a.y; xf[c][2] = b.x; xf[c][3] = b.y;
   }
+#pragma unroll
+  for (int il = 0; il < 4; ++il) {
+    const int e = 3 - il;
+    const float mul = scale * (kh ? kTwoOverD[4 + il] : kTwoOverD[il]);
+    const float v0 = kh ? kV0[4 + il] : kV0[il];
+    uint32_t h32 = 0, l32 = 0;
+#pragma unroll
+    for (int cp = 0; cp < 2; ++cp) {   // two columns per conversion instruction
+      const float za = vtd[2 * cp][e] * xf[2 * cp][e], zb = vtd[2 * cp + 1][e] * xf[2 * cp + 1][e];
+      const float2 zp = make_float2(za * mul, zb * mul);
+      const __nv_fp8x2_storage_t qh = __nv_cvt_float2_to_fp8x2(zp, __NV_SATFINITE, __NV_E4M3);
+      const float2 fh = __half22float2(__half2(__nv_cvt_fp8x2_to_halfraw2(qh, __NV_E4M3)));
+      const __nv_fp8x2_storage_t ql = __nv_cvt_float2_to_fp8x2(make_float2(zp.x - fh.x, zp.y - fh.y), __NV_SATFINITE, __NV_E4M3);
+      const float2 fl = __half22float2(__half2(__nv_cvt_fp8x2_to_halfraw2(ql, __NV_E4M3)));
+      c_sum = fmaf(v0, (fh.x + fl.x) + (fh.y + fl.y), c_sum);
+      z_sum += za + zb;
+      h32 |= (uint32_t)qh << (16 * cp);
+      l32 |= (uint32_t)ql << (16 * cp);
+    }
+    hi[il] = h32;
+    lo[il] = l32;
+  }
+  // n = r (hi) and n = 16 + r (lo); 16 consecutive k bytes starting at 16*kh
+  const int off_hi = (r % 8) * 16 + (r / 8) * 256 + kh * 128;
+  const int off_lo = (r % 8) * 16 + ((16 + r) / 8) * 256 + kh * 128;
+  *reinterpret_cast<uint4*>(tile + off_hi) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+  *reinterpret_cast<uint4*>(tile + off_lo) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
   // constant of this (block, chunk, rank): C_r / s_r + sum Z over the chunk's columns
-  kred[word][r] = c_sum * inv_scale + z_sum;
+  kred[word][kh][r] = c_sum * inv_scale + z_sum;
   __syncthreads();
   if (tid < 16) {
     float v = 0.f;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) v += kred[i][tid];
+    for (int i = 0; i < 16; ++i) v += kred[i][0][tid] + kred[i][1][tid];
     P.kconst[(((int64_t)blockIdx.y * P.n_chunks + chunk) * R + row) * 16 + tid] = v;
   }
+  if (tid == 0) TL_MAX(2);
 }
 
 // cycle accounting for the optional trace (one elected lane per role writes)
@@ -493,6 +536,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
   Smem& S = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
 
   pdl_trigger();   // the kernel after this one may be launched; it waits for this grid before it reads y
+  if (threadIdx.x == 0) TL_MIN(3);
   const int NCH = P.n_chunks;
   const int step0 = first_step_of_cta(P, blockIdx.x);
   const int total = min((int)blockIdx.x < P.n_first ? P.steps_first : P.steps_per_cta, P.step_base[P.n_weights] - step0);   // steps of this CTA
@@ -605,6 +649,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
         TR_BEGIN(t1);
         if (!mbar_wait(&S.zfull[zslot], (g / kNZr) & 1, wait_ns)) { if (leader) GIVE_UP(2); ok = false; break; }
         TR_ADD(5, t1);
+        if (g == 0 && leader) TL_MIN(4);
         const uint32_t zaddr = smem_u32(S.zs[zslot]) + (RT == 1 ? (uint32_t)e * 8u * 1024u * R : 0u);
         const uint32_t dcol = tbase + (e * kND + b) * kDCols;
 #pragma unroll 1
@@ -833,6 +878,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
       wk.advance(P, kRows, len);
     }
     TR_ADD(10, t_epi);
+    if (warp == kWarpEpi && lane == 0) TL_MAX(5);
     }
   }
 
@@ -890,7 +936,8 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
   }
   // ---- shared row groups: the last CTA to deliver adds the partial sums in CTA order ------
   const int n_pending = S.n_pending;
-  if (n_pending == 0) return;
+  if (tid == 0) TL_MAX(6);
+  if (n_pending == 0 && P.post_mode == 0) return;
   asm volatile("griddepcontrol.wait;" ::: "memory");     // the counters were zeroed by the Z' kernel
   for (int q = 0; q < n_pending; ++q) {
     const int wi = S.pending[q][0], rg = S.pending[q][1];
@@ -911,16 +958,46 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
 #pragma unroll
       for (int r = 0; r < R; ++r) {
         float sum = 0.f;
-        for (int c = c_first; c <= c_last; ++c) {
-          // the row group is CTA c's first row segment unless it starts after c's first step
-          const int slot = (gs <= first_step_of_cta(P, c)) ? 0 : 1;
-          sum += __ldcg(P.partials + (((int64_t)c * 2 + slot) * R + r) * kRows + tid);
+        // eight loads in flight at a time; the additions stay in CTA order (bit-identical run to run)
+        for (int c0 = c_first; c0 <= c_last; c0 += 8) {
+          float v[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int c = c0 + i;
+            // the row group is CTA c's first row segment unless it starts after c's first step
+            const int slot = (gs <= first_step_of_cta(P, c)) ? 0 : 1;
+            v[i] = (c <= c_last) ? __ldcg(P.partials + (((int64_t)c * 2 + slot) * R + r) * kRows + tid) : 0.f;
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) sum += v[i];
         }
         if (w.bias) sum += __half2float(reinterpret_cast<const __half*>(w.bias)[m]);
         store_y(P, wi, r, m, sum);
       }
     }
   }
+  // ---- output stage: the last CTA to finish applies the row operation that follows the projection in a decoder
+  //      layer to the finished outputs (one CTA's work; saves a kernel and its launch boundary) ------------------
+  if (P.post_mode != 0) {
+    __threadfence();     // this CTA's outputs are visible before it is counted as finished
+    __syncthreads();
+    if (tid == 0) S.last = (atomicAdd(&P.counters[P.seg_base[P.n_weights]], 1) == (int)gridDim.x - 1);
+    __syncthreads();
+    if (S.last) {
+      __threadfence();
+      float* red = reinterpret_cast<float*>(S.zs);   // the operand rings are idle now
+      for (int r = 0; r < R; ++r) {
+        float* am = P.post_absmax ? P.post_absmax + r : nullptr;
+        if (P.post_mode == 1)
+          add_rmsnorm_row<true>(P.post_h + r * P.post_h_stride, P.y[0] + r * P.y_stride[0], P.post_norm_w, P.post_eps,
+                                P.post_x + r * P.post_x_stride, P.w[0].out_features, red, am);
+        else
+          silu_mul_row<true>(P.y[0] + r * P.y_stride[0], P.y[1] + r * P.y_stride[1], P.post_x + r * P.post_x_stride,
+                             P.w[0].out_features, red, am);
+      }
+    }
+  }
+  if (tid == 0) TL_MAX(6);
 }
 
 struct TcPlan {
@@ -1018,7 +1095,7 @@ void make_tc_plan(const bsb_weight* ws, int n, int R, TcPlan& pl) {
   const int64_t s_off = off;
   off = align_up64(off + (int64_t)blks * R * 16 * 4, 256);
   const int64_t c_off = off;
-  off = align_up64(off + (int64_t)tiles * 4, 256);
+  off = align_up64(off + (int64_t)(tiles + 1) * 4, 256);   // one counter per row group + the count of finished CTAs
   const int64_t p_off = off;
   off = align_up64(off + part_floats * 4, 256);
   for (int i = 0; i < n; ++i) {
@@ -1086,6 +1163,11 @@ void gemv_tc5_set_wait_limit_ns(unsigned long long ns) { g_wait_ns = ns; }
 #ifdef BSB_TUNING
 static unsigned long long* g_trace = nullptr;
 static int g_dbg = 0;
+// wall-clock timeline: every decode call takes the next 8-slot record of a device buffer the caller provides
+// (slots 0, 1, 3, 4 preset to ~0ull, the others to 0); -1 capacity = off
+static unsigned long long* g_timeline = nullptr;
+static int g_timeline_cap = 0, g_timeline_n = 0;
+void gemv_tc5_set_timeline(unsigned long long* p, int records) { g_timeline = p; g_timeline_cap = records; g_timeline_n = 0; }
 void gemv_tc5_set_dbg(int m) {
   if (m >= 200 && m <= 202) g_force_rt = m - 200;   // row tiles per CTA: 200 = choose, 201 / 202 = forced
   else if (m >= 1000 && m < 2000) g_target_ctas = m - 1000;   // grid size wanted (1000 = default)
@@ -1112,7 +1194,8 @@ int64_t gemv_tc5_workspace_bytes(const bsb_weight* ws, int n_weights, int rows_p
 // rows = 1 or 2 input rows in one pass: x rows x_stride apart, row r of weight i goes to ys[i] + r * y_strides[i]
 // (y_strides may be nullptr when rows == 1)
 int launch_gemv_tc5(const bsb_weight* ws, int n_weights, const __half* x, int64_t x_stride, int rows, __half* const* ys,
-                    const int64_t* y_strides, void* workspace, int64_t workspace_bytes, cudaStream_t s, bool out_f32) {
+                    const int64_t* y_strides, void* workspace, int64_t workspace_bytes, cudaStream_t s, bool out_f32,
+                    const float* x_absmax, const bsb_output_op* op) {
   BSB_CHECK_ARG(n_weights >= 1 && n_weights <= kMaxGroup, "gemv: 1..%d weights per group", kMaxGroup);
   BSB_CHECK_ARG(rows == 1 || (rows == 2 && y_strides != nullptr && x_stride % 8 == 0), "gemv: 1 or 2 rows per pass (16-byte aligned rows)");
   for (int i = 0; i < n_weights; ++i) {
@@ -1149,9 +1232,37 @@ int launch_gemv_tc5(const bsb_weight* ws, int n_weights, const __half* x, int64_
 #ifdef BSB_TUNING
   P.trace = g_trace;
   P.dbg = g_dbg;
+  P.timeline = (g_timeline && g_timeline_n < g_timeline_cap) ? g_timeline + 8 * (g_timeline_n++) : nullptr;
 #endif
   P.x_stride = x_stride;
   P.out_f32 = out_f32 ? 1 : 0;
+  P.absmax_const = 1;
+  P.x_absmax = x_absmax;
+  if (op != nullptr && op->mode != BSB_OUTPUT_NONE) {
+    BSB_CHECK_ARG(op->mode == BSB_OUTPUT_ADD_RMSNORM || op->mode == BSB_OUTPUT_SILU_MUL, "gemv: unknown output op %d", op->mode);
+    BSB_CHECK_ARG(!out_f32, "gemv: an output op needs fp16 outputs");
+    BSB_CHECK_ARG(op->x_out != nullptr && (uintptr_t)op->x_out % 16 == 0 && op->x_stride % 8 == 0, "gemv: output op needs a 16-byte aligned x_out");
+    const int M = ws[0].out_features;
+    BSB_CHECK_ARG(M % 8 == 0, "gemv: an output op needs out_features %% 8 == 0");
+    for (int i = 0; i < n_weights; ++i)
+      BSB_CHECK_ARG((uintptr_t)ys[i] % 16 == 0 && (rows == 1 || y_strides[i] % 8 == 0), "gemv: an output op needs 16-byte aligned output rows");
+    if (op->mode == BSB_OUTPUT_ADD_RMSNORM) {
+      BSB_CHECK_ARG(n_weights == 1, "gemv: add+rmsnorm follows a single projection");
+      BSB_CHECK_ARG(M <= kRowThreads * kRowVecs * 8, "gemv: add+rmsnorm rows hold at most %d elements", kRowThreads * kRowVecs * 8);
+      BSB_CHECK_ARG(op->h != nullptr && op->norm_weight != nullptr && ((uintptr_t)op->h | (uintptr_t)op->norm_weight) % 16 == 0 &&
+                    op->h_stride % 8 == 0, "gemv: add+rmsnorm needs 16-byte aligned h and norm_weight");
+    } else {
+      BSB_CHECK_ARG(n_weights == 2 && ws[1].out_features == M, "gemv: silu*mul follows a gate / up pair of equal width");
+    }
+    P.post_mode = op->mode;
+    P.post_eps = op->eps;
+    P.post_h = reinterpret_cast<__half*>(op->h);
+    P.post_norm_w = reinterpret_cast<const __half*>(op->norm_weight);
+    P.post_x = reinterpret_cast<__half*>(op->x_out);
+    P.post_absmax = op->x_absmax;
+    P.post_h_stride = op->h_stride;
+    P.post_x_stride = op->x_stride;
+  }
   for (int i = 0; i < n_weights; ++i) {
     P.y[i] = ys[i];
     P.y_stride[i] = y_strides ? y_strides[i] : 0;
@@ -1159,6 +1270,7 @@ int launch_gemv_tc5(const bsb_weight* ws, int n_weights, const __half* x, int64_
     if (ws[i].vt_absmax) {
       P.vt_absmax[i] = ws[i].vt_absmax;
     } else {
+      P.absmax_const = 0;
       float* am = (float*)(base + pl.absmax_off[i]);
       if (int rc = launch_vt_absmax(ws[i], am, s)) return rc;
       P.vt_absmax[i] = am;
@@ -1166,7 +1278,7 @@ int launch_gemv_tc5(const bsb_weight* ws, int n_weights, const __half* x, int64_
   }
   {
     const dim3 zgrid(P.n_chunks, pl.total_blocks, rows);
-    cudaError_t le = launch_pdl(zprep_tc5_kernel, zgrid, dim3(256), 0, s, P, x);
+    cudaError_t le = launch_pdl(zprep_tc5_kernel, zgrid, dim3(kZprepThreads), 0, s, P, x);
     if (le != cudaSuccess) {
       set_error("launch of zprep_tc5_kernel failed: %s", cudaGetErrorString(le));
       return BSB_ECUDA;

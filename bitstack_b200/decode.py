@@ -123,6 +123,11 @@ class BitStackLlamaDecoder:
                  batch=1, fused_level=6, rank=0, world_size=1, group=None, fused_glue=True):
         self.shape, self.device, self.max_len, self.batch = shape, torch.device(device), max_len, batch
         self.fused_glue = fused_glue
+        # Row operations between projections done by the projection calls themselves (`forward_grouped` hooks): three
+        # launches fewer per layer, but the operation then runs on ONE thread block at the very end of the decode
+        # kernel, behind two more device-wide round trips; measured 237 tokens/s against 252 with the stand-alone
+        # kernels (which hand max |x| to the next call) on the 8B workload.  Off by default.
+        self.fuse_output_ops = False
         self.rank, self.world, self.group = rank, world_size, group
         s = shape
         assert s.n_kv_heads % world_size == 0 and s.intermediate % (128 * world_size) == 0 and s.vocab % world_size == 0
@@ -173,11 +178,11 @@ class BitStackLlamaDecoder:
         rot = torch.cat([-x[..., half:], x[..., :half]], dim=-1)
         return x * cos + rot * sin
 
-    def _row_parallel(self, mod, x):
+    def _row_parallel(self, mod, x, x_absmax=None):
         """A column-sharded projection (o / down): on one device the plain forward; tensor parallel, fp32 partial sums
         of this rank's input columns, summed over the ranks and rounded to fp16 once."""
         if self.world == 1:
-            return mod(x)
+            return forward_grouped([mod], x, x_absmax=x_absmax)[0] if x_absmax is not None else mod(x)
         part = mod.forward_partial(x)
         torch.distributed.all_reduce(part, group=self.group)
         return part.half()
@@ -233,22 +238,47 @@ class BitStackLlamaDecoder:
         h = self.embed.index_select(0, self.tokens).contiguous()            # [B, hidden], residual stream
         fused_att = hd in (64, 128) and self.max_len <= 8192
         mask = None if fused_att else (self.arange <= self.pos).view(1, 1, 1, self.max_len)
+        if self.world == 1 and self.fuse_output_ops and B <= 6:
+            return self._decode_fused_output_ops(h, fused_att, mask)
         delta = None                                                         # output of the previous MLP, not yet added to h
+        # the stand-alone row kernels deliver max |x| with x: the operand preparation of the next call need not scan x
+        am = torch.empty(B, dtype=torch.float32, device=self.device) if B <= 6 else None
         for i, lay in enumerate(self.layers):
             qkv = [lay["self_attn.q_proj"], lay["self_attn.k_proj"], lay["self_attn.v_proj"]]
-            q, k, v = forward_grouped(qkv, glue.add_rmsnorm(h, delta, lay["in_norm"], s.rms_eps))
-            if fused_att:
-                att = glue.decode_attention(q, k, v, self.cos, self.sin, self.pos, self.k_cache[i], self.v_cache[i],
-                                            self.q_local, self.kv_local, hd)
-            else:
-                glue.rope_cache(q, k, v, self.cos, self.sin, self.pos, self.k_cache[i], self.v_cache[i],
-                                self.q_local, self.kv_local, hd)
-                att = F.scaled_dot_product_attention(q.view(B, self.q_local, 1, hd), self.k_cache[i], self.v_cache[i],
-                                                     attn_mask=mask, enable_gqa=True).reshape(B, self.q_local * hd)
+            q, k, v = forward_grouped(qkv, glue.add_rmsnorm(h, delta, lay["in_norm"], s.rms_eps, absmax=am), x_absmax=am)
+            att = self._attention(i, q, k, v, fused_att, mask)
             o = self._row_parallel(lay["self_attn.o_proj"], att)
-            g, u = forward_grouped([lay["mlp.gate_proj"], lay["mlp.up_proj"]], glue.add_rmsnorm(h, o, lay["post_norm"], s.rms_eps))
-            delta = self._row_parallel(lay["mlp.down_proj"], glue.silu_mul(g, u))
+            g, u = forward_grouped([lay["mlp.gate_proj"], lay["mlp.up_proj"]],
+                                   glue.add_rmsnorm(h, o, lay["post_norm"], s.rms_eps, absmax=am), x_absmax=am)
+            a = glue.silu_mul(g, u, absmax=am)
+            delta = self._row_parallel(lay["mlp.down_proj"], a, x_absmax=am)
         x = glue.add_rmsnorm(h, delta, self.final_norm, s.rms_eps)
+        return x @ self.lm_head.t()
+
+    def _attention(self, i, q, k, v, fused_att, mask):
+        s, B, hd = self.shape, self.batch, self.shape.head_dim
+        if fused_att:
+            return glue.decode_attention(q, k, v, self.cos, self.sin, self.pos, self.k_cache[i], self.v_cache[i],
+                                         self.q_local, self.kv_local, hd)
+        glue.rope_cache(q, k, v, self.cos, self.sin, self.pos, self.k_cache[i], self.v_cache[i], self.q_local, self.kv_local, hd)
+        return F.scaled_dot_product_attention(q.view(B, self.q_local, 1, hd), self.k_cache[i], self.v_cache[i],
+                                              attn_mask=mask, enable_gqa=True).reshape(B, self.q_local * hd)
+
+    def _decode_fused_output_ops(self, h, fused_att, mask):
+        """The decode step with the row operations between projections done by the projection calls themselves
+        (`forward_grouped` hooks): the o and down calls add their output to the residual stream and normalise it for
+        the next projection, the gate / up call applies SiLU * up, and each hands max |x| to the next call.  Per layer:
+        four projection calls and the attention, no other launch.  Same roundings as the stand-alone kernels."""
+        s = self.shape
+        am = [torch.empty(self.batch, dtype=torch.float32, device=self.device) for _ in range(3)]
+        x = glue.add_rmsnorm(h, None, self.layers[0]["in_norm"], s.rms_eps, absmax=am[0])
+        for i, lay in enumerate(self.layers):
+            q, k, v = forward_grouped([lay["self_attn.q_proj"], lay["self_attn.k_proj"], lay["self_attn.v_proj"]], x, x_absmax=am[0])
+            att = self._attention(i, q, k, v, fused_att, mask)
+            _, x = forward_grouped([lay["self_attn.o_proj"]], att, add_rmsnorm=(h, lay["post_norm"], s.rms_eps), out_absmax=am[1])
+            _, _, x = forward_grouped([lay["mlp.gate_proj"], lay["mlp.up_proj"]], x, x_absmax=am[1], silu_mul=True, out_absmax=am[2])
+            nxt = self.layers[i + 1]["in_norm"] if i + 1 < len(self.layers) else self.final_norm
+            _, x = forward_grouped([lay["mlp.down_proj"]], x, x_absmax=am[2], add_rmsnorm=(h, nxt, s.rms_eps), out_absmax=am[0])
         return x @ self.lm_head.t()
 
     # ------------------------------------------------------------------ public API

@@ -15,16 +15,20 @@ def _s(t):
     return torch.cuda.current_stream(t.device).cuda_stream
 
 
-def add_rmsnorm(h: torch.Tensor, delta, weight: torch.Tensor, eps: float) -> torch.Tensor:
-    """In place h += delta (skipped when delta is None); returns rmsnorm(h) * weight.  h: [rows, hidden] fp16."""
+def add_rmsnorm(h: torch.Tensor, delta, weight: torch.Tensor, eps: float, absmax: torch.Tensor = None) -> torch.Tensor:
+    """In place h += delta (skipped when delta is None); returns rmsnorm(h) * weight.  h: [rows, hidden] fp16.
+    `absmax` (fp32 [rows], optional) receives max |result| per row."""
     assert h.is_cuda and h.dtype == torch.float16 and h.is_contiguous() and h.dim() == 2
     if delta is not None:
         delta = delta.reshape(h.shape)
         assert delta.dtype == torch.float16 and delta.is_contiguous()
+    if absmax is not None:
+        assert absmax.dtype == torch.float32 and absmax.is_contiguous() and absmax.numel() >= h.shape[0]
     y = torch.empty_like(h)
     with torch.cuda.device(h.device):
         rc = _lib.load().bsb_add_rmsnorm(h.data_ptr(), None if delta is None else delta.data_ptr(), weight.data_ptr(),
-                                         float(eps), y.data_ptr(), h.shape[0], h.shape[1], _s(h))
+                                         float(eps), y.data_ptr(), None if absmax is None else absmax.data_ptr(),
+                                         h.shape[0], h.shape[1], _s(h))
     _lib.check(rc, "bsb_add_rmsnorm")
     return y
 
@@ -80,10 +84,13 @@ def greedy_step(logits: torch.Tensor, tokens: torch.Tensor, pos) -> torch.Tensor
     return tokens
 
 
-def silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+def silu_mul(gate: torch.Tensor, up: torch.Tensor, absmax: torch.Tensor = None) -> torch.Tensor:
+    """silu(gate) * up on [rows, n] fp16 (n % 8 == 0); `absmax` (fp32 [rows], optional) receives max |result| per row."""
     assert gate.is_cuda and gate.dtype == torch.float16 and gate.is_contiguous() and up.is_contiguous()
+    g2 = gate.reshape(-1, gate.shape[-1])
     out = torch.empty_like(gate)
     with torch.cuda.device(gate.device):
-        rc = _lib.load().bsb_silu_mul(gate.data_ptr(), up.data_ptr(), out.data_ptr(), gate.numel(), _s(gate))
+        rc = _lib.load().bsb_silu_mul(gate.data_ptr(), up.data_ptr(), out.data_ptr(),
+                                      None if absmax is None else absmax.data_ptr(), g2.shape[0], g2.shape[1], _s(gate))
     _lib.check(rc, "bsb_silu_mul")
     return out

@@ -6,6 +6,10 @@ bitstack/utils/decompose.py:7-21) without `accelerate`:
 * `retrieve_compression_config(configs, max_memory_MB)` and `generate_configs(...)` have the reference's
   names, arguments, results and error (model_utils.py:53-66, 179-187).  `configs` is the list stored
   in a checkpoint's `compression_config.json`: `[{"memory": bytes, "layers": {"layer.3.self_attn.q_proj": 5, ...}}, ...]`.
+* `load_bitstack_linears(..., rank, world)` places the packed blocks across devices for tensor parallelism: a rank
+  reads only its output rows of q/k/v/gate/up (one contiguous byte range of every `qweight_j` and `u_j`) or its input
+  columns of o/down (a strided cut of `qweight_j` and `vt_j`), as `bitstack_b200.sharding` defines them.  The reference
+  places whole layers on devices through accelerate (model_utils.py:189-205); it has no tensor parallelism.
 * `load_bitstack_linears(...)` builds one `BitStackLinear` per decomposed projection, named
   `layer.{i}.{sub}` as `decompose()` names them, and reads ONLY the first `nb` residual blocks of each
   (`qweight_{j}`, `u_{j}`, `vt_{j}`, j < nb: the checkpoint keys of bitstack/modules/BitStackLinear.py:38-46)
@@ -27,6 +31,7 @@ from typing import Dict, Iterable, List, Mapping, Optional, Tuple
 import numpy as np
 import torch
 
+from . import sharding
 from .linear import BitStackLinear
 
 _DTYPES = {
@@ -114,6 +119,28 @@ class SafetensorsFile:
             raise ValueError(f"{self.path}: short read of {name}")
         dst.copy_(torch.from_numpy(raw).view(t_dt).reshape(dst.shape), non_blocking=False)
 
+    def read_rows_into(self, name: str, row_begin: int, row_end: int, dst: torch.Tensor) -> None:
+        """Copies rows [row_begin, row_end) of tensor `name`, seen as a matrix whose first dimension has the stored
+        tensor's leading extent (any trailing shape), into `dst`: one contiguous byte range of the file."""
+        e = self.entries[name]
+        np_dt, t_dt = _DTYPES[e["dtype"]]
+        shape = e["shape"]
+        n0 = int(shape[0]) if shape else 1
+        total = int(np.prod(shape, dtype=np.int64))
+        if not (0 <= row_begin <= row_end <= n0):
+            raise ValueError(f"{name}: rows [{row_begin}, {row_end}) outside 0..{n0}")
+        per_row = (total // n0) * np.dtype(np_dt).itemsize if n0 else 0
+        nbytes = (row_end - row_begin) * per_row
+        if dst.dtype != t_dt or dst.numel() * dst.element_size() != nbytes:
+            raise ValueError(f"{name}: destination does not hold rows [{row_begin}, {row_end})")
+        if nbytes == 0:
+            return
+        b = e["data_offsets"][0]
+        raw = np.fromfile(self.path, dtype=np.uint8, count=nbytes, offset=self.data_start + b + row_begin * per_row)
+        if raw.size != nbytes:
+            raise ValueError(f"{self.path}: short read of {name}")
+        dst.copy_(torch.from_numpy(raw).view(t_dt).reshape(dst.shape), non_blocking=False)
+
     def read(self, name: str, device="cpu") -> torch.Tensor:
         dt, shape = self.info(name)
         out = torch.empty(shape, dtype=dt, device=device)
@@ -180,6 +207,11 @@ class Checkpoint:
             raise KeyError(f"{name} is not in the checkpoint at {self.directory}")
         self._file(self.weight_map[name]).read_into(name, dst)
 
+    def read_rows_into(self, name: str, row_begin: int, row_end: int, dst: torch.Tensor) -> None:
+        if name not in self.weight_map:
+            raise KeyError(f"{name} is not in the checkpoint at {self.directory}")
+        self._file(self.weight_map[name]).read_rows_into(name, row_begin, row_end, dst)
+
     def compression_configs(self):
         """The list stored by the reference in `compression_config.json` (main.py:168-184)."""
         with open(os.path.join(self.directory, "compression_config.json")) as f:
@@ -210,7 +242,8 @@ def stored_blocks(ckpt: Checkpoint, prefix: str) -> int:
 @torch.no_grad()
 def load_bitstack_linears(directory: str, compression_config: Optional[Mapping[str, int]] = None, *, max_memory_MB=None,
                           niter: Optional[int] = None, k: int = 16, device="cuda", fused_level: int = 6,
-                          names: Optional[Iterable[str]] = None) -> Dict[str, BitStackLinear]:
+                          names: Optional[Iterable[str]] = None, rank: int = 0, world: int = 1,
+                          shard_rule=None) -> Dict[str, BitStackLinear]:
     """Builds the BitStack projections of a decomposed checkpoint with only the blocks the budget allows.
 
     Block counts come from `compression_config` ({`layer.{i}.{sub}`: blocks}), else from the checkpoint's
@@ -218,6 +251,12 @@ def load_bitstack_linears(directory: str, compression_config: Optional[Mapping[s
     as `decompose(init_only=True)` (decompose.py:14-19).  Each module comes back stacked
     (`stack_blocks()` done: `qweight [nb, out*in/8]`, `u [nb, out, k]`, `vt [nb, k, in]`), named, and with
     `w_bit` = the loaded block count.
+
+    `world > 1` places the blocks for tensor parallelism: this `rank` gets the output-row shard of a projection
+    (`shard_rule(name) == "rows"`: a contiguous byte range of each `qweight_j` / `u_j` is read, nothing else of them
+    touches memory) or its input-column shard (`"cols"`: partial-sum outputs, see `BitStackLinear.forward_partial`).
+    The default rule shards `o_proj` / `down_proj` by columns and every other projection by rows; a rule may return
+    None to keep a projection whole.  The module then has the shard's `out_features` / `in_features`.
     """
     ckpt = Checkpoint(directory)
     if compression_config is None and max_memory_MB is not None:
@@ -227,6 +266,10 @@ def load_bitstack_linears(directory: str, compression_config: Optional[Mapping[s
     projections = discover_projections(ckpt)
     wanted = list(names) if names is not None else sorted(projections, key=lambda s: (int(s.split(".")[1]), s))
     dev = torch.device(device)
+    if world < 1 or not (0 <= rank < world):
+        raise ValueError(f"rank {rank} outside world size {world}")
+    if shard_rule is None:
+        shard_rule = default_shard_rule
     out: Dict[str, BitStackLinear] = {}
     for lname in wanted:
         if lname not in projections:
@@ -243,23 +286,63 @@ def load_bitstack_linears(directory: str, compression_config: Optional[Mapping[s
         if kk != k or vt_shape[0] != k:
             raise ValueError(f"{lname}: checkpoint rank is {kk}, k={k} was asked for")
         has_bias = f"{prefix}.bias" in ckpt
-        mod = BitStackLinear(w_bit=0, in_features=in_features, out_features=out_features, k=k, bias=has_bias,
+        kind = shard_rule(lname) if world > 1 else None
+        if kind not in (None, "rows", "cols"):
+            raise ValueError(f"{lname}: shard rule returned {kind!r}")
+        full_out, full_in = out_features, in_features
+        if kind == "rows":
+            if full_out % world or (full_out // world * full_in) % 8:
+                raise ValueError(f"{lname}: {full_out} output rows cannot be cut into {world} byte-aligned shards")
+            out_features = full_out // world
+        elif kind == "cols":
+            if full_in % (8 * world):
+                raise ValueError(f"{lname}: {full_in} input columns cannot be cut into {world} byte-aligned shards")
+            in_features = full_in // world
+        # a column shard's outputs are partial sums: only rank 0 adds the bias, so that the all-reduce adds it once
+        keep_bias = has_bias and (kind != "cols" or rank == 0)
+        mod = BitStackLinear(w_bit=0, in_features=in_features, out_features=out_features, k=k, bias=keep_bias,
                              no_avd=False, dev=dev, fused_level=fused_level)
         mod.name = lname
         q = torch.empty(nb, out_features * in_features // 8, dtype=torch.uint8, device=dev)
         u = torch.empty(nb, out_features, k, dtype=torch.float16, device=dev)
         vt = torch.empty(nb, k, in_features, dtype=torch.float16, device=dev)
+        r0 = rank * out_features
         for j in range(nb):
-            ckpt.read_into(f"{prefix}.qweight_{j}", q[j])
-            ckpt.read_into(f"{prefix}.u_{j}", u[j])
-            ckpt.read_into(f"{prefix}.vt_{j}", vt[j])
-        if has_bias:
-            ckpt.read_into(f"{prefix}.bias", mod.bias)
+            if kind == "rows":
+                # rows [r0, r0 + out) of the sign matrix are one byte range of the flat qweight_j
+                row_bytes = full_in // 8
+                ckpt.read_rows_into(f"{prefix}.qweight_{j}", r0 * row_bytes, (r0 + out_features) * row_bytes, q[j])
+                ckpt.read_rows_into(f"{prefix}.u_{j}", r0, r0 + out_features, u[j])
+                ckpt.read_into(f"{prefix}.vt_{j}", vt[j])
+            elif kind == "cols":
+                hq = torch.empty(1, full_out * full_in // 8, dtype=torch.uint8)
+                hu = torch.empty(1, full_out, k, dtype=torch.float16)
+                hvt = torch.empty(1, k, full_in, dtype=torch.float16)
+                ckpt.read_into(f"{prefix}.qweight_{j}", hq[0])
+                ckpt.read_into(f"{prefix}.u_{j}", hu[0])
+                ckpt.read_into(f"{prefix}.vt_{j}", hvt[0])
+                sq, su, svt = sharding.shard_cols(hq, hu, hvt, full_out, full_in, rank, world)
+                q[j].copy_(sq[0]); u[j].copy_(su[0]); vt[j].copy_(svt[0])
+            else:
+                ckpt.read_into(f"{prefix}.qweight_{j}", q[j])
+                ckpt.read_into(f"{prefix}.u_{j}", u[j])
+                ckpt.read_into(f"{prefix}.vt_{j}", vt[j])
+        if keep_bias:
+            if kind == "rows":
+                ckpt.read_rows_into(f"{prefix}.bias", r0, r0 + out_features, mod.bias)
+            else:
+                ckpt.read_into(f"{prefix}.bias", mod.bias)
         mod.qweight, mod.u, mod.vt = q, u, vt
         mod.w_bit = nb
         mod._stacked_blocks = nb
         out[lname] = mod
     return out
+
+
+def default_shard_rule(name: str) -> str:
+    """Tensor-parallel cut of a decoder layer's projections: the two projections that consume a sharded activation
+    (attention output, MLP down) are cut by input columns, all others by output rows."""
+    return "cols" if name.endswith(("o_proj", "down_proj")) else "rows"
 
 
 def checkpoint_budget_table(directory: str, k: int = 16) -> Dict[str, int]:

@@ -128,14 +128,43 @@ int bsb_linear_forward_grouped(const bsb_weight* ws, int32_t n_weights, const ui
                                const int64_t* y_strides, void* workspace, int64_t workspace_bytes,
                                int algo, void* stream);
 
+/* bsb_linear_forward_grouped with the two hooks that let a decode step (rows <= 6) run without separate launches
+ * for the row operations between its projections.  No counterpart in the reference, which leaves those operations
+ * to the Hugging Face modules around the projections (bitstack/utils/scale_utils.py:3-5 names the classes).
+ *   x_absmax  optional fp32 [rows]: max |x| of every input row, as the operation that produced x delivered it
+ *             (an output op below, bsb_add_rmsnorm, bsb_silu_mul).  The decode kernel's operand preparation
+ *             then does not have to scan x for it.  NULL = computed inside.
+ *   op        optional output op, applied by the last thread block of the decode kernel once every output of the
+ *             call is in memory, with the roundings of the stand-alone bsb_add_rmsnorm / bsb_silu_mul:
+ *               BSB_OUTPUT_ADD_RMSNORM (one weight): h += y; x_out = rmsnorm(h) * norm_weight
+ *               BSB_OUTPUT_SILU_MUL (a gate / up pair of equal width): x_out = silu(y[0]) * y[1]
+ *             x_absmax (may be NULL) receives max |x_out| per row.  The ys are still written.
+ * Both hooks need the decode path: rows <= 6 and every weight with k == 16, in_features % 128 == 0, 16-byte
+ * aligned tensors and at least one active block; otherwise BSB_EINVAL (use the stand-alone kernels). */
+enum { BSB_OUTPUT_NONE = 0, BSB_OUTPUT_ADD_RMSNORM = 1, BSB_OUTPUT_SILU_MUL = 2 };
+typedef struct bsb_output_op {
+  int32_t mode;
+  float eps;                   /* rmsnorm epsilon */
+  uint16_t* h;                 /* ADD_RMSNORM: fp16 residual stream [rows][out_features], updated in place */
+  const uint16_t* norm_weight; /* ADD_RMSNORM: fp16 [out_features] */
+  uint16_t* x_out;             /* fp16 [rows][out_features] */
+  float* x_absmax;             /* fp32 [rows] or NULL */
+  int64_t h_stride;            /* elements between rows of h */
+  int64_t x_stride;            /* elements between rows of x_out */
+} bsb_output_op;
+int bsb_linear_forward_grouped_ex(const bsb_weight* ws, int32_t n_weights, const uint16_t* x, int64_t rows,
+                                  int64_t x_stride, const float* x_absmax, uint16_t* const* ys,
+                                  const int64_t* y_strides, const bsb_output_op* op, void* workspace,
+                                  int64_t workspace_bytes, void* stream);
+
 /* Scratch bytes bsb_linear_forward_grouped needs. */
 int64_t bsb_linear_grouped_workspace_bytes(const bsb_weight* ws, int32_t n_weights, int64_t rows, int algo);
 
 /* ---- decode-time glue (no counterpart in the reference, which leaves these ops to the Hugging
  * Face Llama modules; bitstack/utils/scale_utils.py:3-5 names the classes it wraps) ------------
  * bsb_add_rmsnorm: h[rows][hidden] += delta (if delta != NULL; fp16 residual stream, written
- *   back), then y = h * rsqrt(mean(h^2) + eps) * weight with fp32 arithmetic.  hidden % 8 == 0,
- *   hidden <= 16384, 16-byte aligned buffers.
+ *   back), then y = h * rsqrt(mean(h^2) + eps) * weight with fp32 arithmetic; y_absmax (fp32 [rows], may be
+ *   NULL) receives max |y| per row.  hidden % 8 == 0, hidden <= 16384, 16-byte aligned buffers.
  * bsb_rope_cache: rotary embedding at position *pos (device scalar) on q[batch][q_heads*dim] in
  *   place and on k, which is written with v into caches [batch][kv_heads][max_len][dim];
  *   cos/sin tables are [max_len][dim] in the "rotate half" convention.
@@ -146,9 +175,10 @@ int64_t bsb_linear_grouped_workspace_bytes(const bsb_weight* ws, int32_t n_weigh
  *   first use and is left ready for the next call; calls sharing a scratch must be stream-ordered.
  * bsb_greedy_step: tokens[b] = first index of the maximum of logits[b][0..vocab) (fp16 rows row_stride apart), then
  *   *pos += 1 (pos may be NULL): the sampling and bookkeeping of a greedy decode step in one launch.
- * bsb_silu_mul: out = silu(gate) * up over n fp16 elements. */
-int bsb_add_rmsnorm(uint16_t* h, const uint16_t* delta, const uint16_t* weight, float eps, uint16_t* y, int64_t rows,
-                    int32_t hidden, void* stream);
+ * bsb_silu_mul: out = silu(gate) * up on [rows][n] fp16 (n % 8 == 0, 16-byte aligned); out_absmax (fp32 [rows], may be
+ *   NULL) receives max |out| per row. */
+int bsb_add_rmsnorm(uint16_t* h, const uint16_t* delta, const uint16_t* weight, float eps, uint16_t* y, float* y_absmax,
+                    int64_t rows, int32_t hidden, void* stream);
 int bsb_rope_cache(uint16_t* q, const uint16_t* k, const uint16_t* v, const uint16_t* cos_table, const uint16_t* sin_table,
                    const int64_t* pos, uint16_t* k_cache, uint16_t* v_cache, int32_t batch, int32_t q_heads,
                    int32_t kv_heads, int32_t head_dim, int32_t max_len, void* stream);
@@ -159,7 +189,8 @@ int bsb_decode_attention(const uint16_t* q, const uint16_t* k, const uint16_t* v
 int64_t bsb_decode_attention_scratch_bytes(int32_t batch, int32_t q_heads, int32_t head_dim);
 int bsb_greedy_step(const uint16_t* logits, int64_t batch, int64_t vocab, int64_t row_stride, int64_t* tokens, int64_t* pos,
                     void* stream);
-int bsb_silu_mul(const uint16_t* gate, const uint16_t* up, uint16_t* out, int64_t n, void* stream);
+int bsb_silu_mul(const uint16_t* gate, const uint16_t* up, uint16_t* out, float* out_absmax, int64_t rows, int32_t n,
+                 void* stream);
 
 /* Forward for callers that may not allocate device memory.  It has no counterpart in the
  * reference.  Some hosts hand a plug-in a fixed set of buffers and forbid any device

@@ -150,3 +150,44 @@ def test_loaded_checkpoint_runs_on_the_gpu_path(tmp_path):
     x_np = orc.synthetic_input(1, 512, seed=77)
     y = mod(torch.from_numpy(x_np).to(dev)).float().cpu().numpy()
     assert orc.max_normalised_error(y, orc.forward_f64(x_np, q, u, vt, 1, None)) <= 4e-3
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_tensor_parallel_placement_reads_this_ranks_shard(tmp_path, world):
+    """`rank` / `world`: every rank's modules hold exactly `sharding.shard_rows` / `shard_cols` of the full tensors,
+    the row shards concatenate and the column-shard partial sums add up to the single-device float64 result, and a
+    bias lives on rank 0 only for a column-sharded projection."""
+    from bitstack_b200 import sharding
+    tensors, shapes = _fake_checkpoint(tmp_path, n_layers=2, blocks=3, shards=2, seed=5)
+    cfg = {f"layer.{i}.{sub}": 2 + (i + k) % 2 for i in range(2) for k, sub in enumerate(shapes)}
+    full = loader.load_bitstack_linears(str(tmp_path), cfg, device="cpu")
+    per_rank = [loader.load_bitstack_linears(str(tmp_path), cfg, device="cpu", rank=r, world=world) for r in range(world)]
+    x_rng = np.random.default_rng(1)
+    for name, mod in full.items():
+        m, n = mod.out_features, mod.in_features
+        nb = cfg[name]
+        kind = loader.default_shard_rule(name)
+        x = x_rng.standard_normal((2, n)).astype(np.float16)
+        y_full = orc.forward_f64(x, mod.qweight.numpy(), mod.u.numpy(), mod.vt.numpy(), nb)
+        acc = []
+        for r in range(world):
+            sm = per_rank[r][name]
+            cut = sharding.shard_rows if kind == "rows" else sharding.shard_cols
+            q, u, vt = cut(mod.qweight, mod.u, mod.vt, m, n, r, world)
+            assert torch.equal(sm.qweight, q) and torch.equal(sm.u, u) and torch.equal(sm.vt, vt), (name, r)
+            assert sm.w_bit == nb and sm.name == name
+            if kind == "rows":
+                assert (sm.out_features, sm.in_features) == (m // world, n)
+                acc.append(orc.forward_f64(x, q.numpy(), u.numpy(), vt.numpy(), nb))
+            else:
+                assert (sm.out_features, sm.in_features) == (m, n // world)
+                assert (sm.bias is not None) == (mod.bias is not None and r == 0)
+                lo = r * (n // world)
+                acc.append(orc.forward_f64(x[:, lo:lo + n // world], q.numpy(), u.numpy(), vt.numpy(), nb))
+        y = np.concatenate(acc, axis=1) if kind == "rows" else np.sum(acc, axis=0)
+        assert np.abs(y - y_full).max() <= 1e-9 * max(np.abs(y_full).max(), 1.0)
+    with pytest.raises(ValueError):
+        loader.load_bitstack_linears(str(tmp_path), cfg, device="cpu", rank=2, world=2)
+    # 16 output rows of k_proj cannot be cut into 32 shards
+    with pytest.raises(ValueError):
+        loader.load_bitstack_linears(str(tmp_path), cfg, device="cpu", rank=0, world=32)
