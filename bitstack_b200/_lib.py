@@ -24,18 +24,6 @@ class BsbWeight(C.Structure):
     ]
 
 
-class BsbOutputOp(C.Structure):
-    """Mirror of `struct bsb_output_op`."""
-    _fields_ = [
-        ("mode", C.c_int32), ("eps", C.c_float),
-        ("h", C.c_void_p), ("norm_weight", C.c_void_p), ("x_out", C.c_void_p), ("x_absmax", C.c_void_p),
-        ("h_stride", C.c_int64), ("x_stride", C.c_int64),
-    ]
-
-
-OUTPUT_NONE, OUTPUT_ADD_RMSNORM, OUTPUT_SILU_MUL = 0, 1, 2
-
-
 class BitStackLibraryError(RuntimeError):
     pass
 
@@ -57,7 +45,7 @@ SIGNATURES = {
     "bsb_linear_forward": (C.c_int, [_WP, _P, _I64, _I64, _P, _I64, _P, _I64, C.c_int, _P]),
     "bsb_linear_forward_partial": (C.c_int, [_WP, _P, _I64, _I64, _P, _I64, _P, _I64, C.c_int, _P]),
     "bsb_linear_forward_grouped": (C.c_int, [_WP, _I32, _P, _I64, _I64, C.POINTER(_P), C.POINTER(_I64), _P, _I64, C.c_int, _P]),
-    "bsb_linear_forward_grouped_ex": (C.c_int, [_WP, _I32, _P, _I64, _I64, _P, C.POINTER(_P), C.POINTER(_I64), C.POINTER(BsbOutputOp), _P, _I64, _P]),
+    "bsb_linear_forward_grouped_ex": (C.c_int, [_WP, _I32, _P, _I64, _I64, _P, C.POINTER(_P), C.POINTER(_I64), _P, _I64, _P]),
     "bsb_linear_grouped_workspace_bytes": (_I64, [_WP, _I32, _I64, C.c_int]),
     "bsb_add_rmsnorm": (C.c_int, [_P, _P, _P, C.c_float, _P, _P, _I64, _I32, _P]),
     "bsb_rope_cache": (C.c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _I32, _I32, _I32, _I32, _I32, _P]),

@@ -285,7 +285,7 @@ int bsb_linear_forward_grouped(const bsb_weight* ws, int32_t n_weights, const ui
 
 int bsb_linear_forward_grouped_ex(const bsb_weight* ws, int32_t n_weights, const uint16_t* x, int64_t rows, int64_t x_stride,
                                   const float* x_absmax, uint16_t* const* ys, const int64_t* y_strides,
-                                  const bsb_output_op* op, void* workspace, int64_t workspace_bytes, void* stream) {
+                                  void* workspace, int64_t workspace_bytes, void* stream) {
   BSB_CHECK_ARG(n_weights >= 1 && n_weights <= 4 && ws && ys && y_strides && x, "bad group arguments");
   BSB_CHECK_ARG(rows >= 1 && rows <= kDecodeRowsMax, "the extended call runs on the decode path: 1..%d rows (got %lld)",
                 kDecodeRowsMax, (long long)rows);
@@ -305,16 +305,8 @@ int bsb_linear_forward_grouped_ex(const bsb_weight* ws, int32_t n_weights, const
     const int nr = (rows - r >= 2) ? 2 : 1;
     __half* yr[4];
     for (int i = 0; i < n_weights; ++i) yr[i] = (__half*)ys[i] + r * y_strides[i];
-    bsb_output_op pass_op;
-    if (op != nullptr) {   // this pass's rows of the output op's buffers
-      pass_op = *op;
-      if (pass_op.h) pass_op.h += r * pass_op.h_stride;
-      if (pass_op.x_out) pass_op.x_out += r * pass_op.x_stride;
-      if (pass_op.x_absmax) pass_op.x_absmax += r;
-    }
     if (int rc = launch_gemv_tc5(ws, n_weights, (const __half*)x + r * x_stride, x_stride, nr, yr, y_strides, workspace,
-                                 workspace_bytes, (cudaStream_t)stream, false, x_absmax ? x_absmax + r : nullptr,
-                                 op ? &pass_op : nullptr))
+                                 workspace_bytes, (cudaStream_t)stream, false, x_absmax ? x_absmax + r : nullptr))
       return rc;
     r += nr;
   }

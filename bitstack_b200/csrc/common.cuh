@@ -127,9 +127,9 @@ void gemv_tc5_set_dbg(int mode);
 void gemv_tc5_set_timeline(unsigned long long* device_buffer, int records);
 #endif
 // out_f32: the ys point at fp32 rows (partial sums of a tensor-parallel shard) instead of fp16 ones;
-// x_absmax: optional max |x| per row of this pass; op: optional output stage (its pointers are those of this pass's rows)
+// x_absmax: optional max |x| per row of this pass
 int launch_gemv_tc5(const bsb_weight* ws, int n_weights, const __half* x, int64_t x_stride, int rows, __half* const* ys,
                     const int64_t* y_strides, void* workspace, int64_t workspace_bytes, cudaStream_t s, bool out_f32 = false,
-                    const float* x_absmax = nullptr, const bsb_output_op* op = nullptr);
+                    const float* x_absmax = nullptr);
 
 }  // namespace bsb

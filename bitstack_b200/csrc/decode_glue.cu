@@ -15,7 +15,7 @@ namespace {
 __global__ void __launch_bounds__(kRowThreads) add_rmsnorm_kernel(__half* __restrict__ h, const __half* __restrict__ delta,
                                                                   const __half* __restrict__ weight, float eps,
                                                                   __half* __restrict__ y, int hidden, float* __restrict__ absmax) {
-  __shared__ float red[kRowThreads / 32];
+  __shared__ float red[32];
   pdl_enter();
   const int64_t row = blockIdx.x;
   add_rmsnorm_row<false>(h + row * hidden, delta ? delta + row * hidden : nullptr, weight, eps, y + row * hidden, hidden, red,
@@ -279,9 +279,10 @@ __global__ void __launch_bounds__(1024) greedy_step_kernel(const __half* __restr
 }
 
 // out[row] = silu(gate[row]) * up[row]; optionally max |out[row]|.  One CTA per row (rowops.cuh).
-__global__ void __launch_bounds__(kRowThreads) silu_mul_kernel(const __half* __restrict__ g, const __half* __restrict__ u,
-                                                               __half* __restrict__ out, int n, float* __restrict__ absmax) {
-  __shared__ float red[kRowThreads / 32];
+constexpr int kSiluThreads = 1024;
+__global__ void __launch_bounds__(kSiluThreads) silu_mul_kernel(const __half* __restrict__ g, const __half* __restrict__ u,
+                                                                __half* __restrict__ out, int n, float* __restrict__ absmax) {
+  __shared__ float red[32];
   pdl_enter();
   const int64_t row = blockIdx.x;
   silu_mul_row<false>(g + row * n, u + row * n, out + row * n, n, red, absmax ? absmax + row : nullptr);
@@ -370,7 +371,7 @@ int bsb_silu_mul(const uint16_t* gate, const uint16_t* up, uint16_t* out, float*
   BSB_CHECK_ARG(((uintptr_t)gate | (uintptr_t)up | (uintptr_t)out) % 16 == 0, "buffers must be 16-byte aligned");
   if (rows == 0 || n == 0) return BSB_OK;
   BSB_CHECK_ARG(rows <= 65535 * 32, "too many rows");
-  BSB_CUDA(launch_pdl(silu_mul_kernel, dim3((unsigned)rows), dim3(kRowThreads), 0, (cudaStream_t)stream, (const __half*)gate,
+  BSB_CUDA(launch_pdl(silu_mul_kernel, dim3((unsigned)rows), dim3(kSiluThreads), 0, (cudaStream_t)stream, (const __half*)gate,
                       (const __half*)up, (__half*)out, n, out_absmax));
   return check_launch("silu_mul_kernel");
 }

@@ -31,7 +31,6 @@
 #endif
 
 #include "common.cuh"
-#include "rowops.cuh"
 
 namespace bsb {
 
@@ -64,15 +63,6 @@ struct alignas(64) TcParams {
   bsb_weight w[kMaxGroup];
   const float* vt_absmax[kMaxGroup];
   const float* x_absmax;           // optional max |x| per input row of this pass (from the kernel that produced x), or nullptr
-  // output stage, run by the last CTA to finish once every output of the call is in memory (bsb_output_op):
-  // 1: h += y[0]; x_out = rmsnorm(h) * norm_w     2: x_out = silu(y[0]) * y[1]     (rows of this pass)
-  int post_mode;
-  float post_eps;
-  __half* post_h;
-  const __half* post_norm_w;
-  __half* post_x;
-  float* post_absmax;
-  int64_t post_h_stride, post_x_stride;
   int absmax_const;                // every vt_absmax came from the caller (a constant of the weight), none is computed in front of this call
   __half* y[kMaxGroup];            // fp16 rows, or fp32 rows when out_f32 is set
   int out_f32;                     // outputs are fp32 partial sums of a tensor-parallel shard (no rounding)
@@ -93,7 +83,7 @@ struct alignas(64) TcParams {
   uint8_t* zops;     // [(weight,block)][chunk][16 words][rows][1 KB]
   float* kconst;     // [(weight,block)][chunk][rows][16]
   float* inv_scale;  // [(weight,block)][rows][16]
-  int* counters;     // [row group]: CTAs that have delivered their partial sums; then one more: CTAs that have finished
+  int* counters;     // [row group]: CTAs that have delivered their partial sums
   int* status;       // the library's sticky status word of this device: 0 = fine, else the code of the first wait that gave up
   unsigned long long wait_ns;   // time limit of every wait
 #ifdef BSB_TUNING
@@ -128,7 +118,9 @@ __device__ __forceinline__ uint64_t global_ns() {
   return t;
 }
 // wall-clock marks of one call in the tuning build: slot 0 / 1 / 2 = first Z' CTA entered / first passed its wait / last
-// left; 3 = first decode CTA entered, 4 = first Z' slab consumed, 5 = last epilogue done, 6 = last decode CTA left
+// left; 3 = first decode CTA entered, 4 = first Z' slab consumed, 5 = last epilogue done, 6 = last decode CTA left,
+// 7 = last Z' CTA has the row maximum, 8 / 9 = last decode / Z' CTA entered, 10 = first decode CTA done,
+// 11 = last decode CTA consumed its first Z' slab
 #ifdef BSB_TUNING
 #define TL_MIN(slot) do { if (P.timeline) atomicMin(P.timeline + (slot), (unsigned long long)global_ns()); } while (0)
 #define TL_MAX(slot) do { if (P.timeline) atomicMax(P.timeline + (slot), (unsigned long long)global_ns()); } while (0)
@@ -300,7 +292,7 @@ __global__ void __launch_bounds__(kZprepThreads) zprep_tc5_kernel(const __grid_c
   // this thread's columns: 8c + base + e (c = 0..3, e = 0..3), whose bit class is 7 - base - e = 4 kh + (3 - e)
   const int base = kh ? 0 : 4;
 
-  if (tid == 0) TL_MIN(0);
+  if (tid == 0) { TL_MIN(0); TL_MAX(9); }
   uint2 vq[4];
   const __half* vt = reinterpret_cast<const __half*>(w.vt) + (int64_t)j * w.vt_block_stride + (int64_t)r * N + col0 + base;
 #pragma unroll
@@ -317,13 +309,18 @@ __global__ void __launch_bounds__(kZprepThreads) zprep_tc5_kernel(const __grid_c
   }
   // x and the scratch of the previous call are safe to touch once the kernels before this one are done; then the
   // decode kernel of this call may be scheduled (it waits for this grid before it touches anything written here)
+#ifdef BSB_ZPREP_EARLY   // measurement variant: the decode kernel's CTAs are dispatched while this kernel still waits
+  pdl_trigger();
+  pdl_wait();
+#else
   pdl_enter();
+#endif
   if (tid == 0) TL_MIN(1);
   if (!P.absmax_const) vmax = P.vt_absmax[wi][j * 16 + r];
 
   x += (int64_t)row * P.x_stride;
   if (blockIdx.x == 0 && blockIdx.y == 0 && row == 0)
-    for (int i = tid; i <= P.seg_base[P.n_weights]; i += blockDim.x) P.counters[i] = 0;   // the last one counts finished CTAs
+    for (int i = tid; i < P.seg_base[P.n_weights]; i += blockDim.x) P.counters[i] = 0;
   uint2 xq[4];
 #pragma unroll
   for (int c = 0; c < 4; ++c) xq[c] = in_range ? __ldg(reinterpret_cast<const uint2*>(x + col0 + base + 8 * c)) : make_uint2(0, 0);
@@ -536,7 +533,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
   Smem& S = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
 
   pdl_trigger();   // the kernel after this one may be launched; it waits for this grid before it reads y
-  if (threadIdx.x == 0) TL_MIN(3);
+  if (threadIdx.x == 0) { TL_MIN(3); TL_MAX(8); }
   const int NCH = P.n_chunks;
   const int step0 = first_step_of_cta(P, blockIdx.x);
   const int total = min((int)blockIdx.x < P.n_first ? P.steps_first : P.steps_per_cta, P.step_base[P.n_weights] - step0);   // steps of this CTA
@@ -582,7 +579,9 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
   tc_fence_after();
   const uint32_t tbase = S.tmem_base;
   const uint32_t colA = 2 * kND * kDCols;   // = 128: accumulators D(e, b) at (e*kND + b)*kDCols, operand stages behind them
-  if (warp == 0) TR_ADD(13, t_cta);
+#ifdef BSB_TRACE
+  if (tid == 0) { unsigned smid; asm volatile("mov.u32 %0, %%smid;" : "=r"(smid)); S.trace[13] = smid; }   // slot 13: the multiprocessor
+#endif
 
   if (warp == kWarpLoad) {
     // ---- sign loader: tiled TMA into the tile ring (the packed signs do not depend on the Z'
@@ -649,7 +648,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
         TR_BEGIN(t1);
         if (!mbar_wait(&S.zfull[zslot], (g / kNZr) & 1, wait_ns)) { if (leader) GIVE_UP(2); ok = false; break; }
         TR_ADD(5, t1);
-        if (g == 0 && leader) TL_MIN(4);
+        if (g == 0 && leader) { TL_MIN(4); TL_MAX(11); }
         const uint32_t zaddr = smem_u32(S.zs[zslot]) + (RT == 1 ? (uint32_t)e * 8u * 1024u * R : 0u);
         const uint32_t dcol = tbase + (e * kND + b) * kDCols;
 #pragma unroll 1
@@ -936,8 +935,8 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
   }
   // ---- shared row groups: the last CTA to deliver adds the partial sums in CTA order ------
   const int n_pending = S.n_pending;
-  if (tid == 0) TL_MAX(6);
-  if (n_pending == 0 && P.post_mode == 0) return;
+  if (tid == 0) { TL_MAX(6); TL_MIN(10); }
+  if (n_pending == 0) return;
   asm volatile("griddepcontrol.wait;" ::: "memory");     // the counters were zeroed by the Z' kernel
   for (int q = 0; q < n_pending; ++q) {
     const int wi = S.pending[q][0], rg = S.pending[q][1];
@@ -973,27 +972,6 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
         }
         if (w.bias) sum += __half2float(reinterpret_cast<const __half*>(w.bias)[m]);
         store_y(P, wi, r, m, sum);
-      }
-    }
-  }
-  // ---- output stage: the last CTA to finish applies the row operation that follows the projection in a decoder
-  //      layer to the finished outputs (one CTA's work; saves a kernel and its launch boundary) ------------------
-  if (P.post_mode != 0) {
-    __threadfence();     // this CTA's outputs are visible before it is counted as finished
-    __syncthreads();
-    if (tid == 0) S.last = (atomicAdd(&P.counters[P.seg_base[P.n_weights]], 1) == (int)gridDim.x - 1);
-    __syncthreads();
-    if (S.last) {
-      __threadfence();
-      float* red = reinterpret_cast<float*>(S.zs);   // the operand rings are idle now
-      for (int r = 0; r < R; ++r) {
-        float* am = P.post_absmax ? P.post_absmax + r : nullptr;
-        if (P.post_mode == 1)
-          add_rmsnorm_row<true>(P.post_h + r * P.post_h_stride, P.y[0] + r * P.y_stride[0], P.post_norm_w, P.post_eps,
-                                P.post_x + r * P.post_x_stride, P.w[0].out_features, red, am);
-        else
-          silu_mul_row<true>(P.y[0] + r * P.y_stride[0], P.y[1] + r * P.y_stride[1], P.post_x + r * P.post_x_stride,
-                             P.w[0].out_features, red, am);
       }
     }
   }
@@ -1095,7 +1073,7 @@ void make_tc_plan(const bsb_weight* ws, int n, int R, TcPlan& pl) {
   const int64_t s_off = off;
   off = align_up64(off + (int64_t)blks * R * 16 * 4, 256);
   const int64_t c_off = off;
-  off = align_up64(off + (int64_t)(tiles + 1) * 4, 256);   // one counter per row group + the count of finished CTAs
+  off = align_up64(off + (int64_t)tiles * 4, 256);
   const int64_t p_off = off;
   off = align_up64(off + part_floats * 4, 256);
   for (int i = 0; i < n; ++i) {
@@ -1163,7 +1141,7 @@ void gemv_tc5_set_wait_limit_ns(unsigned long long ns) { g_wait_ns = ns; }
 #ifdef BSB_TUNING
 static unsigned long long* g_trace = nullptr;
 static int g_dbg = 0;
-// wall-clock timeline: every decode call takes the next 8-slot record of a device buffer the caller provides
+// wall-clock timeline: every decode call takes the next 12-slot record of a device buffer the caller provides
 // (slots 0, 1, 3, 4 preset to ~0ull, the others to 0); -1 capacity = off
 static unsigned long long* g_timeline = nullptr;
 static int g_timeline_cap = 0, g_timeline_n = 0;
@@ -1195,7 +1173,7 @@ int64_t gemv_tc5_workspace_bytes(const bsb_weight* ws, int n_weights, int rows_p
 // (y_strides may be nullptr when rows == 1)
 int launch_gemv_tc5(const bsb_weight* ws, int n_weights, const __half* x, int64_t x_stride, int rows, __half* const* ys,
                     const int64_t* y_strides, void* workspace, int64_t workspace_bytes, cudaStream_t s, bool out_f32,
-                    const float* x_absmax, const bsb_output_op* op) {
+                    const float* x_absmax) {
   BSB_CHECK_ARG(n_weights >= 1 && n_weights <= kMaxGroup, "gemv: 1..%d weights per group", kMaxGroup);
   BSB_CHECK_ARG(rows == 1 || (rows == 2 && y_strides != nullptr && x_stride % 8 == 0), "gemv: 1 or 2 rows per pass (16-byte aligned rows)");
   for (int i = 0; i < n_weights; ++i) {
@@ -1232,37 +1210,12 @@ int launch_gemv_tc5(const bsb_weight* ws, int n_weights, const __half* x, int64_
 #ifdef BSB_TUNING
   P.trace = g_trace;
   P.dbg = g_dbg;
-  P.timeline = (g_timeline && g_timeline_n < g_timeline_cap) ? g_timeline + 8 * (g_timeline_n++) : nullptr;
+  P.timeline = (g_timeline && g_timeline_n < g_timeline_cap) ? g_timeline + 12 * (g_timeline_n++) : nullptr;
 #endif
   P.x_stride = x_stride;
   P.out_f32 = out_f32 ? 1 : 0;
   P.absmax_const = 1;
   P.x_absmax = x_absmax;
-  if (op != nullptr && op->mode != BSB_OUTPUT_NONE) {
-    BSB_CHECK_ARG(op->mode == BSB_OUTPUT_ADD_RMSNORM || op->mode == BSB_OUTPUT_SILU_MUL, "gemv: unknown output op %d", op->mode);
-    BSB_CHECK_ARG(!out_f32, "gemv: an output op needs fp16 outputs");
-    BSB_CHECK_ARG(op->x_out != nullptr && (uintptr_t)op->x_out % 16 == 0 && op->x_stride % 8 == 0, "gemv: output op needs a 16-byte aligned x_out");
-    const int M = ws[0].out_features;
-    BSB_CHECK_ARG(M % 8 == 0, "gemv: an output op needs out_features %% 8 == 0");
-    for (int i = 0; i < n_weights; ++i)
-      BSB_CHECK_ARG((uintptr_t)ys[i] % 16 == 0 && (rows == 1 || y_strides[i] % 8 == 0), "gemv: an output op needs 16-byte aligned output rows");
-    if (op->mode == BSB_OUTPUT_ADD_RMSNORM) {
-      BSB_CHECK_ARG(n_weights == 1, "gemv: add+rmsnorm follows a single projection");
-      BSB_CHECK_ARG(M <= kRowThreads * kRowVecs * 8, "gemv: add+rmsnorm rows hold at most %d elements", kRowThreads * kRowVecs * 8);
-      BSB_CHECK_ARG(op->h != nullptr && op->norm_weight != nullptr && ((uintptr_t)op->h | (uintptr_t)op->norm_weight) % 16 == 0 &&
-                    op->h_stride % 8 == 0, "gemv: add+rmsnorm needs 16-byte aligned h and norm_weight");
-    } else {
-      BSB_CHECK_ARG(n_weights == 2 && ws[1].out_features == M, "gemv: silu*mul follows a gate / up pair of equal width");
-    }
-    P.post_mode = op->mode;
-    P.post_eps = op->eps;
-    P.post_h = reinterpret_cast<__half*>(op->h);
-    P.post_norm_w = reinterpret_cast<const __half*>(op->norm_weight);
-    P.post_x = reinterpret_cast<__half*>(op->x_out);
-    P.post_absmax = op->x_absmax;
-    P.post_h_stride = op->h_stride;
-    P.post_x_stride = op->x_stride;
-  }
   for (int i = 0; i < n_weights; ++i) {
     P.y[i] = ys[i];
     P.y_stride[i] = y_strides ? y_strides[i] : 0;

@@ -3,7 +3,8 @@
 //   add + RMSNorm:  h (+= delta);  y = h * rsqrt(mean(h^2) + eps) * weight      (fp32 inside, fp16 residual stream)
 //   SiLU * up:      out = silu(gate) * up                                        (fp16 SiLU, as torch rounds it)
 // Both also deliver max |result| of the row, which the next projection's operand preparation needs.
-// One CTA of kRowThreads threads works on one row; `red` is shared scratch of kRowThreads / 32 floats.
+// One CTA works on one row (add + RMSNorm: kRowThreads threads; SiLU * up: any multiple of 32); `red` is shared
+// scratch of 32 floats.
 #pragma once
 #include <cuda_fp16.h>
 #include <stdint.h>
@@ -19,6 +20,7 @@ __device__ __forceinline__ uint4 row_load(const uint4* p) {
   return COHERENT ? __ldcg(p) : __ldg(p);
 }
 
+// reduction over the CTA (any multiple of 32 threads up to 1024; `red` holds 32 floats)
 __device__ __forceinline__ float row_block_reduce(float v, float* red, bool is_max) {
   for (int o = 16; o > 0; o >>= 1) {
     const float t = __shfl_xor_sync(0xFFFFFFFFu, v, o);
@@ -27,9 +29,9 @@ __device__ __forceinline__ float row_block_reduce(float v, float* red, bool is_m
   __syncthreads();   // `red` may still be read from a previous reduction
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
   __syncthreads();
-  float tot = is_max ? 0.f : 0.f;
-#pragma unroll
-  for (int i = 0; i < kRowThreads / 32; ++i) tot = is_max ? fmaxf(tot, red[i]) : tot + red[i];
+  const int nw = (int)blockDim.x >> 5;
+  float tot = 0.f;
+  for (int i = 0; i < nw; ++i) tot = is_max ? fmaxf(tot, red[i]) : tot + red[i];
   return tot;
 }
 
@@ -110,7 +112,7 @@ __device__ __forceinline__ void silu_mul_row(const __half* __restrict__ gate, co
   const uint4* ur = reinterpret_cast<const uint4*>(up);
   uint4* orow = reinterpret_cast<uint4*>(out);
   float am = 0.f;
-  for (int i = threadIdx.x; i < n / 8; i += kRowThreads) {
+  for (int i = threadIdx.x; i < n / 8; i += (int)blockDim.x) {
     const uint4 gv = row_load<COHERENT>(gr + i), uv = row_load<COHERENT>(ur + i);
     const __half2* gp = reinterpret_cast<const __half2*>(&gv);
     const __half2* up2 = reinterpret_cast<const __half2*>(&uv);

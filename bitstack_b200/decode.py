@@ -123,11 +123,6 @@ class BitStackLlamaDecoder:
                  batch=1, fused_level=6, rank=0, world_size=1, group=None, fused_glue=True):
         self.shape, self.device, self.max_len, self.batch = shape, torch.device(device), max_len, batch
         self.fused_glue = fused_glue
-        # Row operations between projections done by the projection calls themselves (`forward_grouped` hooks): three
-        # launches fewer per layer, but the operation then runs on ONE thread block at the very end of the decode
-        # kernel, behind two more device-wide round trips; measured 237 tokens/s against 252 with the stand-alone
-        # kernels (which hand max |x| to the next call) on the 8B workload.  Off by default.
-        self.fuse_output_ops = False
         self.rank, self.world, self.group = rank, world_size, group
         s = shape
         assert s.n_kv_heads % world_size == 0 and s.intermediate % (128 * world_size) == 0 and s.vocab % world_size == 0
@@ -238,8 +233,6 @@ class BitStackLlamaDecoder:
         h = self.embed.index_select(0, self.tokens).contiguous()            # [B, hidden], residual stream
         fused_att = hd in (64, 128) and self.max_len <= 8192
         mask = None if fused_att else (self.arange <= self.pos).view(1, 1, 1, self.max_len)
-        if self.world == 1 and self.fuse_output_ops and B <= 6:
-            return self._decode_fused_output_ops(h, fused_att, mask)
         delta = None                                                         # output of the previous MLP, not yet added to h
         # the stand-alone row kernels deliver max |x| with x: the operand preparation of the next call need not scan x
         am = torch.empty(B, dtype=torch.float32, device=self.device) if B <= 6 else None
@@ -263,23 +256,6 @@ class BitStackLlamaDecoder:
         glue.rope_cache(q, k, v, self.cos, self.sin, self.pos, self.k_cache[i], self.v_cache[i], self.q_local, self.kv_local, hd)
         return F.scaled_dot_product_attention(q.view(B, self.q_local, 1, hd), self.k_cache[i], self.v_cache[i],
                                               attn_mask=mask, enable_gqa=True).reshape(B, self.q_local * hd)
-
-    def _decode_fused_output_ops(self, h, fused_att, mask):
-        """The decode step with the row operations between projections done by the projection calls themselves
-        (`forward_grouped` hooks): the o and down calls add their output to the residual stream and normalise it for
-        the next projection, the gate / up call applies SiLU * up, and each hands max |x| to the next call.  Per layer:
-        four projection calls and the attention, no other launch.  Same roundings as the stand-alone kernels."""
-        s = self.shape
-        am = [torch.empty(self.batch, dtype=torch.float32, device=self.device) for _ in range(3)]
-        x = glue.add_rmsnorm(h, None, self.layers[0]["in_norm"], s.rms_eps, absmax=am[0])
-        for i, lay in enumerate(self.layers):
-            q, k, v = forward_grouped([lay["self_attn.q_proj"], lay["self_attn.k_proj"], lay["self_attn.v_proj"]], x, x_absmax=am[0])
-            att = self._attention(i, q, k, v, fused_att, mask)
-            _, x = forward_grouped([lay["self_attn.o_proj"]], att, add_rmsnorm=(h, lay["post_norm"], s.rms_eps), out_absmax=am[1])
-            _, _, x = forward_grouped([lay["mlp.gate_proj"], lay["mlp.up_proj"]], x, x_absmax=am[1], silu_mul=True, out_absmax=am[2])
-            nxt = self.layers[i + 1]["in_norm"] if i + 1 < len(self.layers) else self.final_norm
-            _, x = forward_grouped([lay["mlp.down_proj"]], x, x_absmax=am[2], add_rmsnorm=(h, nxt, s.rms_eps), out_absmax=am[0])
-        return x @ self.lm_head.t()
 
     # ------------------------------------------------------------------ public API
     @torch.no_grad()

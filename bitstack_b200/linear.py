@@ -297,15 +297,12 @@ class BitStackLinear(nn.Module):
         return y.reshape(*x.shape[:-1], self.out_features)
 
 
-def forward_grouped(modules, x, algo=_lib.ALGO_AUTO, *, x_absmax=None, add_rmsnorm=None, silu_mul=False, out_absmax=None):
+def forward_grouped(modules, x, algo=_lib.ALGO_AUTO, *, x_absmax=None):
     """Apply several BitStackLinear modules to the same input with one fused launch
     sequence (q/k/v or gate/up of a decoder layer).  Returns a list of outputs.
 
-    Decode-step hooks (rows <= 6, see `bsb_linear_forward_grouped_ex`): `x_absmax` (fp32 [rows]) is max |x| per row as
-    the producer of x delivered it; `add_rmsnorm=(h, norm_weight, eps)` after a single projection makes the call also
-    do h += y in place and return rmsnorm(h) * norm_weight as an extra last element of the result list;
-    `silu_mul=True` after a gate / up pair returns silu(y0) * y1 as that extra element; `out_absmax` (fp32 [rows])
-    receives max |extra| per row."""
+    `x_absmax` (fp32 [rows], decode path only: rows <= 6): max |x| per row as the producer of x delivered it
+    (`glue.add_rmsnorm` / `glue.silu_mul`), so that the operand preparation does not scan x for it."""
     x2 = x.reshape(-1, x.shape[-1])
     if x2.stride(-1) != 1:
         x2 = x2.contiguous()
@@ -319,8 +316,6 @@ def forward_grouped(modules, x, algo=_lib.ALGO_AUTO, *, x_absmax=None, add_rmsno
     yptrs = (C.c_void_p * n)(*[y.data_ptr() for y in ys])
     ystr = (C.c_int64 * n)(*[m.out_features for m in modules])
     lib = _lib.load()
-    extended = x_absmax is not None or add_rmsnorm is not None or silu_mul
-    extra = None
     with torch.cuda.device(x.device):
         need = lib.bsb_linear_grouped_workspace_bytes(descs, n, rows, algo)
         if need < 0:
@@ -328,32 +323,12 @@ def forward_grouped(modules, x, algo=_lib.ALGO_AUTO, *, x_absmax=None, add_rmsno
         ws = get_workspace(x.device, need)
         stream = torch.cuda.current_stream(x.device).cuda_stream
         xs = x2.stride(0) if rows > 1 else x2.shape[-1]
-        if not extended:
+        if x_absmax is None:
             rc = lib.bsb_linear_forward_grouped(descs, n, x2.data_ptr(), rows, xs, yptrs, ystr, ws.data_ptr(), ws.numel(),
                                                 algo, stream)
         else:
-            op = _lib.BsbOutputOp()
-            if add_rmsnorm is not None or silu_mul:
-                extra = torch.empty(rows, modules[0].out_features, dtype=torch.float16, device=x.device)
-                op.x_out, op.x_stride = extra.data_ptr(), extra.stride(0)
-                if out_absmax is not None:
-                    assert out_absmax.dtype == torch.float32 and out_absmax.numel() >= rows
-                    op.x_absmax = out_absmax.data_ptr()
-            if add_rmsnorm is not None:
-                h, norm_w, eps = add_rmsnorm
-                h2 = h.reshape(rows, -1)
-                assert h2.dtype == torch.float16 and h2.stride(-1) == 1 and h2.shape[1] == modules[0].out_features
-                assert norm_w.dtype == torch.float16 and norm_w.is_contiguous()
-                op.mode, op.eps, op.h, op.h_stride, op.norm_weight = _lib.OUTPUT_ADD_RMSNORM, float(eps), h2.data_ptr(), h2.stride(0), norm_w.data_ptr()
-            elif silu_mul:
-                op.mode = _lib.OUTPUT_SILU_MUL
-            if x_absmax is not None:
-                assert x_absmax.dtype == torch.float32 and x_absmax.numel() >= rows
-            rc = lib.bsb_linear_forward_grouped_ex(descs, n, x2.data_ptr(), rows, xs,
-                                                   None if x_absmax is None else x_absmax.data_ptr(), yptrs, ystr,
-                                                   C.byref(op), ws.data_ptr(), ws.numel(), stream)
+            assert x_absmax.dtype == torch.float32 and x_absmax.is_cuda and x_absmax.numel() >= rows
+            rc = lib.bsb_linear_forward_grouped_ex(descs, n, x2.data_ptr(), rows, xs, x_absmax.data_ptr(), yptrs, ystr,
+                                                   ws.data_ptr(), ws.numel(), stream)
     _lib.check(rc, "bsb_linear_forward_grouped")
-    out = [y.reshape(*x.shape[:-1], m.out_features) for y, m in zip(ys, modules)]
-    if extra is not None:
-        out.append(extra.reshape(*x.shape[:-1], modules[0].out_features))
-    return out
+    return [y.reshape(*x.shape[:-1], m.out_features) for y, m in zip(ys, modules)]

@@ -128,34 +128,16 @@ int bsb_linear_forward_grouped(const bsb_weight* ws, int32_t n_weights, const ui
                                const int64_t* y_strides, void* workspace, int64_t workspace_bytes,
                                int algo, void* stream);
 
-/* bsb_linear_forward_grouped with the two hooks that let a decode step (rows <= 6) run without separate launches
- * for the row operations between its projections.  No counterpart in the reference, which leaves those operations
- * to the Hugging Face modules around the projections (bitstack/utils/scale_utils.py:3-5 names the classes).
- *   x_absmax  optional fp32 [rows]: max |x| of every input row, as the operation that produced x delivered it
- *             (an output op below, bsb_add_rmsnorm, bsb_silu_mul).  The decode kernel's operand preparation
- *             then does not have to scan x for it.  NULL = computed inside.
- *   op        optional output op, applied by the last thread block of the decode kernel once every output of the
- *             call is in memory, with the roundings of the stand-alone bsb_add_rmsnorm / bsb_silu_mul:
- *               BSB_OUTPUT_ADD_RMSNORM (one weight): h += y; x_out = rmsnorm(h) * norm_weight
- *               BSB_OUTPUT_SILU_MUL (a gate / up pair of equal width): x_out = silu(y[0]) * y[1]
- *             x_absmax (may be NULL) receives max |x_out| per row.  The ys are still written.
- * Both hooks need the decode path: rows <= 6 and every weight with k == 16, in_features % 128 == 0, 16-byte
- * aligned tensors and at least one active block; otherwise BSB_EINVAL (use the stand-alone kernels). */
-enum { BSB_OUTPUT_NONE = 0, BSB_OUTPUT_ADD_RMSNORM = 1, BSB_OUTPUT_SILU_MUL = 2 };
-typedef struct bsb_output_op {
-  int32_t mode;
-  float eps;                   /* rmsnorm epsilon */
-  uint16_t* h;                 /* ADD_RMSNORM: fp16 residual stream [rows][out_features], updated in place */
-  const uint16_t* norm_weight; /* ADD_RMSNORM: fp16 [out_features] */
-  uint16_t* x_out;             /* fp16 [rows][out_features] */
-  float* x_absmax;             /* fp32 [rows] or NULL */
-  int64_t h_stride;            /* elements between rows of h */
-  int64_t x_stride;            /* elements between rows of x_out */
-} bsb_output_op;
+/* bsb_linear_forward_grouped for a decode step (rows <= 6) whose input comes with its row maxima.  No counterpart
+ * in the reference.  x_absmax: fp32 [rows], max |x| of every input row as the operation that produced x delivered
+ * it (bsb_add_rmsnorm, bsb_silu_mul): the decode kernel's operand preparation needs that number for the scale of
+ * its fp8 operand and then does not have to scan x for it (NULL = computed inside, as bsb_linear_forward_grouped
+ * does).  A value smaller than the true maximum would clip the operand: pass what the producer computed.
+ * Needs the decode path: rows <= 6 and every weight with k == 16, in_features % 128 == 0, 16-byte aligned tensors
+ * and at least one active block; otherwise BSB_EINVAL. */
 int bsb_linear_forward_grouped_ex(const bsb_weight* ws, int32_t n_weights, const uint16_t* x, int64_t rows,
                                   int64_t x_stride, const float* x_absmax, uint16_t* const* ys,
-                                  const int64_t* y_strides, const bsb_output_op* op, void* workspace,
-                                  int64_t workspace_bytes, void* stream);
+                                  const int64_t* y_strides, void* workspace, int64_t workspace_bytes, void* stream);
 
 /* Scratch bytes bsb_linear_forward_grouped needs. */
 int64_t bsb_linear_grouped_workspace_bytes(const bsb_weight* ws, int32_t n_weights, int64_t rows, int algo);

@@ -142,9 +142,8 @@ def test_fused_decode_step_matches_unfused(dev):
     counts = decode.seeded_block_counts(shape, seed=3, lo=2, hi=4)
     prompt = torch.randint(0, 1000, (1, 9), device=dev)
     outs = []
-    for fused, in_call in ((False, False), (True, False), (True, True)):
+    for fused in (False, True):
         m = decode.BitStackLlamaDecoder(shape, counts, dev, seed=5, max_len=128, fused_glue=fused)
-        m.fuse_output_ops = in_call      # row operations applied by the projection calls' output stage
         m.prefill(prompt)
         toks, logits = [], None
         for _ in range(4):
@@ -160,35 +159,28 @@ def test_fused_decode_step_matches_unfused(dev):
 
 
 @pytest.mark.parametrize("rows", [1, 2, 5])
-def test_output_ops_of_the_projection_call_match_the_separate_kernels(dev, rows):
-    """The row operation that follows a projection (h += y; rmsnorm, or silu(gate) * up) done by the projection call
-    itself against the stand-alone glue kernels: residual stream, result and its max |.| bit for bit; and a call that
-    is handed max |x| by the producer of x gives the same outputs as one that scans x itself."""
+def test_row_kernels_deliver_the_row_maximum_and_the_projection_call_takes_it(dev, rows):
+    """The stand-alone row kernels (add + rmsnorm, silu * up) also deliver max |result| per row; a projection call that
+    is handed that number gives bit-identical outputs to one that scans x itself."""
     from bitstack_b200 import forward_grouped, glue
     from bitstack_b200.layer_bench import synthetic_projection
     N, M = 1024, 768
     g = torch.Generator(device=dev).manual_seed(rows)
-    x = torch.randn(rows, N, device=dev, generator=g).half()
-    h = torch.randn(rows, M, device=dev, generator=g).half()
-    w = (1 + 0.1 * torch.randn(M, device=dev, generator=g)).half()
-    proj = synthetic_projection(M, N, 3, 10, dev, seed=1)
-    # add + rmsnorm after a single projection
-    y_ref = forward_grouped([proj], x)[0]
-    h_ref = h.clone()
-    am_ref = torch.zeros(rows, dtype=torch.float32, device=dev)
-    x_ref = glue.add_rmsnorm(h_ref, y_ref, w, 1e-5, absmax=am_ref)
-    h_got, am = h.clone(), torch.zeros(rows, dtype=torch.float32, device=dev)
-    y, x_got = forward_grouped([proj], x, add_rmsnorm=(h_got, w, 1e-5), out_absmax=am)
-    assert torch.equal(y, y_ref) and torch.equal(h_got, h_ref) and torch.equal(x_got, x_ref) and torch.equal(am, am_ref)
-    assert torch.equal(am, x_ref.float().abs().amax(dim=1))
-    # silu * up after a gate / up pair, fed with max |x| from the producer
-    gate, up = synthetic_projection(M, N, 2, 10, dev, seed=2), synthetic_projection(M, N, 4, 10, dev, seed=3)
-    xmax = x.float().abs().amax(dim=1)
-    g_ref, u_ref = forward_grouped([gate, up], x)
-    am2_ref = torch.zeros(rows, dtype=torch.float32, device=dev)
-    a_ref = glue.silu_mul(g_ref, u_ref, absmax=am2_ref)
+    h = torch.randn(rows, N, device=dev, generator=g).half()
+    d = torch.randn(rows, N, device=dev, generator=g).half()
+    w = (1 + 0.1 * torch.randn(N, device=dev, generator=g)).half()
+    am = torch.zeros(rows, dtype=torch.float32, device=dev)
+    h1, h2 = h.clone(), h.clone()
+    x = glue.add_rmsnorm(h1, d, w, 1e-5, absmax=am)
+    assert torch.equal(x, glue.add_rmsnorm(h2, d, w, 1e-5)) and torch.equal(h1, h2)
+    assert torch.equal(am, x.float().abs().amax(dim=1))
+    mods = [synthetic_projection(M, N, 3, 10, dev, seed=1), synthetic_projection(256, N, 2, 10, dev, seed=2)]
+    for a, b in zip(forward_grouped(mods, x, x_absmax=am), forward_grouped(mods, x)):
+        assert torch.equal(a, b)
+    gate = torch.randn(rows, N, device=dev, generator=g).half()
+    up = torch.randn(rows, N, device=dev, generator=g).half()
     am2 = torch.zeros(rows, dtype=torch.float32, device=dev)
-    g_got, u_got, a_got = forward_grouped([gate, up], x, x_absmax=xmax, silu_mul=True, out_absmax=am2)
-    assert torch.equal(g_got, g_ref) and torch.equal(u_got, u_ref) and torch.equal(a_got, a_ref) and torch.equal(am2, am2_ref)
-    want = (torch.nn.functional.silu(g_ref) * u_ref).float()
-    assert (a_ref.float() - want).abs().max() <= 2e-3 * want.abs().max()
+    a = glue.silu_mul(gate, up, absmax=am2)
+    assert torch.equal(a, glue.silu_mul(gate, up)) and torch.equal(am2, a.float().abs().amax(dim=1))
+    want = (torch.nn.functional.silu(gate) * up).float()
+    assert (a.float() - want).abs().max() <= 2e-3 * want.abs().max()
