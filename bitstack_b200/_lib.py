@@ -11,7 +11,7 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("BITSTACK_B200_LIB") or os.path.join(_HERE, "libbitstack_b200.so")
 
-ALGO_AUTO, ALGO_GENERAL, ALGO_REBUILD_GEMM, ALGO_GEMV_TC5 = 0, 1, 3, 4
+ALGO_AUTO, ALGO_GENERAL, ALGO_REBUILD_GEMM, ALGO_GEMV_TC5, ALGO_SIGN_GEMM, ALGO_SIGN_GEMM_MMA = 0, 1, 3, 4, 5, 6
 
 
 class BsbWeight(C.Structure):

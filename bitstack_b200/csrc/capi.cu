@@ -91,10 +91,15 @@ int check_weight(const bsb_weight* w) {
 // largest batch that goes through the decode kernel (pairs of rows); above it the weight is rebuilt once and
 // multiplied by the GEMM
 static const int kDecodeRowsMax = 6;
+static const int kFusedRowsMax = 16;
 
 static int pick_algo(const bsb_weight& w, int64_t rows, int algo) {
   if (algo != BSB_ALGO_AUTO) return algo;
   if (rows <= kDecodeRowsMax && gemv_tc5_supported(w)) return BSB_ALGO_GEMV_TC5;   // two rows per pass: cheaper than rebuilding W up to here
+  // 7 .. 16 rows: the fused sign-GEMM (W never leaves the multiprocessor) beats rebuilding W; above that the sign stage,
+  // which is paid per block and per 16-row tile of the batch in the register variant, loses to rebuild + GEMM
+  // (measured on 14336 x 4096, 8 blocks: 159 us against 199 at 16 rows, 214 against 200 at 32)
+  if (rows <= kFusedRowsMax && signgemm_mma_supported(w, rows)) return BSB_ALGO_SIGN_GEMM_MMA;
   if (rebuild_supported(w) && gemm_supported(rows, w.out_features, w.in_features)) return BSB_ALGO_REBUILD_GEMM;
   return BSB_ALGO_GENERAL;
 }
@@ -103,6 +108,10 @@ static int64_t workspace_for(const bsb_weight& w, int64_t rows, int algo) {
   switch (pick_algo(w, rows, algo)) {
     case BSB_ALGO_GEMV_TC5:
       return gemv_tc5_workspace_bytes(&w, 1, rows >= 2 ? 2 : 1);
+    case BSB_ALGO_SIGN_GEMM:
+      return signgemm_workspace_bytes(w, rows);
+    case BSB_ALGO_SIGN_GEMM_MMA:
+      return signgemm_mma_workspace_bytes(w, rows);
     case BSB_ALGO_REBUILD_GEMM:
       return align_up64((int64_t)w.out_features * w.in_features * 2, 256);   // the rebuilt fp16 W
     default:
@@ -155,6 +164,10 @@ static int forward_one(const bsb_weight& w, const __half* x, int64_t rows, int64
       }
       return BSB_OK;
     }
+    case BSB_ALGO_SIGN_GEMM:
+      return launch_signgemm(w, x, rows, x_stride, y, y32, y_stride, workspace, workspace_bytes, s);
+    case BSB_ALGO_SIGN_GEMM_MMA:
+      return launch_signgemm_mma(w, x, rows, x_stride, y, y32, y_stride, workspace, workspace_bytes, s);
     case BSB_ALGO_REBUILD_GEMM: {
       BSB_CHECK_ARG(rebuild_supported(w) && gemm_supported(rows, w.out_features, w.in_features),
                     "REBUILD_GEMM: unsupported shape/alignment (out=%d in=%d k=%d)", w.out_features,
@@ -343,6 +356,7 @@ int bsb_read_status(int32_t* code_out, int32_t clear) {
 int bsb_set_wait_limit_ms(int32_t ms) {
   BSB_CHECK_ARG(ms >= 1 && ms <= 60000, "wait limit must be 1..60000 ms");
   gemv_tc5_set_wait_limit_ns((unsigned long long)ms * 1000000ull);
+  signgemm_set_wait_limit_ns((unsigned long long)ms * 1000000ull);
   return BSB_OK;
 }
 

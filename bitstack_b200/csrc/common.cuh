@@ -116,6 +116,19 @@ bool gemm_tc5_supported(int64_t rows, int out_features, int in_features);
 int launch_gemm_tc5(const __half* x, int64_t rows, int64_t x_stride, const __half* w, int out_features,
                     int in_features, const __half* bias, __half* y, float* y32, int64_t y_stride, cudaStream_t s);
 
+// small-batch path (7 .. 64 rows): signs expanded inside the multiprocessor into the fp16 operand of a tcgen05 MMA
+bool signgemm_supported(const bsb_weight& w, int64_t rows);
+int64_t signgemm_workspace_bytes(const bsb_weight& w, int64_t rows);
+void signgemm_set_wait_limit_ns(unsigned long long ns);
+int launch_signgemm(const bsb_weight& w, const __half* x, int64_t rows, int64_t x_stride, __half* y, float* y32, int64_t y_stride,
+                    void* workspace, int64_t workspace_bytes, cudaStream_t s);
+
+// the same with warp-level MMAs and everything between the two MMAs in registers
+bool signgemm_mma_supported(const bsb_weight& w, int64_t rows);
+int64_t signgemm_mma_workspace_bytes(const bsb_weight& w, int64_t rows);
+int launch_signgemm_mma(const bsb_weight& w, const __half* x, int64_t rows, int64_t x_stride, __half* y, float* y32, int64_t y_stride,
+                        void* workspace, int64_t workspace_bytes, cudaStream_t s);
+
 // decode path (tcgen05: sign operand expanded into tensor memory)
 int launch_vt_absmax(const bsb_weight& w, float* out, cudaStream_t s);
 bool gemv_tc5_supported(const bsb_weight& w);

@@ -52,7 +52,7 @@ constexpr float kMinD = 0.75f;
 constexpr unsigned long long kDefaultWaitNs = 200ull * 1000 * 1000;   // default limit of every wait (bsb_set_wait_limit_ms)
 
 __constant__ float kV0[8] = {8.f, 4.f, 2.f, 0.75f, 0.375f, 0.09375f, 0.f, 1.f};
-__constant__ float kD[8] = {1.f, 1.f, 1.f, 0.75f, 1.125f, 1.40625f, 2.f, -2.f};
+// class steps d_i (set bit minus clear bit): 1, 1, 1, 0.75, 1.125, 1.40625, 2, -2 (kTwoOverD below holds 2 / d_i)
 __host__ __device__ constexpr uint32_t class_byte(int i) {
   return i == 0 ? 0x50u : i == 1 ? 0x48u : i == 2 ? 0x40u : i == 3 ? 0x34u
        : i == 4 ? 0x2Cu : i == 5 ? 0x1Cu : i == 6 ? 0x00u : 0x38u;

@@ -7,10 +7,13 @@ constructor, buffer names / shapes / dtypes (these are the checkpoint keys),
 (0-5) runs the same fused CUDA path here -- the levels only differed in how the
 reference staged its Triton kernels -- and extra levels pin one kernel:
 
-    0-5, 6  automatic choice (decode kernel, two rows per pass, for <= 6 rows; rebuild + tcgen05 GEMM above)
+    0-5, 6  automatic choice (decode kernel, two rows per pass, for <= 6 rows; fused sign-GEMM up to 16 rows;
+            rebuild + tcgen05 GEMM above)
     7       shape-agnostic CUDA-core kernel
     9       rebuild fp16 weight + tcgen05 GEMM
     10      decode kernel (tcgen05, sign operand in tensor memory), any row count
+    11      fused sign-GEMM, tcgen05 variant (signs applied to tcgen05 rank-16 products in shared memory; up to 64 rows)
+    12      fused sign-GEMM, register variant (warp-level MMAs, nothing between the two MMAs leaves the registers)
 
 Differences from the reference's levels that a caller can observe: level 5 there takes 3-D inputs only and ignores
 the bias (bitstack/modules/BitStackLinear.py:150-157); here every level takes any leading shape and adds the bias.
@@ -31,7 +34,8 @@ from .pack import pack_sign, unpack_sign
 
 _LEVEL_TO_ALGO = {0: _lib.ALGO_AUTO, 1: _lib.ALGO_AUTO, 2: _lib.ALGO_AUTO, 3: _lib.ALGO_AUTO,
                   4: _lib.ALGO_AUTO, 5: _lib.ALGO_AUTO, 6: _lib.ALGO_AUTO,
-                  7: _lib.ALGO_GENERAL, 9: _lib.ALGO_REBUILD_GEMM, 10: _lib.ALGO_GEMV_TC5}
+                  7: _lib.ALGO_GENERAL, 9: _lib.ALGO_REBUILD_GEMM, 10: _lib.ALGO_GEMV_TC5, 11: _lib.ALGO_SIGN_GEMM,
+                  12: _lib.ALGO_SIGN_GEMM_MMA}
 
 # scratch memory per (device index, stream handle); grown on demand, never shrunk
 _workspaces: dict = {}

@@ -61,7 +61,10 @@ enum {
   BSB_ALGO_AUTO = 0,
   BSB_ALGO_GENERAL = 1,   /* any shape, CUDA cores, fp32 */
   BSB_ALGO_REBUILD_GEMM = 3, /* batch/prefill: rebuild fp16 W, then the tcgen05 GEMM */
-  BSB_ALGO_GEMV_TC5 = 4   /* decode (1-6 rows): packed signs expanded into tensor memory, tcgen05 fp8 MMAs */
+  BSB_ALGO_GEMV_TC5 = 4,  /* decode (1-6 rows): packed signs expanded into tensor memory, tcgen05 fp8 MMAs */
+  BSB_ALGO_SIGN_GEMM = 5, /* small batch (up to 64 rows): signs applied to tcgen05 rank-16 products inside the
+                             multiprocessor and fed to the tcgen05 GEMM from shared memory; W is never written */
+  BSB_ALGO_SIGN_GEMM_MMA = 6 /* the same fusion with warp-level MMAs, everything between the two MMAs in registers */
 };
 
 int bsb_version(void);
@@ -204,7 +207,8 @@ int bsb_linear_forward_noalloc(const bsb_weight* w, const uint16_t* x, int64_t r
  * stays set until it is read -- later calls do not clear it.
  *   bsb_read_status: synchronises the current device, copies the word to *code_out and, if `clear` is non-zero,
  *     resets it.  Returns BSB_OK when the word is 0, BSB_ETIMEOUT otherwise.  Codes: 1-8 decode kernel (1 Z' ring,
- *     2 Z' slab, 3/4 operand stage full/empty, 5/6 accumulator full/empty, 7/8 sign ring), 21-24 GEMM.
+ *     2 Z' slab, 3/4 operand stage full/empty, 5/6 accumulator full/empty, 7/8 sign ring), 21-24 GEMM, 31-37 fused
+ *     sign-GEMM.
  *     Call it wherever the host synchronises anyway (bsb_linear_forward_host does).
  *   bsb_set_wait_limit_ms: the time limit of every such wait (default 200 ms), for kernels launched afterwards. */
 int bsb_read_status(int32_t* code_out, int32_t clear);

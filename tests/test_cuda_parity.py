@@ -590,3 +590,52 @@ def test_new_factor_values_in_place_are_seen(dev):
         sd[f"vt_{j}"] = torch.from_numpy(vt10[j])
     lvl0.load_state_dict(sd)
     assert errs(lvl0(x).float().cpu().numpy(), orc.forward_f64(x_np, q, u, vt10, 3))[0] <= EXACT_TOL
+
+
+# --------------------------------------------------------------------------- fused sign-GEMM (7 .. 64 rows)
+@pytest.mark.parametrize("level", [11, 12])
+@pytest.mark.parametrize("m,n,nb,rows,bias", [(256, 512, 1, 16, False), (384, 1024, 3, 7, True), (1040, 640, 2, 33, True),
+                                              (128, 128, 5, 64, False), (4096, 4096, 8, 16, False), (1792, 4096, 5, 48, False),
+                                              (4096, 1792, 4, 16, True), (14336, 4096, 7, 64, False), (4096, 14336, 3, 9, False)])
+def test_fused_sign_gemm_small_batches(dev, m, n, nb, rows, bias, level):
+    """Levels 11 / 12 pin the two variants of the fused small-batch kernel (signs applied to rank-16 products inside the
+    multiprocessor, no W in memory; 11 = tcgen05, 12 = warp-level MMAs in registers): row counts that are not multiples
+    of the 16-row MMA step, row tiles and super-chunks that end inside a tile (1040 rows, 640 / 1792 columns), a bias,
+    one and many blocks; the status word must stay 0 and the same call must be bit-identical run to run."""
+    if level == 11 and n % 128 != 0:
+        pytest.skip("the tcgen05 variant needs in_features % 128 == 0")
+    import ctypes as C
+    from bitstack_b200 import _lib
+    q, u, vt = orc.synthetic_layer(m, n, nb, seed=m + n + nb)
+    b = (np.random.default_rng(rows).standard_normal(m) * 0.1).astype(np.float16) if bias else None
+    mod = make_module(q, u, vt, b, dev, level=level)
+    x_np = orc.synthetic_input(rows, n, seed=rows + n)
+    x = torch.from_numpy(x_np).to(dev)
+    y = mod(x)
+    st = C.c_int32(-1)
+    assert _lib.load().bsb_read_status(C.byref(st), 1) == 0 and st.value == 0
+    idx = np.sort(np.random.default_rng(3).choice(m, size=min(96, m), replace=False))
+    e_max, e_l2 = errs(y.float().cpu().numpy()[:, idx], orc.forward_f64_rows(x_np, q, u, vt, nb, idx, b))
+    assert e_max <= EXACT_TOL and e_l2 <= EXACT_TOL, (e_max, e_l2)
+    assert torch.equal(y, mod(x))
+    # the automatic choice takes the register variant up to 16 rows
+    if level == 12 and rows <= 16:
+        mod.fused_level = 6
+        assert torch.equal(mod(x), y)
+    # fp32 partial sums (tensor-parallel variant)
+    mod.fused_level = level
+    part = mod.forward_partial(x)
+    assert part.dtype == torch.float32 and torch.equal(part.half(), y)
+
+
+def test_fused_sign_gemm_real_decomposition(dev, golden_dir):
+    z = np.load(os.path.join(golden_dir, "decomp_1024.npz"))
+    q, u, vt = z["qweight"], z["u"], z["vt"]
+    nb = u.shape[0]
+    mod = make_module(q, u, vt, None, dev, level=12)
+    x_np = _heavy_tailed_input(24, vt.shape[2], seed=8)
+    y = mod(torch.from_numpy(x_np).to(dev)).float().cpu().numpy()
+    e_max, e_l2 = errs(y, orc.forward_f64(x_np, q, u, vt, nb))
+    assert e_max <= EXACT_TOL and e_l2 <= EXACT_TOL, (e_max, e_l2)
+    e_max, e_l2 = errs(y, orc.forward_l0(x_np, q, u, vt, nb).float().numpy())
+    assert e_max <= TOL and e_l2 <= TOL, (e_max, e_l2)
