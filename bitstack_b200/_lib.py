@@ -53,6 +53,11 @@ SIGNATURES = {
     "bsb_decode_attention_scratch_bytes": (C.c_int64, [_I32, _I32, _I32]),
     "bsb_greedy_step": (C.c_int, [_P, _I64, _I64, _I64, _P, _P, _P]),
     "bsb_silu_mul": (C.c_int, [_P, _P, _P, _P, _I64, _I32, _P]),
+    "bsb_peer_area_bytes": (_I64, [_I32, _I32, _I32]),
+    "bsb_peer_alloc": (C.c_int, [_I64, C.POINTER(_P), _P]),
+    "bsb_peer_open": (C.c_int, [_P, C.POINTER(_P)]),
+    "bsb_peer_close": (C.c_int, [_P, _I32]),
+    "bsb_peer_allreduce_add_rmsnorm": (C.c_int, [C.POINTER(_P), _I32, _I32, _I32, _I32, _P, _I64, _I32, _I32, _P, _P, C.c_float, _P, _P, _P]),
     "bsb_noalloc_scratch_bytes": (_I64, []),
     "bsb_linear_forward_noalloc": (C.c_int, [_WP, _P, _I64, _I64, _P, _I64, _P]),
     "bsb_read_status": (C.c_int, [C.POINTER(C.c_int32), _I32]),

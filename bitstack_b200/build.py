@@ -18,7 +18,7 @@ LIB = os.path.join(HERE, "libbitstack_b200.so")
 # side build with -DBSB_TUNING: the same library plus timing-experiment modes and a fault-injection mode of the decode
 # kernel (bsb_tuning_set_mode / bsb_tuning_set_trace); the tests of the give-up path load it, the product never does
 TUNING_LIB = os.path.join(HERE, "libbitstack_b200_tuning.so")
-SOURCES = ["capi.cu", "pack_kernels.cu", "general_kernels.cu", "rebuild_gemm.cu", "gemv_tc5.cu", "gemm_tc5.cu", "signgemm_tc5.cu", "signgemm_mma.cu", "decode_glue.cu"]
+SOURCES = ["capi.cu", "pack_kernels.cu", "general_kernels.cu", "rebuild_gemm.cu", "gemv_tc5.cu", "gemm_tc5.cu", "signgemm_tc5.cu", "signgemm_mma.cu", "decode_glue.cu", "peer_reduce.cu"]
 HEADERS = [os.path.join(CSRC, "common.cuh"), os.path.join(CSRC, "rowops.cuh"), os.path.join(os.path.dirname(HERE), "include", "bitstack_b200.h")]
 FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",
          "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]

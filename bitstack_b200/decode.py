@@ -120,10 +120,19 @@ class BitStackLlamaDecoder:
     """Random-init Llama-architecture decoder whose linears are BitStack modules."""
 
     def __init__(self, shape: LlamaShape, block_counts: Dict[str, int], device, seed=0, max_len=1024,
-                 batch=1, fused_level=6, rank=0, world_size=1, group=None, fused_glue=True):
+                 batch=1, fused_level=6, rank=0, world_size=1, group=None, fused_glue=True, peer_reduce=True):
         self.shape, self.device, self.max_len, self.batch = shape, torch.device(device), max_len, batch
         self.fused_glue = fused_glue
         self.rank, self.world, self.group = rank, world_size, group
+        # tensor parallel decode: the all-reduce after o / down as one kernel over NVLink peer memory (peer.py), fused
+        # with the add + RMSNorm that follows; NCCL when the peers' memory cannot be mapped or the batch is too large
+        self.peer = None
+        if world_size > 1 and peer_reduce and batch <= 16:
+            try:
+                from .peer import PeerReduce
+                self.peer = PeerReduce(group, self.device, max_rows=batch, max_width=shape.hidden)
+            except Exception as e:   # noqa: BLE001 - any set-up failure means "use NCCL"
+                self.peer_error = str(e)
         s = shape
         assert s.n_kv_heads % world_size == 0 and s.intermediate % (128 * world_size) == 0 and s.vocab % world_size == 0
         gen = torch.Generator(device=self.device).manual_seed(seed)  # same seed on every rank: replicated tensors agree
@@ -233,6 +242,8 @@ class BitStackLlamaDecoder:
         h = self.embed.index_select(0, self.tokens).contiguous()            # [B, hidden], residual stream
         fused_att = hd in (64, 128) and self.max_len <= 8192
         mask = None if fused_att else (self.arange <= self.pos).view(1, 1, 1, self.max_len)
+        if self.peer is not None:
+            return self._decode_fused_peer(h, fused_att, mask)
         delta = None                                                         # output of the previous MLP, not yet added to h
         # the stand-alone row kernels deliver max |x| with x: the operand preparation of the next call need not scan x
         am = torch.empty(B, dtype=torch.float32, device=self.device) if B <= 6 else None
@@ -256,6 +267,22 @@ class BitStackLlamaDecoder:
         glue.rope_cache(q, k, v, self.cos, self.sin, self.pos, self.k_cache[i], self.v_cache[i], self.q_local, self.kv_local, hd)
         return F.scaled_dot_product_attention(q.view(B, self.q_local, 1, hd), self.k_cache[i], self.v_cache[i],
                                               attn_mask=mask, enable_gqa=True).reshape(B, self.q_local * hd)
+
+    def _decode_fused_peer(self, h, fused_att, mask):
+        """Tensor-parallel decode step with the one-shot peer all-reduce: o and down deliver fp32 partial sums, one
+        kernel per rank exchanges them over NVLink, adds them in rank order, updates the residual stream and
+        normalises it for the next projection.  Same values as the NCCL path (sum in fp32, one rounding)."""
+        s, B = self.shape, self.batch
+        am = torch.empty(B, dtype=torch.float32, device=self.device) if B <= 6 else None
+        x = glue.add_rmsnorm(h, None, self.layers[0]["in_norm"], s.rms_eps, absmax=am)
+        for i, lay in enumerate(self.layers):
+            q, k, v = forward_grouped([lay["self_attn.q_proj"], lay["self_attn.k_proj"], lay["self_attn.v_proj"]], x, x_absmax=am)
+            att = self._attention(i, q, k, v, fused_att, mask)
+            x = self.peer.allreduce_add_rmsnorm(lay["self_attn.o_proj"].forward_partial(att), h, lay["post_norm"], s.rms_eps, am)
+            g, u = forward_grouped([lay["mlp.gate_proj"], lay["mlp.up_proj"]], x, x_absmax=am)
+            nxt = self.layers[i + 1]["in_norm"] if i + 1 < len(self.layers) else self.final_norm
+            x = self.peer.allreduce_add_rmsnorm(lay["mlp.down_proj"].forward_partial(glue.silu_mul(g, u)), h, nxt, s.rms_eps, am)
+        return x @ self.lm_head.t()
 
     # ------------------------------------------------------------------ public API
     @torch.no_grad()

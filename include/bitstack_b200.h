@@ -177,6 +177,30 @@ int bsb_greedy_step(const uint16_t* logits, int64_t batch, int64_t vocab, int64_
 int bsb_silu_mul(const uint16_t* gate, const uint16_t* up, uint16_t* out, float* out_absmax, int64_t rows, int32_t n,
                  void* stream);
 
+/* ---- tensor parallelism: one-shot all-reduce over NVLink peer memory, fused with the add + RMSNorm that follows a
+ * column-sharded projection.  No counterpart in the reference (single-device forward,
+ * bitstack/modules/BitStackLinear.py:88-157).  One process per GPU; every rank owns an AREA of device memory that
+ * all ranks map (CUDA inter-process handles) and calls bsb_peer_allreduce_add_rmsnorm with its fp32 partial sums
+ * (bsb_linear_forward_partial): the kernel stores them into the peers' areas with plain stores over NVLink, waits
+ * -- time-bounded, status word + NaN outputs on a give-up -- for the peers' partials, adds all of them in rank order
+ * (bit-identical on every rank), rounds once to fp16 and continues as bsb_add_rmsnorm does: h += sum,
+ * x_out = rmsnorm(h) * norm_weight, x_absmax = max |x_out| per row.  It replaces ncclAllReduce + a conversion + the
+ * add/norm kernel; NCCL stays the fallback where peer mapping is not available.
+ *   bsb_peer_area_bytes   size of an area for `world` ranks and up to max_rows x max_width fp32 partials.
+ *   bsb_peer_alloc        set-up only (this one allocates): a zeroed area on the current device + its 64-byte handle.
+ *   bsb_peer_open         set-up only: maps the area behind a peer's handle into this process.
+ *   bsb_peer_close        releases an area (own != 0) or a mapping.
+ *   areas[p]              the area of rank p as mapped in the calling process (areas[rank] = its own).
+ * Every rank must make the same sequence of calls with the same rows / width.  width % 8 == 0, width <= 16384,
+ * 16-byte aligned buffers, world <= 8. */
+int64_t bsb_peer_area_bytes(int32_t world, int32_t max_rows, int32_t max_width);
+int bsb_peer_alloc(int64_t bytes, void** area_out, uint8_t* handle_out);
+int bsb_peer_open(const uint8_t* handle, void** area_out);
+int bsb_peer_close(void* area, int32_t own);
+int bsb_peer_allreduce_add_rmsnorm(void* const* areas, int32_t rank, int32_t world, int32_t max_rows, int32_t max_width,
+                                   const float* partial, int64_t partial_stride, int32_t rows, int32_t width, uint16_t* h,
+                                   const uint16_t* norm_weight, float eps, uint16_t* x_out, float* x_absmax, void* stream);
+
 /* Forward for callers that may not allocate device memory.  It has no counterpart in the
  * reference.  Some hosts hand a plug-in a fixed set of buffers and forbid any device
  * allocation once they are running -- an inference server with a frozen memory plan, a
@@ -208,7 +232,7 @@ int bsb_linear_forward_noalloc(const bsb_weight* w, const uint16_t* x, int64_t r
  *   bsb_read_status: synchronises the current device, copies the word to *code_out and, if `clear` is non-zero,
  *     resets it.  Returns BSB_OK when the word is 0, BSB_ETIMEOUT otherwise.  Codes: 1-8 decode kernel (1 Z' ring,
  *     2 Z' slab, 3/4 operand stage full/empty, 5/6 accumulator full/empty, 7/8 sign ring), 21-24 GEMM, 31-37 fused
- *     sign-GEMM.
+ *     sign-GEMM, 51 peer all-reduce.
  *     Call it wherever the host synchronises anyway (bsb_linear_forward_host does).
  *   bsb_set_wait_limit_ms: the time limit of every such wait (default 200 ms), for kernels launched afterwards. */
 int bsb_read_status(int32_t* code_out, int32_t clear);

@@ -20,7 +20,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, batch, out_q):
+def _worker(rank, world, port, batch, peer, out_q):
     import datetime
     import torch.distributed as dist
     os.environ["MASTER_ADDR"] = "127.0.0.1"
@@ -35,7 +35,8 @@ def _worker(rank, world, port, batch, out_q):
     gen = torch.Generator().manual_seed(2)
     prompt = torch.randint(0, shape.vocab, (batch, 9), generator=gen).to(dev)
     tp = decode.BitStackLlamaDecoder(shape, counts, dev, seed=6, max_len=128, batch=batch, rank=rank, world_size=world,
-                                     group=dist.group.WORLD)
+                                     group=dist.group.WORLD, peer_reduce=peer)
+    assert (tp.peer is not None) == peer, getattr(tp, "peer_error", None)
     tp.prefill(prompt)
     toks = []
     for _ in range(5):
@@ -57,15 +58,18 @@ def _worker(rank, world, port, batch, out_q):
     os._exit(0)    # skip the communicator destructors (they were seen to block at exit after graph / PDL work)
 
 
+@pytest.mark.parametrize("peer", [False, True])
 @pytest.mark.parametrize("batch", [1, 3])
-def test_two_rank_decoder_matches_one_device(batch):
+def test_two_rank_decoder_matches_one_device(batch, peer):
+    """peer=False: NCCL all-reduce of the fp32 partials; peer=True: the one-shot all-reduce over NVLink peer memory fused
+    with the add + RMSNorm (`bsb_peer_allreduce_add_rmsnorm`)."""
     if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, batch, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, batch, peer, q)) for r in range(2)]
     for p in procs:
         p.start()
     same, err, got, want = q.get(timeout=300)
