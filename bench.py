@@ -138,10 +138,13 @@ class ClockSampler:
 
 # ----------------------------------------------------------------------------- CPU restatement
 def cpu_sample(shape, counts, budget_s, threads=None):
-    """Time the oracle's restatement of the reference's unfused forward on a bounded
-    sample of this workload's projections; returns extrapolated tokens/s."""
+    """Time the reference's unfused forward on the host cores on a bounded sample of this workload's projections;
+    returns extrapolated tokens/s.  The reference's OWN `BitStackLinear.forward_l0` runs when its files are staged
+    under oracle/_ref (oracle/make_ref.py; kind "reference"), else the oracle's restatement of it (kind "port")."""
     from oracle import bitstack_oracle as orc
+    from oracle import make_ref
     from bitstack_b200 import decode
+    Ref = make_ref.import_reference() if make_ref.ref_available() else None
     # under torch.distributed.run OMP_NUM_THREADS is 1: use every host core whatever launched this process
     torch.set_num_threads(threads or os.cpu_count() or 1)
     shapes = shape.proj_shapes()
@@ -167,8 +170,17 @@ def cpu_sample(shape, counts, budget_s, threads=None):
         u = (torch.randn(nb, out_f, 16) * 0.05).abs().half()
         vt = (torch.randn(nb, 16, in_f) * 0.05).abs().half()
         x = torch.randn(1, in_f).half()
-        t0 = time.perf_counter()
-        orc.forward_l0(x, q, u, vt, nb)
+        if Ref is not None:
+            mod = Ref(w_bit=nb, in_features=in_f, out_features=out_f, k=16, bias=False, no_avd=False, dev="cpu", fused_level=0)
+            for j in range(nb):
+                setattr(mod, f"qweight_{j}", q[j])
+                setattr(mod, f"u_{j}", u[j])
+                setattr(mod, f"vt_{j}", vt[j])
+            t0 = time.perf_counter()
+            mod(x)
+        else:
+            t0 = time.perf_counter()
+            orc.forward_l0(x, q, u, vt, nb)
         dt = time.perf_counter() - t0
         picked.append(name)
         t_used += dt
@@ -177,7 +189,7 @@ def cpu_sample(shape, counts, budget_s, threads=None):
         if t_used >= budget_s:
             break
     sec_per_token = t_used * total_bytes / max(bytes_done, 1)
-    return {"value": 1.0 / sec_per_token, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+    return {"value": 1.0 / sec_per_token, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "reference" if Ref is not None else "port",
             "sample": f"{len(picked)} of {len(counts)} projections ({bytes_done/1e6:.0f} MB of {total_bytes/1e6:.0f} MB packed "
                       f"blocks per token) in {t_used:.1f} s, extrapolated by packed bytes; attention/head glue not included",
             "gb_per_s": bytes_done / t_used / 1e9, "host_cpus": os.cpu_count()}
