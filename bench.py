@@ -64,6 +64,7 @@ def parse():
     ap.add_argument("--repeats", type=int, default=10, help="repeats of the timed K-step region (the median is reported)")
     ap.add_argument("--no-70b", action="store_true", help="skip the 70B-architecture batch-16 leg")
     ap.add_argument("--steps-70b", type=int, default=8)
+    ap.add_argument("--no-prefill-leg", action="store_true", help="skip the timed prefill leg (short profiler runs)")
     return ap.parse_args()
 
 
@@ -369,7 +370,7 @@ def run_ours(args):
     # ---- prefill through the batch path (tensor-pipe figure) -------------------------------
     _progress("model built")
     prefill = {}
-    for toks in sorted({prompt, 2048 if not args.layers else prompt}):
+    for toks in ([] if args.no_prefill_leg else sorted({prompt, 2048 if not args.layers else prompt})):
         prefill[f"{toks}_tokens"] = timed_prefill(model, shape, batch, toks, world, dev, peaks, barrier)
     # ---- device-timed value ------------------------------------------------------------
     model.prefill(prompt_host.to(dev))
