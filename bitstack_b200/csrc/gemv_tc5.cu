@@ -416,6 +416,12 @@ __global__ void __launch_bounds__(kZprepThreads) zprep_tc5_kernel(const __grid_c
 #define TR_BEGIN(var) do { } while (0)
 #define TR_ADD(slot, var) do { } while (0)
 #endif
+// wall-clock mark of one thread into the CTA's trace record (slots 16-31)
+#ifdef BSB_TRACE
+#define TR_NS(slot) do { if (P.trace) P.trace[(int64_t)blockIdx.x * 32 + (slot)] = global_ns(); } while (0)
+#else
+#define TR_NS(slot) do { } while (0)
+#endif
 // timing experiments of the tuning build select a mode at run time; the product build has none of it
 #ifdef BSB_TUNING
 #define DBG_IS(n) (P.dbg == (n))
@@ -463,7 +469,7 @@ struct __align__(1024) SmemLayout {
   int failed;                           // a wait of this CTA gave up: its outputs are marked NaN
   int n_pending;
   int pending[2][2];                    // row groups shared with other CTAs (at most the first and the last): weight, row group
-  int last;
+  int last[2];                          // this CTA was the last to deliver row group pending[q]
 };
 
 constexpr int kWarpMma = 8;     // warps 8, 9: MMA issuers 0, 1
@@ -544,7 +550,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
   // wait, 12 CTA total, 13 set-up
 #ifdef BSB_TRACE
   unsigned long long* tr = (P.trace && lane == 0 && (warp == 0 || warp == kWarpMma || warp == kWarpLoad || warp == kWarpEpi))
-                               ? P.trace + (int64_t)blockIdx.x * 16 : nullptr;
+                               ? P.trace + (int64_t)blockIdx.x * 32 : nullptr;
 #endif
   TR_BEGIN(t_cta);
   const unsigned long long wait_ns = P.wait_ns;
@@ -601,6 +607,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
                       wk.rg * kRows + t * kTileRows, wk.js, &S.sfull[slot]);
         wk.advance(P, kRows);
       }
+      TR_NS(19);
     }
   } else if (warp == kWarpLoad + 1) {
     // ---- Z' loader: one 16 KB bulk copy per step ---------------------------------------------
@@ -614,8 +621,10 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
         const uint8_t* zsrc = P.zops + ((int64_t)(P.blk_base[wk.wi] + wk.js) * NCH + wk.ci) * kSlabBytes;
         mbar_expect_tx(&S.zfull[slot], kSlabBytes);
         bulk_g2s(S.zs[slot], zsrc, kSlabBytes, &S.zfull[slot]);
+        if (g == 0) TR_NS(24);
         wk.advance(P, kRows);
       }
+      TR_NS(20);
     }
   } else if (warp == kWarpMma || warp == kWarpMma + 1) {
     // ---- MMA issuer e: RT == 1: words 8e .. 8e+7 of every chunk; RT == 2: all 16 words for row
@@ -648,7 +657,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
         TR_BEGIN(t1);
         if (!mbar_wait(&S.zfull[zslot], (g / kNZr) & 1, wait_ns)) { if (leader) GIVE_UP(2); ok = false; break; }
         TR_ADD(5, t1);
-        if (g == 0 && leader) { TL_MIN(4); TL_MAX(11); }
+        if (g == 0 && leader) { TL_MIN(4); TL_MAX(11); if (e == 0) TR_NS(21); }
         const uint32_t zaddr = smem_u32(S.zs[zslot]) + (RT == 1 ? (uint32_t)e * 8u * 1024u * R : 0u);
         const uint32_t dcol = tbase + (e * kND + b) * kDCols;
 #pragma unroll 1
@@ -682,6 +691,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
         wk.advance(P, kRows);
       }
       TR_ADD(4, t_mma);
+      if (leader && e == 0) TR_NS(17);
     }
   } else if (warp < kWarpMma) {
     // ---- producer group e: one sign row per thread.  RT == 1: bytes 32e .. 32e+31 of the row
@@ -743,6 +753,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
         }
       }
       TR_ADD(0, t_prod);
+      if (tid == 0) TR_NS(16);
     }
   } else if (warp >= kWarpEpi) {
     // ---- epilogue warps: y[m] += sum_r U_j[m,r] (T[m,r] / s_r - K_r) per block segment; T = sum
@@ -862,8 +873,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
             yacc[t][r] = 0.f;
           }
         }
-        if (!direct) {
-          __threadfence();
+        if (!direct) {   // (made visible to the other CTAs by the counting thread's fence at the end of the kernel)
           if (rtid == 0) {
             S.pending[n_pend][0] = wk.wi;
             S.pending[n_pend][1] = wk.rg;
@@ -877,7 +887,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
       wk.advance(P, kRows, len);
     }
     TR_ADD(10, t_epi);
-    if (warp == kWarpEpi && lane == 0) TL_MAX(5);
+    if (warp == kWarpEpi && lane == 0) { TL_MAX(5); TR_NS(18); }
     }
   }
 
@@ -889,7 +899,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
   if (P.trace) {
     if (tid == 0) S.trace[15] = global_ns();
     __syncthreads();
-    if (tid < 16) P.trace[(int64_t)blockIdx.x * 16 + tid] = S.trace[tid];
+    if (tid < 16) P.trace[(int64_t)blockIdx.x * 32 + tid] = S.trace[tid];
   }
 #endif
   if (warp == kWarpLoad) {
@@ -934,48 +944,58 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_tc5_kernel(const __grid_cons
     __syncthreads();
   }
   // ---- shared row groups: the last CTA to deliver adds the partial sums in CTA order ------
+  // Both row groups of the CTA are handled side by side: thread 0 counts the first one in, thread 256 the second, and
+  // threads 0-255 / 256-511 add up whichever of the two this CTA completed.  The block barrier above ordered every
+  // thread's partial sums before the counting thread's release, which orders them before the count; on the reading
+  // side the acquiring count and the barrier below order the other CTAs' sums before the loads (strong loads, from L2).
   const int n_pending = S.n_pending;
-  if (tid == 0) { TL_MAX(6); TL_MIN(10); }
+  if (tid == 0) { TL_MAX(6); TL_MIN(10); TR_NS(22); }
   if (n_pending == 0) return;
   asm volatile("griddepcontrol.wait;" ::: "memory");     // the counters were zeroed by the Z' kernel
-  for (int q = 0; q < n_pending; ++q) {
-    const int wi = S.pending[q][0], rg = S.pending[q][1];
-    const bsb_weight& w = P.w[wi];
-    const int per_rg = w.blocks * NCH;
-    const int gs = P.step_base[wi] + rg * per_rg, ge = gs + per_rg;   // steps of the row group
-    const int c_first = cta_of_step(P, gs), c_last = cta_of_step(P, ge - 1);
-    __syncthreads();
-    if (tid == 0) {
-      const int old = atomicAdd(&P.counters[P.seg_base[wi] + rg], 1);
-      S.last = (old == c_last - c_first);
+  const int q = tid >> 8, rl = tid & 255;
+  int wi = 0, rg = 0, gs = 0, c_first = 0, c_last = -1;
+  if (q < n_pending) {
+    wi = S.pending[q][0];
+    rg = S.pending[q][1];
+    const int per_rg = P.w[wi].blocks * NCH;
+    gs = P.step_base[wi] + rg * per_rg;                                   // steps gs .. gs + per_rg - 1 are the row group's
+    c_first = cta_of_step(P, gs);
+    c_last = cta_of_step(P, gs + per_rg - 1);
+    if (rl == 0) {
+      int old;   // release of this CTA's sums and acquire of the others' in one operation
+      asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(old) : "l"(P.counters + P.seg_base[wi] + rg) : "memory");
+      S.last[q] = (old == c_last - c_first);
     }
-    __syncthreads();
-    if (!S.last) continue;
-    __threadfence();
-    const int m = rg * kRows + tid;
-    if (tid < kRows && m < w.out_features) {
+  }
+  __syncthreads();
+  if (q < n_pending && S.last[q]) {
+    const bsb_weight& w = P.w[wi];
+    const int m = rg * kRows + rl;
+    if (rl < kRows && m < w.out_features) {
 #pragma unroll
       for (int r = 0; r < R; ++r) {
         float sum = 0.f;
-        // eight loads in flight at a time; the additions stay in CTA order (bit-identical run to run)
-        for (int c0 = c_first; c0 <= c_last; c0 += 8) {
-          float v[8];
+        // kFix loads in flight at a time; the additions stay in CTA order (bit-identical run to run)
+        constexpr int kFix = (R == 1) ? 16 : 8;
+        for (int c0 = c_first; c0 <= c_last; c0 += kFix) {
+          float v[kFix];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int c = c0 + i;
+          for (int i = 0; i < kFix; ++i) {
+            const int c = min(c0 + i, c_last);
             // the row group is CTA c's first row segment unless it starts after c's first step
             const int slot = (gs <= first_step_of_cta(P, c)) ? 0 : 1;
-            v[i] = (c <= c_last) ? __ldcg(P.partials + (((int64_t)c * 2 + slot) * R + r) * kRows + tid) : 0.f;
+            asm volatile("ld.relaxed.gpu.global.f32 %0, [%1];" : "=f"(v[i]) : "l"(P.partials + (((int64_t)c * 2 + slot) * R + r) * kRows + rl));
+            if (c0 + i > c_last) v[i] = 0.f;
           }
 #pragma unroll
-          for (int i = 0; i < 8; ++i) sum += v[i];
+          for (int i = 0; i < kFix; ++i) sum += v[i];
         }
         if (w.bias) sum += __half2float(reinterpret_cast<const __half*>(w.bias)[m]);
         store_y(P, wi, r, m, sum);
       }
     }
   }
-  if (tid == 0) TL_MAX(6);
+  if (tid == 0) { TL_MAX(6); TR_NS(23); }
 }
 
 struct TcPlan {
