@@ -45,7 +45,7 @@ TARGET_PACKED_BYTES = int(5.5e9)
 
 
 # DRAM bytes moved per algorithmic byte by the decode kernel: dram__bytes_read.sum + dram__bytes_write.sum of a
-# profiler capture of one launch (127.87 + 4.71 MB) over that launch's algorithmic bytes (126.91 MB); the
+# profiler capture of one launch (133.0 + 3.9 MB) over that launch's algorithmic bytes (126.91 MB); the
 # kernel streams every packed byte once, so the traffic of other launches scales with their bytes.
 NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = (133.0 + 3.9) / 126.9146
 
