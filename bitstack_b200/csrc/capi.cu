@@ -95,7 +95,15 @@ static const int kFusedRowsMax = 16;
 
 static int pick_algo(const bsb_weight& w, int64_t rows, int algo) {
   if (algo != BSB_ALGO_AUTO) return algo;
-  if (rows <= kDecodeRowsMax && gemv_tc5_supported(w)) return BSB_ALGO_GEMV_TC5;   // two rows per pass: cheaper than rebuilding W up to here
+  if (rows <= kDecodeRowsMax && gemv_tc5_supported(w)) {
+    // two rows per pass: cheaper than anything else up to here, except on small weights, where the fixed cost of
+    // every pass dominates and one fused sign-GEMM call serves all rows (measured with 8 blocks, L2 flushed:
+    // 4096 x 4096 at 6 rows 101 -> 63 us, at 4 rows 68 -> 63; 1024 x 4096 at 4 rows 58 -> 34)
+    const int64_t signs = (int64_t)w.out_features * w.in_features * w.blocks;
+    const bool small = (rows >= 3 && signs <= (64ll << 20)) || (rows >= 5 && signs <= (160ll << 20));
+    if (small && signgemm_mma_supported(w, rows)) return BSB_ALGO_SIGN_GEMM_MMA;
+    return BSB_ALGO_GEMV_TC5;
+  }
   // 7 .. 16 rows: the fused sign-GEMM (W never leaves the multiprocessor) beats rebuilding W; above that the sign stage,
   // which is paid per block and per 16-row tile of the batch in the register variant, loses to rebuild + GEMM
   // (measured on 14336 x 4096, 8 blocks: 159 us against 199 at 16 rows, 214 against 200 at 32)

@@ -5,14 +5,14 @@
 // (bitstack/modules/BitStackLinear.py:116-148; bitstack/utils/inference_utils.py:286-387).
 //
 // Per warp: 16 rows of W.  Per (64-column chunk, block j):
-//   MMA 1   P = U_j[16 rows] . Vt_j[chunk]            warp-level m16n8k16 MMAs, fp32 fragments in registers
-//   sign    the accumulator fragment of MMA 1 IS the A fragment of the next MMA once rounded to fp16x2; each pair
-//           is rounded with one cvt and signed with one LOP3 against the shifted sign word (pairing trick: the K
-//           order inside every 32-column group is (16, 0, 17, 1, ..., 31, 15), so the two sign bits of a pair sit
-//           16 apart in the byte-swapped word)
+//   MMA 1   P = U_j[16 rows] . Vt_j[chunk]            warp-level m16n8k16 MMAs with fp16 accumulators: the result is
+//           the fp16 W tile the reference rounds its products to, as packed pairs in registers
+//   sign    the accumulator fragment of MMA 1 IS the A fragment of the next MMA; each pair is signed with one LOP3
+//           against the shifted sign word (pairing trick: the K order inside every 32-column group is
+//           (16, 0, 17, 1, ..., 31, 15), so the two sign bits of a pair sit 16 apart in the byte-swapped word)
 //   MMA 2   D[16 rows][T] += A . x'[chunk]^T          fp32 accumulation over chunks and blocks in registers
 // Nothing goes through shared or tensor memory between the two MMAs, which is what the step needs: it is bound by
-// the ~2 instructions per (element, block) of the sign stage and by latency, not by tensor throughput -- the
+// the instructions per (element, block) of the sign stage and the legacy tensor pipe, not by memory -- the
 // tcgen05 variant pays a tensor-memory round trip per step and is slower on these shapes (measured, see the
 // batch-path notes).  Vt (column-permuted) and x' chunks are staged in shared memory with cp.async, double buffered.
 // A CTA = 8 warps = 128 rows x a K range (split-K over CTAs); fp32 partials are added in split order by a last
@@ -36,11 +36,13 @@ __device__ __forceinline__ void mma_f16_16816(float (&d)[4], const uint32_t (&a)
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ void mma_f16_16816_zero(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+// a rank-16 product with fp16 accumulators, from zero: the two result registers are the rounded pairs (row g | row g + 8,
+// columns 2t, 2t+1), i.e. already one half of the next MMA's A fragment
+__device__ __forceinline__ void mma_f16_16816_h(uint32_t (&d)[2], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
-      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
-      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
+      "mma.sync.aligned.m16n8k16.row.col.f16.f16.f16.f16 {%0,%1}, {%2,%3,%4,%5}, {%6,%7}, {%8,%8};\n"
+      : "=r"(d[0]), "=r"(d[1])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0u));
 }
 __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_ptr) {
   const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem_ptr);
@@ -56,10 +58,9 @@ template <int N>
 __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
 }
-// two products -> fp16x2 (high half = hi, low half = lo); both signs flipped where bit 31 / bit 15 of `bits` is CLEAR
-__device__ __forceinline__ uint32_t pack_signed(float hi, float lo, uint32_t bits) {
-  uint32_t p, out;
-  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(p) : "f"(hi), "f"(lo));
+// a packed pair with both signs flipped where bit 31 / bit 15 of `bits` is CLEAR
+__device__ __forceinline__ uint32_t sign_pair(uint32_t p, uint32_t bits) {
+  uint32_t out;
   asm("lop3.b32 %0, %1, %2, %3, 0xD2;" : "=r"(out) : "r"(p), "r"(bits), "r"(0x80008000u));   // p ^ (~bits & mask)
   return out;
 }
@@ -143,15 +144,15 @@ __global__ void __launch_bounds__(256) signgemm_mma_kernel(const SgmParams P) {
   const __half* u_all = reinterpret_cast<const __half*>(w.u);
   // operands of a block that come straight from global memory: the A fragment of U_j (rows m0+g / m0+g+8, ranks
   // 2t,2t+1 / 2t+8,2t+9) and the 64 sign bits of the two rows for this chunk
-  auto fetch = [&](int j, int c, uint32_t (&af)[4], uint2& lo, uint2& hi) {
-    const __half* u = u_all + (int64_t)j * w.u_block_stride;
-    af[0] = __ldg(reinterpret_cast<const uint32_t*>(u + (int64_t)(m0 + g) * 16 + 2 * t));
-    af[1] = __ldg(reinterpret_cast<const uint32_t*>(u + (int64_t)(m0 + g + 8) * 16 + 2 * t));
-    af[2] = __ldg(reinterpret_cast<const uint32_t*>(u + (int64_t)(m0 + g) * 16 + 2 * t + 8));
-    af[3] = __ldg(reinterpret_cast<const uint32_t*>(u + (int64_t)(m0 + g + 8) * 16 + 2 * t + 8));
-    const uint8_t* q = w.qweight + (int64_t)j * w.q_block_stride;
-    lo = __ldg(reinterpret_cast<const uint2*>(q + ((int64_t)(m0 + g) * N + (int64_t)c * kChunk) / 8));
-    hi = __ldg(reinterpret_cast<const uint2*>(q + ((int64_t)(m0 + g + 8) * N + (int64_t)c * kChunk) / 8));
+  const __half* u_thr = u_all + (int64_t)(m0 + g) * 16 + 2 * t;          // this thread's first U pair of block 0
+  const uint8_t* q_thr = w.qweight + (int64_t)(m0 + g) * (N / 8);          // this thread's first sign row of block 0
+  auto fetch = [&](const __half* u, const uint8_t* q, uint32_t (&af)[4], uint2& lo, uint2& hi) {
+    af[0] = __ldg(reinterpret_cast<const uint32_t*>(u));
+    af[1] = __ldg(reinterpret_cast<const uint32_t*>(u + 8 * 16));
+    af[2] = __ldg(reinterpret_cast<const uint32_t*>(u + 8));
+    af[3] = __ldg(reinterpret_cast<const uint32_t*>(u + 8 * 16 + 8));
+    lo = __ldg(reinterpret_cast<const uint2*>(q));
+    hi = __ldg(reinterpret_cast<const uint2*>(q + N));                     // 8 rows further: 8 * N / 8 bytes
   };
 
   if (c_begin < c_end) load_chunk(0, c_begin);
@@ -180,31 +181,35 @@ __global__ void __launch_bounds__(256) signgemm_mma_kernel(const SgmParams P) {
       }
       uint32_t a_next[4];
       uint2 lo_next, hi_next;
-      fetch(0, c, a_next, lo_next, hi_next);
+      const __half* u_j = u_thr;
+      const uint8_t* q_j = q_thr + c * (kChunk / 8);
+      fetch(u_j, q_j, a_next, lo_next, hi_next);
 #pragma unroll 1
       for (int j = 0; j < nb; ++j) {
         const uint32_t a[4] = {a_next[0], a_next[1], a_next[2], a_next[3]};
         // byte swap: column c of a 32-group -> bit 31 - c; the shift by t selects this thread's pair of every 8-column tile
         const uint32_t wg[2] = {__byte_perm(lo_next.x, 0, 0x0123) << t, __byte_perm(lo_next.y, 0, 0x0123) << t};
         const uint32_t wh[2] = {__byte_perm(hi_next.x, 0, 0x0123) << t, __byte_perm(hi_next.y, 0, 0x0123) << t};
-        if (j + 1 < nb) fetch(j + 1, c, a_next, lo_next, hi_next);
+        u_j += w.u_block_stride;
+        q_j += w.q_block_stride;
+        if (j + 1 < nb) fetch(u_j, q_j, a_next, lo_next, hi_next);
         const __half* vj = vs + j * 16 * kRowHalves;
 #pragma unroll
         for (int p = 0; p < 4; ++p) {   // 16 K positions of MMA 2 = two 8-column tiles of MMA 1
           uint32_t b[4];
           // lanes 0-7: ranks 0-7 @ tile 2p; 8-15: ranks 8-15 @ same tile; 16-23 / 24-31: the same for tile 2p+1
           ldmatrix_x4_trans(b, vj + ((lane & 7) + ((lane >> 3) & 1) * 8) * kRowHalves + (2 * p + (lane >> 4)) * 8);
-          float d0[4], d1[4];
-          mma_f16_16816_zero(d0, a, b[0], b[1]);
-          mma_f16_16816_zero(d1, a, b[2], b[3]);
+          uint32_t d0[2], d1[2];
+          mma_f16_16816_h(d0, a, b[0], b[1]);
+          mma_f16_16816_h(d1, a, b[2], b[3]);
           // pair index inside the 32-group = 4 (tile % 4) + t: the words are pre-shifted by t
           const int sh = (p & 1) * 8;
           const uint32_t sg = wg[p >> 1], sh2 = wh[p >> 1];
           uint32_t a2[4];
-          a2[0] = pack_signed(d0[1], d0[0], sg << sh);          // row g,     K 2t, 2t+1
-          a2[1] = pack_signed(d0[3], d0[2], sh2 << sh);         // row g + 8
-          a2[2] = pack_signed(d1[1], d1[0], sg << (sh + 4));    // row g,     K 2t+8, 2t+9
-          a2[3] = pack_signed(d1[3], d1[2], sh2 << (sh + 4));   // row g + 8
+          a2[0] = sign_pair(d0[0], sg << sh);          // row g,     K 2t, 2t+1
+          a2[1] = sign_pair(d0[1], sh2 << sh);         // row g + 8
+          a2[2] = sign_pair(d1[0], sg << (sh + 4));    // row g,     K 2t+8, 2t+9
+          a2[3] = sign_pair(d1[1], sh2 << (sh + 4));   // row g + 8
 #pragma unroll
           for (int nt = 0; nt < TN; ++nt) {
             uint32_t b0, b1;

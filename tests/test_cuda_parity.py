@@ -360,6 +360,11 @@ def test_decode_kernel_row_pairs(dev, rows):
     xs[:, :1024] = x
     y = mods[0](xs[:, :1024]).float().cpu().numpy()
     assert errs(y, refs[0])[0] <= EXACT_TOL
+    # the automatic choice (small weights at 3-6 rows: one fused sign-GEMM call instead of a decode pass per row pair)
+    q, u, vt = orc.synthetic_layer(512, 1024, 3, seed=40)
+    auto = make_module(q, u, vt, None, dev, level=6)
+    e_max, e_l2 = errs(auto(x).float().cpu().numpy(), refs[0])
+    assert e_max <= EXACT_TOL and e_l2 <= EXACT_TOL, (e_max, e_l2)
 
 
 def test_linearity_and_block_additivity(dev):
