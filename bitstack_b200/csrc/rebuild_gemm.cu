@@ -1,6 +1,6 @@
 // Batch / prefill path, first generation: rebuild the fp16 weight from the packed
-// blocks (rank-16 products on the tensor cores, signs applied in registers, fp32
-// accumulation over blocks, ONE fp16 rounding), then a dense x.W^T contraction.
+// blocks (rank-16 products on the tensor cores rounded to fp16, signs applied to packed
+// pairs in registers, fp16 sum over blocks like the reference), then a dense x.W^T contraction.
 //
 // Replaces, for rows > 4, what the reference does with an unpack kernel, a
 // reconstruct kernel and cuBLAS (bitstack/modules/BitStackLinear.py:116-148,
@@ -18,14 +18,6 @@ __device__ __forceinline__ void mma_f16_16816(float (&d)[4], const uint32_t (&a)
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// same with a zero C operand: D = A.B (no register tuple to clear before every MMA)
-__device__ __forceinline__ void mma_f16_16816_zero(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
-      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
-      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
-}
-
 __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_ptr) {
   const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem_ptr);
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
@@ -33,17 +25,31 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* 
                : "r"(addr));
 }
 
-// a ^ (~b & 0x80000000): flips the sign of the fp32 pattern `a` when bit 31 of `b` is clear
-__device__ __forceinline__ uint32_t flip_if_clear(uint32_t a, uint32_t b) {
+// rank-16 product with fp16 accumulators, from zero: the two result registers are the rounded products of rows g and
+// g + 8, columns 2t, 2t+1 of the 8-column tile, packed as pairs
+__device__ __forceinline__ void mma_f16_16816_h(uint32_t (&d)[2], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f16.f16.f16.f16 {%0,%1}, {%2,%3,%4,%5}, {%6,%7}, {%8,%8};\n"
+      : "=r"(d[0]), "=r"(d[1])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0u));
+}
+
+// p ^ (~bits & 0x80008000): flips the signs of the packed pair `p` where bit 31 / bit 15 of `bits` is clear
+__device__ __forceinline__ uint32_t sign_pair(uint32_t p, uint32_t bits) {
   uint32_t out;
   // minterms of a ^ (~b & c) over (a, b, c) with a = 0xF0, b = 0xCC, c = 0xAA: 0xF0 ^ (0x33 & 0xAA) = 0xD2
-  asm("lop3.b32 %0, %1, %2, %3, 0xD2;" : "=r"(out) : "r"(a), "r"(b), "r"(0x80000000u));
+  asm("lop3.b32 %0, %1, %2, %3, 0xD2;" : "=r"(out) : "r"(p), "r"(bits), "r"(0x80008000u));
   return out;
 }
 
 // ---------------------------------------------------------------------------
 // rebuild: CTA = 8 warps = 128 rows x 64 columns of W; warp = 16 rows x 64 cols
 // ---------------------------------------------------------------------------
+// The sign stage works on PAIRS: the staged Vt slab has the columns of every 32-group in the order
+// (16, 0, 17, 1, ..., 31, 15), so an accumulator register of the product holds columns 16 + k (low half) and k (high
+// half) of the group; the byte-swapped sign word of the group shifted left by k has exactly those two sign bits at
+// bits 15 and 31: one shift, one LOP3 and one packed add per pair and block.  The sum over blocks is taken in fp16,
+// block after block, as the reference's own reconstruction does (bitstack/modules/BitStackLinear.py:7-15,88-100).
 constexpr int kRbCols = 64;
 constexpr int kRbRowsPerCta = 128;
 constexpr int kRbRowTiles = 4;             // 128-row tiles per CTA
@@ -68,24 +74,33 @@ __global__ void __launch_bounds__(256) rebuild_weight_kernel(bsb_weight w, __hal
   if ((blockIdx.y * kRbRowTiles + rt) * kRbRowsPerCta >= M) break;   // uniform for the CTA
   const bool active = m0 < M;  // out_features is a multiple of 16
 
-  float acc[8][4];
+  __half2 acc[8][2];           // [8-position tile of the permuted order][row g / g + 8]
 #pragma unroll
-  for (int i = 0; i < 8; ++i)
-#pragma unroll
-    for (int c = 0; c < 4; ++c) acc[i][c] = 0.f;
+  for (int i = 0; i < 8; ++i) acc[i][0] = acc[i][1] = __float2half2_rn(0.f);
 
-  for (int j0 = 0; j0 < w.blocks; j0 += kRbBlockGroup) {
+  // blocks are added from the last to the first: later blocks approximate ever smaller residuals, so the fp16
+  // running sum stays small until the dominant first blocks arrive and is rounded at full magnitude only then
+  for (int j0 = ((w.blocks - 1) / kRbBlockGroup) * kRbBlockGroup; j0 >= 0; j0 -= kRbBlockGroup) {
     const int nj = min(kRbBlockGroup, w.blocks - j0);
+    if (nj <= 0) break;   // no active block: W = 0
     if (rt == 0 || !one_group) {
     __syncthreads();  // previous group fully consumed
-    // stage Vt[j0..j0+nj)[0..16)[n0..n0+64): 16 B per thread per step
-    for (int i = threadIdx.x; i < nj * 16 * (kRbCols / 8); i += blockDim.x) {
-      const int jj = i / (16 * (kRbCols / 8));
-      const int rem = i % (16 * (kRbCols / 8));
-      const int r = rem / (kRbCols / 8), c8 = rem % (kRbCols / 8);
-      const uint4 v = __ldg(reinterpret_cast<const uint4*>(
-          vt_all + (int64_t)(j0 + jj) * w.vt_block_stride + (int64_t)r * N + n0 + c8 * 8));
-      *reinterpret_cast<uint4*>(&vt_s[jj][r][c8 * 8]) = v;
+    // stage Vt[j0..j0+nj)[0..16)[n0..n0+64) in the pair order: a thread takes columns 8h..8h+7 and 16+8h..16+8h+7 of
+    // a 32-group and writes them interleaved (positions 16h .. 16h+15 of the group)
+    for (int i = threadIdx.x; i < nj * 16 * 4; i += blockDim.x) {
+      const int jj = i / 64, rem = i % 64;
+      const int r = rem / 4, grp = (rem >> 1) & 1, h = rem & 1;
+      const __half* src = vt_all + (int64_t)(j0 + jj) * w.vt_block_stride + (int64_t)r * N + n0 + grp * 32 + h * 8;
+      const uint4 lo = __ldg(reinterpret_cast<const uint4*>(src));        // columns k = 8h .. 8h+7      -> odd positions
+      const uint4 hi = __ldg(reinterpret_cast<const uint4*>(src + 16));   // columns 16 + k              -> even positions
+      uint4 o0, o1;
+      o0.x = __byte_perm(hi.x, lo.x, 0x5410); o0.y = __byte_perm(hi.x, lo.x, 0x7632);
+      o0.z = __byte_perm(hi.y, lo.y, 0x5410); o0.w = __byte_perm(hi.y, lo.y, 0x7632);
+      o1.x = __byte_perm(hi.z, lo.z, 0x5410); o1.y = __byte_perm(hi.z, lo.z, 0x7632);
+      o1.z = __byte_perm(hi.w, lo.w, 0x5410); o1.w = __byte_perm(hi.w, lo.w, 0x7632);
+      uint4* dst = reinterpret_cast<uint4*>(&vt_s[jj][r][grp * 32 + h * 16]);
+      dst[0] = o0;
+      dst[1] = o1;
     }
     __syncthreads();
     }
@@ -93,26 +108,30 @@ __global__ void __launch_bounds__(256) rebuild_weight_kernel(bsb_weight w, __hal
 
     // operands of a block that come straight from global memory (A fragment of U_j: rows m0+g /
     // m0+g+8, ranks 2t,2t+1 / 2t+8,2t+9; 64 sign bits of the two rows) are fetched one block ahead
-    auto fetch = [&](int j, uint32_t (&af)[4], uint2& lo, uint2& hi) {
-      const __half* u = u_all + (int64_t)j * w.u_block_stride;
-      af[0] = __ldg(reinterpret_cast<const uint32_t*>(u + (int64_t)(m0 + g) * 16 + 2 * t));
-      af[1] = __ldg(reinterpret_cast<const uint32_t*>(u + (int64_t)(m0 + g + 8) * 16 + 2 * t));
-      af[2] = __ldg(reinterpret_cast<const uint32_t*>(u + (int64_t)(m0 + g) * 16 + 2 * t + 8));
-      af[3] = __ldg(reinterpret_cast<const uint32_t*>(u + (int64_t)(m0 + g + 8) * 16 + 2 * t + 8));
-      const uint8_t* q = w.qweight + (int64_t)j * w.q_block_stride;
-      lo = __ldg(reinterpret_cast<const uint2*>(q + ((int64_t)(m0 + g) * N + n0) / 8));
-      hi = __ldg(reinterpret_cast<const uint2*>(q + ((int64_t)(m0 + g + 8) * N + n0) / 8));
+    const __half* u_j = u_all + (int64_t)(j0 + nj - 1) * w.u_block_stride + (int64_t)(m0 + g) * 16 + 2 * t;
+    const uint8_t* q_j = w.qweight + (int64_t)(j0 + nj - 1) * w.q_block_stride + ((int64_t)(m0 + g) * N + n0) / 8;
+    auto fetch = [&](const __half* u, const uint8_t* q, uint32_t (&af)[4], uint2& lo, uint2& hi) {
+      af[0] = __ldg(reinterpret_cast<const uint32_t*>(u));
+      af[1] = __ldg(reinterpret_cast<const uint32_t*>(u + 8 * 16));
+      af[2] = __ldg(reinterpret_cast<const uint32_t*>(u + 8));
+      af[3] = __ldg(reinterpret_cast<const uint32_t*>(u + 8 * 16 + 8));
+      lo = __ldg(reinterpret_cast<const uint2*>(q));
+      hi = __ldg(reinterpret_cast<const uint2*>(q + N));   // 8 rows further
     };
     uint32_t a_next[4];
     uint2 lo_next, hi_next;
-    fetch(j0, a_next, lo_next, hi_next);
-    for (int jj = 0; jj < nj; ++jj) {
-      uint32_t a[4] = {a_next[0], a_next[1], a_next[2], a_next[3]};
-      const uint2 lo_t = make_uint2(lo_next.x << (2 * t), lo_next.y << (2 * t));
-      const uint2 hi_t = make_uint2(hi_next.x << (2 * t), hi_next.y << (2 * t));
-      if (jj + 1 < nj) fetch(j0 + jj + 1, a_next, lo_next, hi_next);
+    fetch(u_j, q_j, a_next, lo_next, hi_next);
+#pragma unroll 1
+    for (int jj = nj - 1; jj >= 0; --jj) {
+      const uint32_t a[4] = {a_next[0], a_next[1], a_next[2], a_next[3]};
+      // byte swap: column c of a 32-group -> bit 31 - c; the shift by t selects this thread's pair of every tile
+      const uint32_t wg[2] = {__byte_perm(lo_next.x, 0, 0x0123) << t, __byte_perm(lo_next.y, 0, 0x0123) << t};
+      const uint32_t wh[2] = {__byte_perm(hi_next.x, 0, 0x0123) << t, __byte_perm(hi_next.y, 0, 0x0123) << t};
+      u_j -= w.u_block_stride;
+      q_j -= w.q_block_stride;
+      if (jj > 0) fetch(u_j, q_j, a_next, lo_next, hi_next);
 #pragma unroll
-      for (int pair = 0; pair < 4; ++pair) {  // two 8-column tiles per ldmatrix.x4
+      for (int pair = 0; pair < 4; ++pair) {  // two 8-position tiles per ldmatrix.x4
         uint32_t b[4];
         // lanes 0-7: ranks 0-7 @ tile 2*pair; 8-15: ranks 8-15 @ same tile;
         // 16-23 / 24-31: the same for tile 2*pair+1
@@ -121,20 +140,13 @@ __global__ void __launch_bounds__(256) rebuild_weight_kernel(bsb_weight w, __hal
         ldmatrix_x4_trans(b, &vt_s[jj][row][col]);
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          const int i = 2 * pair + h;
-          float d[4];
-          mma_f16_16816_zero(d, a, b[2 * h], b[2 * h + 1]);
-          // column 8i+2t is bit 7-2t of byte i: the words were shifted left by 2t once per block, so the
-          // shift that brings an element's bit to bit 31 is a compile-time constant (the compiler is free to
-          // place it on the multiply pipe); d is flipped when the bit is clear, one LOP3 per element
-          const uint32_t wlo = (i < 4) ? lo_t.x : lo_t.y;
-          const uint32_t whi = (i < 4) ? hi_t.x : hi_t.y;
-          constexpr int kBase = 24;
-          const int sh = kBase - 8 * (i & 3);
-          acc[i][0] += __uint_as_float(flip_if_clear(__float_as_uint(d[0]), wlo << sh));
-          acc[i][1] += __uint_as_float(flip_if_clear(__float_as_uint(d[1]), wlo << (sh + 1)));
-          acc[i][2] += __uint_as_float(flip_if_clear(__float_as_uint(d[2]), whi << sh));
-          acc[i][3] += __uint_as_float(flip_if_clear(__float_as_uint(d[3]), whi << (sh + 1)));
+          const int i = 2 * pair + h;          // tile i: positions 8i + 2t, 8i + 2t + 1 = pair k = 4 (i % 4) + t of group i / 4
+          uint32_t d[2];
+          mma_f16_16816_h(d, a, b[2 * h], b[2 * h + 1]);
+          const int sh = 4 * (i & 3);
+          const uint32_t s0 = sign_pair(d[0], wg[i >> 2] << sh), s1 = sign_pair(d[1], wh[i >> 2] << sh);
+          acc[i][0] = __hadd2(acc[i][0], *reinterpret_cast<const __half2*>(&s0));
+          acc[i][1] = __hadd2(acc[i][1], *reinterpret_cast<const __half2*>(&s1));
         }
       }
     }
@@ -142,9 +154,18 @@ __global__ void __launch_bounds__(256) rebuild_weight_kernel(bsb_weight w, __hal
   if (!active) continue;
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    const int n = n0 + 8 * i + 2 * t;
-    *reinterpret_cast<__half2*>(out + (int64_t)(m0 + g) * N + n) = __floats2half2_rn(acc[i][0], acc[i][1]);
-    *reinterpret_cast<__half2*>(out + (int64_t)(m0 + g + 8) * N + n) = __floats2half2_rn(acc[i][2], acc[i][3]);
+    // a register holds column 16 + k (low half) and column k (high half) of the 32-group, k = 4 (i % 4) + t.  Lanes
+    // t and t ^ 1 swap halves so that the even lane ends up with columns k, k + 1 and the odd one with 16 + k - 1,
+    // 16 + k: every store is an aligned pair of adjacent columns again
+    const int k = 4 * (i & 3) + t;
+    const int n = n0 + (i >> 2) * 32 + ((t & 1) ? 16 + k - 1 : k);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const uint32_t v = *reinterpret_cast<const uint32_t*>(&acc[i][h]);
+      const uint32_t p = __shfl_xor_sync(0xFFFFFFFFu, v, 1);
+      const uint32_t o = (t & 1) ? __byte_perm(v, p, 0x1054) : __byte_perm(v, p, 0x7632);
+      *reinterpret_cast<uint32_t*>(out + (int64_t)(m0 + g + 8 * h) * N + n) = o;
+    }
   }
   }
 }

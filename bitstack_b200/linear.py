@@ -256,7 +256,8 @@ class BitStackLinear(nn.Module):
     # -------------------------------------------------------------------- forward
     @torch.no_grad()
     def reconstruct_weight(self):
-        """fp16 [out, in] weight of the active blocks (fp32 accumulation, one rounding)."""
+        """fp16 [out, in] weight of the active blocks (products rounded to fp16 and summed in fp16 like the reference's
+        reconstruction, last block first; the general kernel for ragged shapes sums in fp32)."""
         dev = self.qweight.device if hasattr(self, "qweight") else self.u_0.device
         d = self.weight_desc(dev)
         w = torch.empty(self.out_features, self.in_features, dtype=torch.float16, device=dev)
