@@ -66,6 +66,24 @@ def get_workspace(device: torch.device, nbytes: int) -> torch.Tensor:
     return ent[0]
 
 
+@torch.no_grad()
+def truncated_svd(a, k, oversample=16, power_iters=4, generator=None):
+    """Leading k singular triplets of the fp32 matrix `a` [m, n]: randomised range finder (k + oversample Gaussian
+    probes) with `power_iters` re-orthogonalised subspace iterations, then an exact SVD of the small projected
+    matrix.  Returns (U [m, k], S [k], Vt [k, n]).  |W| of a weight matrix has one dominant (Perron) direction and a
+    slowly decaying rest, which is why a few power iterations are needed for the trailing ranks."""
+    m, n = a.shape
+    l = min(k + oversample, m, n)
+    omega = torch.randn(n, l, device=a.device, dtype=a.dtype, generator=generator)
+    q, _ = torch.linalg.qr(a @ omega)
+    for _ in range(power_iters):
+        z, _ = torch.linalg.qr(a.t() @ q)
+        q, _ = torch.linalg.qr(a @ z)
+    b = q.t() @ a                                     # [l, n]
+    ub, s, vt = torch.linalg.svd(b, full_matrices=False)
+    return (q @ ub)[:, :k].contiguous(), s[:k].contiguous(), vt[:k, :].contiguous()
+
+
 class BitStackLinear(nn.Module):
     def __init__(self, w_bit, in_features, out_features, k, bias, no_avd, dev, fused_level=0):
         super().__init__()
@@ -93,19 +111,36 @@ class BitStackLinear(nn.Module):
 
     # ------------------------------------------------------------------ offline
     @torch.no_grad()
-    def decompose_weight(self, original_weight):
+    def decompose_weight(self, original_weight, svd="full", oversample=16, power_iters=4, seed=0):
         """Residual sign / rank-k decomposition on the device (same recipe as
         bitstack/modules/BitStackLinear.py:49-75): zeros count as +1, factors are
-        U*sqrt(S), sqrt(S)*Vt of |residual|, the residual uses the fp32 factors."""
+        U*sqrt(S), sqrt(S)*Vt of |residual|, the residual uses the fp32 factors.
+
+        `svd="full"` is the reference's `torch.linalg.svd` of the whole matrix per block.  `svd="randomized"` takes
+        only the leading k triplets with a randomised range finder and `power_iters` subspace iterations
+        (`truncated_svd` below): the cost per block drops from a full decomposition to a few products with
+        (k + oversample)-column matrices.  It is not bit-compatible with the full SVD (the factors differ in the
+        last bits and possibly in sign per rank); tests/test_decompose.py measures what that does to the singular
+        values, to the residual after every block and to the forward."""
+        if svd not in ("full", "randomized"):
+            raise ValueError("svd must be 'full' or 'randomized'")
         weight = original_weight.to(torch.float32)
         shape = weight.shape
+        gen = None
+        if svd == "randomized":
+            gen = torch.Generator(device=weight.device)
+            gen.manual_seed(seed)
         for i in range(self.w_bit):
             sign = weight.sign()
             sign[sign == 0] = 1
-            u, s, vt = torch.linalg.svd(weight.abs(), full_matrices=False)
-            root = torch.diag(torch.sqrt(s[: self.k]))
-            us_k = u[:, : self.k] @ root
-            vt_k = root @ vt[: self.k, :]
+            if svd == "full":
+                u, s, vt = torch.linalg.svd(weight.abs(), full_matrices=False)
+                u, s, vt = u[:, : self.k], s[: self.k], vt[: self.k, :]
+            else:
+                u, s, vt = truncated_svd(weight.abs(), self.k, oversample=oversample, power_iters=power_iters, generator=gen)
+            root = torch.diag(torch.sqrt(s))
+            us_k = u @ root
+            vt_k = root @ vt
             packed = pack_sign(sign.to(torch.int8))
             assert unpack_sign(packed, shape).equal(sign.to(torch.int8))
             setattr(self, f"qweight_{i}", packed)
@@ -117,13 +152,14 @@ class BitStackLinear(nn.Module):
             weight = weight - w_i
 
     @classmethod
-    def from_linear(cls, linear, w_bit, k=1, bias=True, no_avd=False, fused_level=0, name=None, init_only=False):
+    def from_linear(cls, linear, w_bit, k=1, bias=True, no_avd=False, fused_level=0, name=None, init_only=False,
+                    svd="full", **svd_options):
         qlinear = cls(w_bit=w_bit, in_features=linear.in_features, out_features=linear.out_features, bias=bias,
                       k=k, no_avd=no_avd, dev=linear.weight.device, fused_level=fused_level)
         qlinear.name = name
         if init_only:
             return qlinear
-        qlinear.decompose_weight(linear.weight)
+        qlinear.decompose_weight(linear.weight, svd=svd, **svd_options)
         if bias:
             qlinear.bias = linear.bias.detach().to(torch.float16)
         return qlinear
