@@ -233,6 +233,33 @@ class BitStackLlamaDecoder:
         h = F.rms_norm(h[:, -1], (self.shape.hidden,), self.final_norm, self.shape.rms_eps)
         return h @ self.lm_head.t()
 
+    @torch.no_grad()
+    def forward_logits(self, token_ids):
+        """Logits of every position, [B, T, vocab], for token_ids [B, T] on the device (B <= the decoder's batch,
+        T <= max_len; one device).  Uses the first B rows of the KV cache as scratch: call it before `prefill`, not
+        between decode steps.  This is the forward the perplexity evaluations of the importance scoring run."""
+        assert self.world == 1, "forward_logits runs on one device"
+        B, T = token_ids.shape
+        assert B <= self.batch and T <= self.max_len
+        positions = self.arange[:T]
+        h = self.embed.index_select(0, token_ids.reshape(-1)).view(B, T, -1)
+        mask = (self.arange.view(1, -1) <= positions.view(-1, 1)).view(1, 1, T, self.max_len)
+        full_k, full_v = self.k_cache, self.v_cache
+        try:
+            if B < self.batch:
+                self.k_cache = [c[:B] for c in full_k]
+                self.v_cache = [c[:B] for c in full_v]
+            for i in range(self.shape.n_layers):
+                h = self._layer(i, h, positions, positions, mask)
+        finally:
+            self.k_cache, self.v_cache = full_k, full_v
+        h = F.rms_norm(h, (self.shape.hidden,), self.final_norm, self.shape.rms_eps)
+        return h @ self.lm_head.t()
+
+    def bitstack_linears(self):
+        """The BitStack projections in checkpoint order (their `.name` is `layer.{i}.{projection}`)."""
+        return [lay[p] for lay in self.layers for p in PROJ_NAMES]
+
     def _decode_fused(self):
         """One decode step (one new token per sequence) with the fused glue kernels: per layer
         12 launches instead of ~30.  Same math as `_forward` on a single position."""

@@ -171,6 +171,11 @@ class BitStackLinear(nn.Module):
         self._desc = None
 
     # ---------------------------------------------------------------- block count
+    @property
+    def blocks_loaded(self):
+        """Blocks held in memory (set_bit may choose any count up to this one)."""
+        return self._stacked_blocks if self._stacked_blocks else self.w_bit
+
     def pop_one_bit(self):
         self.w_bit -= 1
 
