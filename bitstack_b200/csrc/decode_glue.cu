@@ -72,7 +72,10 @@ __global__ void __launch_bounds__(128) rope_cache_kernel(__half* __restrict__ q,
 //      flight; the 16 partial sums per element are merged in shared memory.
 //   E. every CTA leaves (max, sum, unnormalised output) in `partial`; the last one to arrive on the
 //      head's counter merges the kAttSplits results, writes `out` and resets the counter to 0.
-constexpr int kAttSplits = 4;
+#ifndef BSB_ATT_SPLITS
+#define BSB_ATT_SPLITS 4
+#endif
+constexpr int kAttSplits = BSB_ATT_SPLITS;
 template <int D>
 __global__ void __launch_bounds__(256) decode_attention_kernel(const __half* __restrict__ q, const __half* __restrict__ k,
                                                                const __half* __restrict__ v, const __half* __restrict__ cos_t,
@@ -87,14 +90,28 @@ __global__ void __launch_bounds__(256) decode_attention_kernel(const __half* __r
   __shared__ float s_red[8];
   __shared__ float s_part[kRowsPerPass][D];
   __shared__ int s_last;
-  pdl_enter();
   const int h = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // The position and the cache rows below it were written by kernels that finished before the kernel in front of
+  // this one started (every kernel of the chain waits for its predecessor before it ends), so they may be read
+  // before this kernel's own wait: the first K row of every thread is in flight while the projection kernel drains.
   const int64_t pos = *pos_p;
   if (pos < 0 || pos >= max_len) return;   // out of the cache: nothing is written
   const int hk = h / (Hq / Hkv);
   __half* kc = k_cache + ((int64_t)b * Hkv + hk) * (int64_t)max_len * D;
   __half* vc = v_cache + ((int64_t)b * Hkv + hk) * (int64_t)max_len * D;
+  const int n_all = (int)pos + 1;
+  const int share = (n_all + kAttSplits - 1) / kAttSplits;
+  const int p_lo = min(split * share, n_all);
+  const int n = min(share, n_all - p_lo);
+  uint4 k_first[kVec];
+  const bool have_first = tid < n && p_lo + tid != (int)pos;   // the row of this step's own position is written below
+  if (have_first) {
+    const uint4* row = reinterpret_cast<const uint4*>(kc + (int64_t)(p_lo + tid) * D);
+#pragma unroll
+    for (int c = 0; c < kVec; ++c) k_first[c] = row[c];
+  }
+  pdl_enter();
 
   // ---- A ----
   if (tid < D / 2) {
@@ -118,10 +135,6 @@ __global__ void __launch_bounds__(256) decode_attention_kernel(const __half* __r
   __syncthreads();
 
   // ---- B ----  (positions [p_lo, p_lo + n) of the pos + 1 in the cache; scores are indexed from p_lo)
-  const int n_all = (int)pos + 1;
-  const int share = (n_all + kAttSplits - 1) / kAttSplits;
-  const int p_lo = min(split * share, n_all);
-  const int n = min(share, n_all - p_lo);
   kc += (int64_t)p_lo * D;
   vc += (int64_t)p_lo * D;
   float m_loc = -INFINITY;
@@ -129,7 +142,7 @@ __global__ void __launch_bounds__(256) decode_attention_kernel(const __half* __r
     const uint4* row = reinterpret_cast<const uint4*>(kc + (int64_t)p * D);
     uint4 raw[kVec];
 #pragma unroll
-    for (int c = 0; c < kVec; ++c) raw[c] = row[c];
+    for (int c = 0; c < kVec; ++c) raw[c] = (p == tid && have_first) ? k_first[c] : row[c];
     float dot = 0.f;
 #pragma unroll
     for (int c = 0; c < kVec; ++c) {
