@@ -111,6 +111,11 @@ __global__ void __launch_bounds__(256) decode_attention_kernel(const __half* __r
 #pragma unroll
     for (int c = 0; c < kVec; ++c) k_first[c] = row[c];
   }
+  // the V rows of the share: asked into L2 now, read after the softmax weights are known
+  for (int p = tid; p < 2 * n; p += 256) {
+    const __half* line = vc + (int64_t)(p_lo + (p >> 1)) * D + (p & 1) * (D / 2);   // both halves of a row: two 128-byte lines at D = 128
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(line));
+  }
   pdl_enter();
 
   // ---- A ----
