@@ -16,6 +16,9 @@ __global__ void __launch_bounds__(kRowThreads) add_rmsnorm_kernel(__half* __rest
                                                                   const __half* __restrict__ weight, float eps,
                                                                   __half* __restrict__ y, int hidden, float* __restrict__ absmax) {
   __shared__ float red[32];
+  // the norm weight is a constant that the projections' weight stream has evicted since the last step: it is
+  // asked into L2 while this kernel still waits for the one in front
+  if ((int)threadIdx.x * 64 < hidden) asm volatile("prefetch.global.L2 [%0];" ::"l"(weight + threadIdx.x * 64));
   pdl_enter();
   const int64_t row = blockIdx.x;
   add_rmsnorm_row<false>(h + row * hidden, delta ? delta + row * hidden : nullptr, weight, eps, y + row * hidden, hidden, red,

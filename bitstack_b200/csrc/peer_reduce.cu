@@ -61,6 +61,8 @@ __device__ __forceinline__ int ld_acquire_sys(const int* p) {
 __global__ void __launch_bounds__(kRowThreads) peer_allreduce_add_rmsnorm_kernel(const PeerParams P) {
   __shared__ float red[32];
   __shared__ int s_epoch, s_ok;
+  // the norm weight (a constant, evicted by the weight stream since the last step) is asked into L2 during the wait
+  if ((int)threadIdx.x * 64 < P.width) asm volatile("prefetch.global.L2 [%0];" ::"l"(P.norm_w + threadIdx.x * 64));
   pdl_enter();
   const int r = blockIdx.x, tid = threadIdx.x;
   if (tid == 0) { s_epoch = *reinterpret_cast<volatile int*>(P.local); s_ok = 1; }
