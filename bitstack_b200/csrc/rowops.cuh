@@ -112,8 +112,7 @@ __device__ __forceinline__ void silu_mul_row(const __half* __restrict__ gate, co
   const uint4* ur = reinterpret_cast<const uint4*>(up);
   uint4* orow = reinterpret_cast<uint4*>(out);
   float am = 0.f;
-  for (int i = threadIdx.x; i < n / 8; i += (int)blockDim.x) {
-    const uint4 gv = row_load<COHERENT>(gr + i), uv = row_load<COHERENT>(ur + i);
+  auto one = [&](const uint4& gv, const uint4& uv, int i) {
     const __half2* gp = reinterpret_cast<const __half2*>(&gv);
     const __half2* up2 = reinterpret_cast<const __half2*>(&uv);
     uint4 o;
@@ -128,6 +127,21 @@ __device__ __forceinline__ void silu_mul_row(const __half* __restrict__ gate, co
       am = fmaxf(am, fmaxf(f.x, f.y));
     }
     orow[i] = o;
+  };
+  // two vectors per thread and array are in flight at a time (a 14336-wide row is 1.75 vectors per thread of a
+  // 1024-thread CTA: all of its loads go out together)
+  const int nvec = n / 8, stride = (int)blockDim.x;
+  for (int i0 = threadIdx.x; i0 < nvec; i0 += 2 * stride) {
+    const int i1 = i0 + stride;
+    const bool two = i1 < nvec;
+    const uint4 g0 = row_load<COHERENT>(gr + i0), u0 = row_load<COHERENT>(ur + i0);
+    uint4 g1 = make_uint4(0, 0, 0, 0), u1 = g1;
+    if (two) {
+      g1 = row_load<COHERENT>(gr + i1);
+      u1 = row_load<COHERENT>(ur + i1);
+    }
+    one(g0, u0, i0);
+    if (two) one(g1, u1, i1);
   }
   if (absmax_out != nullptr) {
     am = row_block_reduce(am, red, true);
