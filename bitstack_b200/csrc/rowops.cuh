@@ -120,7 +120,7 @@ __device__ __forceinline__ void silu_mul_row(const __half* __restrict__ gate, co
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       const float2 a = __half22float2(gp[q]), b = __half22float2(up2[q]);
-      const __half2 s = __floats2half2_rn(a.x / (1.f + __expf(-a.x)), a.y / (1.f + __expf(-a.y)));   // fp16 SiLU
+      const __half2 s = __floats2half2_rn(__fdividef(a.x, 1.f + __expf(-a.x)), __fdividef(a.y, 1.f + __expf(-a.y)));   // fp16 SiLU
       const float2 sf = __half22float2(s);
       op[q] = __floats2half2_rn(sf.x * b.x, sf.y * b.y);
       const float2 f = __half22float2(__habs2(op[q]));

@@ -7,6 +7,15 @@ import torch.nn.functional as F
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(autouse=True)
+def _seed():
+    """Every test draws its random inputs from the same seed: greedy tokens of a random-init model sit on near-ties,
+    so an unseeded prompt makes the token comparisons below depend on the draw."""
+    torch.manual_seed(20241)
+    if torch.cuda.is_available():
+        torch.cuda.manual_seed_all(20241)
+
+
 @pytest.fixture(scope="module")
 def dev():
     if not torch.cuda.is_available():
