@@ -224,16 +224,17 @@ __global__ void __launch_bounds__(256) decode_attention_kernel(const __half* __r
     mine[2 + tid] = o;
   }
   if (tid == 0) { mine[0] = m; mine[1] = l; }
-  __threadfence();
   __syncthreads();
   if (tid == 0) {
-    const int old = atomicAdd(&counters[b * Hq + h], 1);
+    // the barrier ordered every thread's stores before this release, which orders them before the count; the
+    // acquiring count and the barrier below order the other shares' results before the loads (from L2)
+    int old;
+    asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(old) : "l"(counters + b * Hq + h) : "memory");
     s_last = (old == kAttSplits - 1);
     if (s_last) counters[b * Hq + h] = 0;   // ready for the next call
   }
   __syncthreads();
   if (!s_last) return;
-  __threadfence();
   if (tid < D) {
     const float* all = partial + ((int64_t)b * Hq + h) * kAttSplits * (D + 2);
     float mm = -INFINITY;
