@@ -387,6 +387,9 @@ int bsb_tuning_set_timeline(void* device_buffer, int32_t records) {
   gemv_tc5_set_timeline((unsigned long long*)device_buffer, records);
   return BSB_OK;
 }
+int bsb_tuning_mma_rate(int32_t n_cols, int32_t per_commit, int32_t iters, int32_t issuers, int32_t ctas_per_sm, float* ns_per_mma_per_sm) {
+  return gemv_tc5_mma_rate(n_cols, per_commit, iters, issuers, ctas_per_sm, ns_per_mma_per_sm);
+}
 #endif
 
 int64_t bsb_debug_launch_count(void) { return (int64_t)g_launches; }

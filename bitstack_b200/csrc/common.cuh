@@ -138,6 +138,7 @@ void gemv_tc5_set_wait_limit_ns(unsigned long long ns);
 void gemv_tc5_set_trace(unsigned long long* device_buffer);
 void gemv_tc5_set_dbg(int mode);
 void gemv_tc5_set_timeline(unsigned long long* device_buffer, int records);
+int gemv_tc5_mma_rate(int n_cols, int per_commit, int iters, int issuers, int ctas_per_sm, float* ns_per_mma_per_sm);
 #endif
 // out_f32: the ys point at fp32 rows (partial sums of a tensor-parallel shard) instead of fp16 ones;
 // x_absmax: optional max |x| per row of this pass

@@ -30,6 +30,8 @@
 #define BSB_TUNING
 #endif
 
+#include <vector>
+
 #include "common.cuh"
 
 namespace bsb {
@@ -1283,6 +1285,107 @@ int launch_gemv_tc5(const bsb_weight* ws, int n_weights, const __half* x, int64_
   profile_mark(s, true);
   return check_launch("gemv_tc5_kernel");
 }
+
+#ifdef BSB_TUNING
+// ------------------------------------------------------------------ issue-rate probe (tuning build only)
+// What one multiprocessor can do with the decode kernel's MMA: every CTA has `issuers` warps (1 or 2), each with its
+// own accumulator of n_cols columns and its own barrier; the elected lane of a warp issues `per_commit` M128 x n_cols
+// x K32 e4m3 MMAs (A from tensor memory, B from shared memory), commits, waits for the commit -- `iters` times -- and
+// reports the wall-clock time of its loop.  alloc_cols (256 or 512 tensor-memory columns per CTA) decides whether two
+// CTAs or one fit on a multiprocessor.
+namespace {
+__global__ void __launch_bounds__(128) mma_rate_kernel(int n_cols, int per_commit, int iters, int issuers, int alloc_cols,
+                                                       unsigned long long wait_ns, unsigned long long* ns_out, int* status) {
+  __shared__ __align__(1024) uint8_t b_tile[256 * 32];   // up to 256 columns x 32 bytes of K, K-major, no swizzle
+  __shared__ uint64_t bar[2];
+  __shared__ uint32_t tmem_slot;
+  const int warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < 256 * 32 / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(b_tile)[i] = 0x38383838u;   // 1.0
+  if (warp == 0) {
+    tmem_alloc(&tmem_slot, alloc_cols);
+    tmem_relinquish();
+  }
+  if (threadIdx.x == 0) {
+    mbar_init(&bar[0], 1);
+    mbar_init(&bar[1], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the generic-proxy writes of b_tile before the MMAs read it
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tbase = tmem_slot;
+  const uint32_t a_col = tbase + issuers * n_cols;   // the A operand: 32 columns behind the accumulators, zeroed
+  {
+    uint32_t z[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) z[i] = 0u;
+    tmem_st32(a_col + ((uint32_t)(warp * 32) << 16), z);
+    tmem_wait_st();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp < issuers) {
+    const bool leader = elect_one();
+    const uint32_t idesc = make_idesc_f8(128, n_cols);
+    const uint64_t bdesc = make_smem_desc(smem_u32(b_tile), 128, 256);
+    const uint32_t d = tbase + warp * n_cols;
+    const uint64_t t0 = global_ns();
+    bool ok = true;
+    for (int it = 0; it < iters && ok; ++it) {
+      if (leader) {
+        mma_ts_f8_first(d, a_col, bdesc, idesc, it > 0 ? 1u : 0u);
+        for (int k = 1; k < per_commit; ++k) mma_ts_f8_acc(d, a_col, bdesc, idesc);
+        mma_commit(&bar[warp]);
+      }
+      __syncwarp();
+      if (!mbar_wait(&bar[warp], it & 1, wait_ns)) {
+        if (leader) atomicCAS(status, 0, 90);
+        ok = false;
+      }
+    }
+    if (leader) ns_out[blockIdx.x * 2 + warp] = global_ns() - t0;
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    __syncwarp();
+    tmem_dealloc(tbase, alloc_cols);
+  }
+}
+}  // namespace
+
+// ns per MMA per multiprocessor (all issuers of all its CTAs together), from the slowest issuer of the grid
+int gemv_tc5_mma_rate(int n_cols, int per_commit, int iters, int issuers, int ctas_per_sm, float* ns_per_mma_per_sm) {
+  BSB_CHECK_ARG(n_cols >= 16 && n_cols <= 256 && n_cols % 16 == 0 && per_commit >= 1 && iters >= 1 && (issuers == 1 || issuers == 2) &&
+                (ctas_per_sm == 1 || ctas_per_sm == 2) && ns_per_mma_per_sm != nullptr, "mma rate probe: bad arguments");
+  const int alloc_cols = ctas_per_sm == 2 ? 256 : 512;
+  BSB_CHECK_ARG(issuers * n_cols + 32 <= alloc_cols, "mma rate probe: %d accumulators of %d columns do not fit %d columns", issuers, n_cols, alloc_cols);
+  const int grid = sm_count() * ctas_per_sm;
+  unsigned long long* d_ns = nullptr;
+  BSB_CUDA(cudaMalloc(&d_ns, (size_t)grid * 2 * sizeof(unsigned long long)));
+  BSB_CUDA(cudaMemset(d_ns, 0, (size_t)grid * 2 * sizeof(unsigned long long)));
+  int* status = device_status_word();
+  if (status == nullptr) return BSB_ECUDA;
+  // unused dynamic shared memory pins the number of CTAs a multiprocessor can host to ctas_per_sm
+  const int dyn_smem = (ctas_per_sm == 2 ? 100 : 200) * 1024;
+  BSB_CUDA(cudaFuncSetAttribute(mma_rate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn_smem));
+  mma_rate_kernel<<<grid, 128, dyn_smem>>>(n_cols, per_commit, iters, issuers, alloc_cols, g_wait_ns, d_ns, status);
+  cudaError_t e = cudaDeviceSynchronize();
+  std::vector<unsigned long long> h((size_t)grid * 2);
+  if (e == cudaSuccess) e = cudaMemcpy(h.data(), d_ns, h.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
+  cudaFree(d_ns);
+  if (e != cudaSuccess) {
+    set_error("mma rate probe: %s", cudaGetErrorString(e));
+    return BSB_ECUDA;
+  }
+  unsigned long long worst = 0;
+  for (unsigned long long v : h) worst = v > worst ? v : worst;
+  *ns_per_mma_per_sm = (float)((double)worst / ((double)iters * per_commit * issuers * ctas_per_sm));
+  return BSB_OK;
+}
+#endif
 
 }  // namespace bsb
 
