@@ -1008,7 +1008,7 @@ struct TcPlan {
   int64_t absmax_off[kMaxGroup];
 };
 
-constexpr int kMinStepsPair = 4;
+constexpr int kMinStepsPair = 1;   // measured: two row tiles per CTA are as fast or faster as soon as every CTA still gets a step
 #ifdef BSB_TUNING
 static int g_force_rt = 0;      // 0 = choose, 1 / 2 = forced
 static int g_target_ctas = 0;   // 0 = two per multiprocessor, else this many
@@ -1038,7 +1038,7 @@ void make_tc_plan(const bsb_weight* ws, int n, int R, TcPlan& pl) {
     steps1 += ceil_div64(ws[i].out_features, kTileRows) * ws[i].blocks * P.n_chunks;
     steps2 += ceil_div64(ws[i].out_features, 2 * kTileRows) * ws[i].blocks * P.n_chunks;
   }
-  // two row tiles per CTA halve the Z' traffic; taken when every CTA still gets a few steps
+  // two row tiles per CTA halve the Z' traffic; taken when every CTA still gets a step
   int RT = (steps2 >= (int64_t)target * kMinStepsPair) ? 2 : 1;
 #ifdef BSB_TUNING
   if (g_force_rt) RT = g_force_rt;
