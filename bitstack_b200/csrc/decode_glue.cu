@@ -99,7 +99,10 @@ __global__ void __launch_bounds__(256) decode_attention_kernel(const __half* __r
   // this one started (every kernel of the chain waits for its predecessor before it ends), so they may be read
   // before this kernel's own wait: the first K row of every thread is in flight while the projection kernel drains.
   const int64_t pos = *pos_p;
-  if (pos < 0 || pos >= max_len) return;   // out of the cache: nothing is written
+  if (pos < 0 || pos >= max_len) {   // out of the cache: nothing is written (the kernel still takes its place in the chain of waits)
+    pdl_enter();
+    return;
+  }
   const int hk = h / (Hq / Hkv);
   __half* kc = k_cache + ((int64_t)b * Hkv + hk) * (int64_t)max_len * D;
   __half* vc = v_cache + ((int64_t)b * Hkv + hk) * (int64_t)max_len * D;
