@@ -32,7 +32,9 @@ __global__ void __launch_bounds__(128) rope_cache_kernel(__half* __restrict__ q,
                                                          const __half* __restrict__ sin_t, const int64_t* __restrict__ pos_p,
                                                          __half* __restrict__ k_cache, __half* __restrict__ v_cache,
                                                          int Hq, int Hkv, int D, int max_len) {
-  pdl_enter();
+  // no early release of the kernel behind this one: decode_attention_kernel reads cache rows in front of its own wait,
+  // which is only safe for rows whose writer has finished before it starts
+  pdl_wait();
   const int b = blockIdx.y, head = blockIdx.x;
   const int64_t pos = *pos_p;
   if (pos < 0 || pos >= max_len) return;   // out of the cache: nothing is written
@@ -260,7 +262,7 @@ __global__ void __launch_bounds__(1024) greedy_step_kernel(const __half* __restr
                                                            int64_t* __restrict__ tokens, int64_t* __restrict__ pos) {
   __shared__ float s_val[32];
   __shared__ int64_t s_idx[32];
-  pdl_enter();
+  pdl_wait();   // no early release: this kernel writes *pos, which decode_attention_kernel reads in front of its own wait
   const __half* row = logits + (int64_t)blockIdx.x * stride;
   float best = -INFINITY;
   int64_t best_i = INT64_MAX;

@@ -158,6 +158,9 @@ int64_t bsb_linear_grouped_workspace_bytes(const bsb_weight* ws, int32_t n_weigh
  *   token per batch row, grouped-query heads, fp32 softmax; out[batch][q_heads*dim].  head_dim 64 or 128,
  *   max_len <= 8192.  `scratch` (bsb_decode_attention_scratch_bytes, 16-byte aligned) must be ZERO before its
  *   first use and is left ready for the next call; calls sharing a scratch must be stream-ordered.
+ *   *pos and the cache rows below it are read before the kernel waits for the work in front of it: they must not be
+ *   written by the kernel launched directly before this call (bsb_rope_cache and bsb_greedy_step, which write them,
+ *   never release their successor early, so calling those directly before is fine).
  * bsb_greedy_step: tokens[b] = first index of the maximum of logits[b][0..vocab) (fp16 rows row_stride apart), then
  *   *pos += 1 (pos may be NULL): the sampling and bookkeeping of a greedy decode step in one launch.
  * bsb_silu_mul: out = silu(gate) * up on [rows][n] fp16 (n % 8 == 0, 16-byte aligned); out_absmax (fp32 [rows], may be
